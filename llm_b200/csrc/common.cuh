@@ -1,0 +1,81 @@
+// Shared helpers of the hand-written kernels: element conversion, vector access,
+// block reductions with a fixed order, and the error channel to the host.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <type_traits>
+
+#define LLMK_API extern "C" __attribute__((visibility("default")))
+
+// Element kinds as the host passes them.
+enum : int { LLMK_F32 = 0, LLMK_BF16 = 1 };
+
+// Return codes: 0 ok, > 0 a cudaError_t, < 0 an argument that this kernel refuses
+// (the text is kept for llmk_last_error()).
+int llmk_fail(int code, const char* fmt, ...);
+
+#define LLMK_REQUIRE(cond, ...)                          \
+  do {                                                   \
+    if (!(cond)) return llmk_fail(-1, __VA_ARGS__);      \
+  } while (0)
+
+#define LLMK_LAUNCH_CHECK(name)                                             \
+  do {                                                                      \
+    cudaError_t e__ = cudaPeekAtLastError();                                \
+    if (e__ != cudaSuccess) {                                               \
+      cudaGetLastError();                                                   \
+      return llmk_fail((int)e__, "%s: %s", name, cudaGetErrorString(e__)); \
+    }                                                                       \
+    return 0;                                                               \
+  } while (0)
+
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  static __device__ __forceinline__ float to_f32(float v) { return v; }
+  static __device__ __forceinline__ float from_f32(float v) { return v; }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+};
+
+template <typename T> __device__ __forceinline__ float to_f32(T v) { return Elem<T>::to_f32(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v) { return Elem<T>::from_f32(v); }
+
+// Sum over a warp, then over the warps of a block, in a fixed order: the result
+// for a row never depends on which other rows the launch holds.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// All threads get the sum. `scratch` holds 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < nwarps; ++w) t += scratch[w];
+  return t;
+}
+
+#define LLMK_ELEM(tag) typename std::remove_pointer<decltype(tag)>::type
+
+template <typename F>
+inline int dispatch_dtype(int dtype, F&& f) {
+  if (dtype == LLMK_F32) return f((float*)nullptr);
+  if (dtype == LLMK_BF16) return f((__nv_bfloat16*)nullptr);
+  return llmk_fail(-1, "unknown element kind %d (0 = float32, 1 = bfloat16)", dtype);
+}

@@ -1,0 +1,166 @@
+"""Python faces of the kernels: each takes torch tensors on the GPU, checks what
+the kernel assumes, and calls the C entry point on the current stream.  There is
+no other implementation behind them: without the library, or with a tensor that is
+not on a CUDA device, they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .build import load
+
+_F32, _BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _kind(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return _F32
+    if dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"kernels take float32 or bfloat16, got {dtype}")
+
+
+def _ptr(t, name="tensor"):
+    if t is None:
+        return c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError(f"{name} must live on a CUDA device (there is no CPU path)")
+    return c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int) -> None:
+    if code != 0:
+        msg = load().llmk_last_error().decode("utf-8", "replace")
+        raise KernelError(f"kernel call failed ({code}): {msg}")
+
+
+def _rows_contig(t: torch.Tensor, name: str) -> None:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be 2-D with unit stride in its last dimension")
+
+
+def embedding(resid: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, n_tokens: int,
+              status: torch.Tensor) -> None:
+    """resid[:n_tokens] (float32) = table[ids]; an id outside the table sets status[0]."""
+    assert resid.dtype == torch.float32 and ids.dtype == torch.int32 and status.dtype == torch.int32
+    assert resid.is_contiguous() and table.is_contiguous()
+    vocab, hidden = table.shape
+    _check(load().llmk_embedding(_ptr(resid), _ptr(table), _ptr(ids), c_int(n_tokens), c_int(hidden),
+                                 c_int(vocab), c_int(_kind(table.dtype)), _ptr(status), _stream()))
+
+
+def add_rmsnorm(resid: torch.Tensor, delta, gamma: torch.Tensor, out, rows: int, eps: float) -> None:
+    """resid[:rows] += delta (if given); out[:rows] = rmsnorm(resid) * gamma (if out given)."""
+    assert resid.dtype == torch.float32 and gamma.dtype == torch.float32 and resid.is_contiguous()
+    hidden = resid.shape[-1]
+    ref = out if out is not None else delta
+    if ref is None:
+        return
+    if delta is not None:
+        assert delta.is_contiguous() and delta.shape[-1] == hidden
+    if out is not None:
+        assert out.is_contiguous() and out.shape[-1] == hidden
+        if delta is not None:
+            assert delta.dtype == out.dtype
+    _check(load().llmk_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(gamma), _ptr(out), c_int(rows),
+                                   c_int(hidden), c_float(eps), c_int(_kind(ref.dtype)), _stream()))
+
+
+def gather_rows(out: torch.Tensor, resid: torch.Tensor, delta, rows: torch.Tensor, n_rows: int) -> None:
+    """out[r] = resid[rows[r]] (+ delta[rows[r]]), float32."""
+    assert out.dtype == torch.float32 and resid.dtype == torch.float32 and rows.dtype == torch.int32
+    kind = _kind(delta.dtype) if delta is not None else _F32
+    _check(load().llmk_gather_rows(_ptr(out), _ptr(resid), _ptr(delta), _ptr(rows), c_int(n_rows),
+                                   c_int(resid.shape[-1]), c_int(kind), _stream()))
+
+
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, rows: int) -> None:
+    """out[:rows, :I] = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    inter = out.shape[-1]
+    assert gate_up.shape[-1] == 2 * inter and out.is_contiguous() and gate_up.is_contiguous()
+    assert out.dtype == gate_up.dtype
+    _check(load().llmk_silu_mul(_ptr(out), _ptr(gate_up), c_int(rows), c_int(inter),
+                                c_int(_kind(out.dtype)), _stream()))
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int) -> None:
+    """out[:rows] = a[:rows] @ w.T with float32 accumulation on the CUDA cores."""
+    _rows_contig(a, "a"); _rows_contig(w, "w"); _rows_contig(out, "out")
+    n, k = w.shape
+    assert a.shape[1] == k and out.shape[1] == n and a.dtype == w.dtype
+    _check(load().llmk_gemm_simt(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
+                                 c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
+                                 c_int(_kind(a.dtype)), c_int(_kind(out.dtype)), _stream()))
+
+
+def rope_kv_write(qkv: torch.Tensor, cos, sin, positions: torch.Tensor, slot_map: torch.Tensor,
+                  k_pages: torch.Tensor, v_pages: torch.Tensor, n_tokens: int, n_heads: int, n_kv: int,
+                  head_dim: int) -> None:
+    """Rotate q (in place) and k by the tables, store k and v at slot_map in the pages."""
+    _rows_contig(qkv, "qkv")
+    assert k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == qkv.dtype
+    assert positions.dtype == torch.int32 and slot_map.dtype == torch.int32
+    assert k_pages.shape[1] == n_kv and k_pages.shape[3] == head_dim
+    assert qkv.shape[1] >= (n_heads + 2 * n_kv) * head_dim
+    if cos is not None:
+        assert cos.dtype == torch.float32 and sin.dtype == torch.float32
+        assert cos.shape[1] == head_dim // 2 and cos.is_contiguous() and sin.is_contiguous()
+    _check(load().llmk_rope_kv_write(_ptr(qkv), c_longlong(qkv.stride(0)), _ptr(cos), _ptr(sin),
+                                     _ptr(positions), _ptr(slot_map), _ptr(k_pages), _ptr(v_pages),
+                                     c_int(n_tokens), c_int(n_heads), c_int(n_kv), c_int(head_dim),
+                                     c_int(k_pages.shape[2]), c_int(_kind(qkv.dtype)), _stream()))
+
+
+def paged_attention_generic(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                            block_table: torch.Tensor, token_entry: torch.Tensor, positions: torch.Tensor,
+                            n_tokens: int, n_heads: int, n_kv: int, head_dim: int, window: int,
+                            scale: float) -> None:
+    """out[t, h*HS:(h+1)*HS] = causal (windowed) attention of q[t, h] over its request's pages."""
+    _rows_contig(out, "out"); _rows_contig(q, "q")
+    assert block_table.dim() == 2 and block_table.is_contiguous() and block_table.dtype == torch.int32
+    assert token_entry.dtype == torch.int32 and positions.dtype == torch.int32
+    assert k_pages.is_contiguous() and v_pages.is_contiguous() and q.dtype == k_pages.dtype == out.dtype
+    _check(load().llmk_paged_attention_generic(
+        _ptr(out), c_longlong(out.stride(0)), _ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
+        _ptr(block_table), c_int(block_table.shape[1]), _ptr(token_entry), _ptr(positions), c_int(n_tokens),
+        c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(k_pages.shape[2]), c_int(window or 0),
+        c_float(scale), c_int(_kind(q.dtype)), _stream()))
+
+
+def sample_rows(out: torch.Tensor, logits: torch.Tensor, rows: int, temperature=None, uniform=None) -> None:
+    """out[r] = argmax of logits[r] (ties to the lowest id) where temperature[r] <= 0 or no
+    temperatures are given, else the inverse-CDF draw of softmax(logits[r] / temperature[r])
+    at uniform[r]."""
+    _rows_contig(logits, "logits")
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32
+    if temperature is not None:
+        assert temperature.dtype == torch.float32 and uniform is not None and uniform.dtype == torch.float32
+    _check(load().llmk_sample_rows(_ptr(out), _ptr(logits), c_longlong(logits.stride(0)), c_int(rows),
+                                   c_int(logits.shape[1]), _ptr(temperature), _ptr(uniform), _stream()))
+
+
+def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: int, head_dim: int,
+                    window: int, scale: float) -> None:
+    """Attention of the step's tokens over their requests' pages; q is the first
+    n_heads * head_dim columns of qkv.  Chooses the kernel for the batch."""
+    paged_attention_generic(out, qkv, k_pages, v_pages, group.block_table, ctx.token_entry, ctx.positions,
+                            ctx.n_tokens, n_heads, n_kv, head_dim, window, scale)
+
+
+def gemm_fast_available(a, w, out, rows: int) -> bool:
+    return False
+
+
+def gemm_fast(a, w, out, rows: int) -> None:
+    raise KernelError("no tensor-core product is built")

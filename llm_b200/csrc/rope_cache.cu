@@ -1,0 +1,70 @@
+// Rotate-half RoPE on q and k, and the write of k and v into the paged cache.
+//
+// The reference does this in the epilogue of its QKV product
+// (kernel/Gemm/QKVGemm.h:27-63): (a, b) = (x_i, x_{i+HS/2}),
+// y_i = a*cos - b*sin, y_{i+HS/2} = a*sin + b*cos with float32 tables
+// (kernel/embedding/RoPECache.h:15-20), k and v stored at the physical place that
+// the step's metadata names (runtime/Engine.h:62-67).  This stand-alone form serves
+// every size; the cache layout is [page][kv_head][token in page][head_dim].
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long qkv_stride,
+                                     const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+                                     int rot_half, const int* __restrict__ positions,
+                                     const int* __restrict__ slot_map, T* __restrict__ k_pages,
+                                     T* __restrict__ v_pages, int n_heads, int n_kv, int head_dim,
+                                     int page_size) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int slot = slot_map[t];
+  const int page = slot / page_size, off = slot % page_size;
+  T* row = qkv + (size_t)t * qkv_stride;
+  const int half = head_dim / 2;
+  const float* cs = cos_table ? cos_table + (size_t)pos * rot_half : nullptr;
+  const float* sn = cos_table ? sin_table + (size_t)pos * rot_half : nullptr;
+  const int rot_items = (n_heads + n_kv) * half;
+  for (int idx = threadIdx.x; idx < rot_items; idx += blockDim.x) {
+    const int head = idx / half, i = idx % half;
+    T* h = row + (size_t)head * head_dim;
+    const float a = to_f32(h[i]), b = to_f32(h[i + half]);
+    const float c = cs ? cs[i] : 1.f, s = cs ? sn[i] : 0.f;
+    const T ya = from_f32<T>(a * c - b * s), yb = from_f32<T>(a * s + b * c);
+    if (head < n_heads) {
+      h[i] = ya;
+      h[i + half] = yb;
+    } else {
+      const int g = head - n_heads;
+      T* dst = k_pages + (((size_t)page * n_kv + g) * page_size + off) * head_dim;
+      dst[i] = ya;
+      dst[i + half] = yb;
+    }
+  }
+  const T* v = row + (size_t)(n_heads + n_kv) * head_dim;
+  for (int idx = threadIdx.x; idx < n_kv * head_dim; idx += blockDim.x) {
+    const int g = idx / head_dim, d = idx % head_dim;
+    v_pages[(((size_t)page * n_kv + g) * page_size + off) * head_dim + d] = v[idx];
+  }
+}
+
+}  // namespace
+
+// qkv [n_tokens, qkv_stride]: q heads, then k heads, then v heads in a row.  q is rotated in
+// place; rotated k and plain v go to the pages.  Tables are [max_position, head_dim/2]; without
+// tables (null) nothing is rotated and k, v are only stored.
+LLMK_API int llmk_rope_kv_write(void* qkv, long long qkv_stride, const float* cos_table,
+                                const float* sin_table, const int* positions, const int* slot_map,
+                                void* k_pages, void* v_pages, int n_tokens, int n_heads, int n_kv,
+                                int head_dim, int page_size, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  LLMK_REQUIRE(head_dim % 2 == 0, "rope_kv_write: head_dim %d must be even", head_dim);
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    rope_kv_write_kernel<T><<<n_tokens, 128, 0, stream>>>((T*)qkv, qkv_stride, cos_table, sin_table,
+                                                         head_dim / 2, positions, slot_map, (T*)k_pages,
+                                                         (T*)v_pages, n_heads, n_kv, head_dim, page_size);
+    LLMK_LAUNCH_CHECK("rope_kv_write");
+  });
+}

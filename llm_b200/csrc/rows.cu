@@ -1,0 +1,154 @@
+// Row-wise kernels: embedding gather, residual add fused with RMSNorm, row gather
+// for the LM head, SiLU(gate) * up.  The residual stream is float32 in every mode;
+// sums, the reciprocal root and the scaling are float32 as well.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+// ---- error channel ----------------------------------------------------------
+static thread_local char g_last_error[512] = "";
+
+int llmk_fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+LLMK_API const char* llmk_last_error() { return g_last_error; }
+LLMK_API int llmk_abi_version() { return 1; }
+
+// ---- embedding --------------------------------------------------------------
+// resid[t, :] = table[ids[t], :]   (the reference copies rows without scaling,
+// kernel/embedding/TokenEmbedding.h:12-17).  An id outside the table sets *status.
+template <typename T>
+__global__ void embedding_kernel(float* __restrict__ resid, const T* __restrict__ table,
+                                 const int* __restrict__ ids, int hidden, int vocab,
+                                 int* __restrict__ status) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicExch(status, 1);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) resid[(size_t)t * hidden + c] = 0.f;
+    return;
+  }
+  const T* row = table + (size_t)id * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) resid[(size_t)t * hidden + c] = to_f32(row[c]);
+}
+
+LLMK_API int llmk_embedding(float* resid, const void* table, const int* ids, int n_tokens, int hidden,
+                            int vocab, int dtype, int* status, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    embedding_kernel<T><<<n_tokens, 256, 0, stream>>>(resid, (const T*)table, ids, hidden, vocab, status);
+    LLMK_LAUNCH_CHECK("embedding");
+  });
+}
+
+// ---- residual add + RMSNorm -------------------------------------------------
+// resid += delta (if delta); out = resid * rsqrt(mean(resid^2) + eps) * gamma.
+// The reference runs the add and the norm as two kernels (kernel/residual/Residual.h:17-19,
+// kernel/LayerNorm/RMSNorm.h:13-30,40-42); here they share one pass over the row.
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                   const float* __restrict__ gamma, T* __restrict__ out, int hidden,
+                                   float eps) {
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * hidden;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = resid[base + c];
+    if (delta) {
+      v += to_f32(delta[base + c]);
+      resid[base + c] = v;
+    }
+    ss += v * v;
+  }
+  const float total = block_sum(ss, scratch);
+  const float rstd = rsqrtf(total / (float)hidden + eps);
+  if (out) {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+      out[base + c] = from_f32<T>(resid[base + c] * rstd * gamma[c]);
+  }
+}
+
+LLMK_API int llmk_add_rmsnorm(float* resid, const void* delta, const float* gamma, void* out, int rows,
+                              int hidden, float eps, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    add_rmsnorm_kernel<T><<<rows, 256, 0, stream>>>(resid, (const T*)delta, gamma, (T*)out, hidden, eps);
+    LLMK_LAUNCH_CHECK("add_rmsnorm");
+  });
+}
+
+// ---- residual add without a norm (the stream's pending term folded in) ------
+template <typename T>
+__global__ void add_kernel(float* __restrict__ resid, const T* __restrict__ delta, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    resid[i] += to_f32(delta[i]);
+}
+
+LLMK_API int llmk_add(float* resid, const void* delta, long long n, int dtype, cudaStream_t stream) {
+  if (n == 0) return 0;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    add_kernel<T><<<blocks, 256, 0, stream>>>(resid, (const T*)delta, (size_t)n);
+    LLMK_LAUNCH_CHECK("add");
+  });
+}
+
+// ---- gather of the rows whose logits are wanted -----------------------------
+// out[r, :] = resid[rows[r], :] (+ delta[rows[r], :]).  The reference runs its LM head
+// on every row (model/modules/Linear.h:25); gathering first leaves only wanted rows.
+template <typename T>
+__global__ void gather_rows_kernel(float* __restrict__ out, const float* __restrict__ resid,
+                                   const T* __restrict__ delta, const int* __restrict__ rows, int hidden) {
+  const size_t src = (size_t)rows[blockIdx.x] * hidden, dst = (size_t)blockIdx.x * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = resid[src + c];
+    if (delta) v += to_f32(delta[src + c]);
+    out[dst + c] = v;
+  }
+}
+
+LLMK_API int llmk_gather_rows(float* out, const float* resid, const void* delta, const int* rows,
+                              int n_rows, int hidden, int dtype, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    gather_rows_kernel<T><<<n_rows, 256, 0, stream>>>(out, resid, (const T*)delta, rows, hidden);
+    LLMK_LAUNCH_CHECK("gather_rows");
+  });
+}
+
+// ---- SiLU(gate) * up --------------------------------------------------------
+// in [rows, 2*inter]: gate in the first half of a row, up in the second.
+// act = g / (1 + exp(-g)) * u in float32 (kernel/activation/SwiGLU.h:31-33).
+template <typename T>
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ in, int inter, size_t total) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / inter, c = i % inter;
+    const float g = to_f32(in[r * 2 * inter + c]);
+    const float u = to_f32(in[r * 2 * inter + inter + c]);
+    out[i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+LLMK_API int llmk_silu_mul(void* out, const void* gate_up, int rows, int inter, int dtype,
+                           cudaStream_t stream) {
+  const size_t total = (size_t)rows * inter;
+  if (total == 0) return 0;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    silu_mul_kernel<T><<<(int)blocks, 256, 0, stream>>>((T*)out, (const T*)gate_up, inter, total);
+    LLMK_LAUNCH_CHECK("silu_mul");
+  });
+}

@@ -1,0 +1,329 @@
+"""The engine: a model on one GPU with its cache, and one step function.
+
+step() takes a batch of (request, its next tokens, the places whose logits are
+wanted): portions of prompts beside single decoded tokens, cut anywhere.  It runs
+only those tokens, as one batch, against the cache that earlier steps left, and
+returns float32 logits at the wanted places.  It is what the reference splits over
+LLM::inference (runtime/LLM.h:205-219) and Engine::prepare (runtime/Engine.h:52-71),
+with three differences: prompt portions and decoded tokens share a batch, the LM
+head runs on wanted rows only, and sampling is a layer above.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, GroupSpec, OutOfPages
+from ..cache.storage import CacheStorage, StateStorage, bytes_per_page
+from ..config.engine_options import EngineOptions
+from ..config.model_config import load_config, parse_config
+from ..csrc import ops
+from ..csrc.build import load as load_kernels
+from ..parts.base import ResidualStream
+from ..weights.loader import load_tensors
+from .context import GroupView, LayerView, StepContext, Workspace
+from .model import Model
+
+_TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class StepError(ValueError):
+    """A batch that the step function refuses."""
+
+
+@dataclass
+class StepEntry:
+    request_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=list)   # indices into tokens
+
+
+class _MetaLayout:
+    """Offsets of the step's int32 metadata inside one buffer (one copy per step)."""
+
+    def __init__(self, max_tokens: int, max_entries: int, max_rows: int, table_widths: List[int]):
+        off = 0
+
+        def take(n):
+            nonlocal off
+            start = off
+            off += (n + 3) // 4 * 4          # keep every array 16-byte aligned
+            return start
+
+        self.cu_tokens = take(max_entries + 1)
+        self.kv_lens = take(max_entries)
+        self.state_slots = take(max_entries)
+        self.token_ids = take(max_tokens)
+        self.positions = take(max_tokens)
+        self.token_entry = take(max_tokens)
+        self.logit_rows = take(max_rows)
+        self.slot_map = [take(max_tokens) for _ in table_widths]
+        self.block_table = [take(max_entries * w) for w in table_widths]
+        self.total = off
+
+
+class Engine:
+    def __init__(self, model_dir: str, options: Optional[EngineOptions] = None):
+        self.options = options = options or EngineOptions()
+        options.validate()
+        if not torch.cuda.is_available():
+            raise RuntimeError("llm_b200 needs a CUDA device: there is no CPU path")
+        load_kernels()
+        self.device = torch.device(options.device)
+        torch.cuda.set_device(self.device)
+        self.dtype = _TORCH_DTYPE[options.dtype]
+
+        self.arch, self.config = load_config(model_dir)
+        self.spec = self.arch.build_spec(self.config)
+        self.model = Model(self.spec, self.dtype, self.device)
+        self.model.bind(load_tensors(model_dir, self.model.parameters(), self.dtype, self.device))
+
+        self.max_seq_len = options.max_seq_len or self.spec.max_position
+        if self.max_seq_len > self.spec.max_position:
+            raise ValueError(f"max_seq_len {self.max_seq_len} exceeds the model's max_position "
+                             f"{self.spec.max_position}")
+        self.max_tokens = options.max_num_batched_tokens
+        self.max_entries = options.max_num_seqs
+        self.max_rows = options.max_logit_rows or self.max_tokens
+        self.page_size = options.kv_block_size
+        self.hidden, self.vocab = self.spec.hidden_size, self.spec.vocab_size
+
+        self._init_cache()
+        self._init_buffers()
+        self._graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
+        self.counters = {"steps": 0, "tokens": 0, "graph_captures": 0, "graph_replays": 0}
+
+    # ---- set-up -------------------------------------------------------------
+    def _init_cache(self) -> None:
+        opt, model = self.options, self.model
+        per_seq_full = (self.max_seq_len + self.page_size - 1) // self.page_size
+        pages: List[int] = []
+        cap = {}
+        for g, (kind, window) in enumerate(model.group_keys):
+            if kind == "window":
+                per_seq = (window + self.max_tokens + self.page_size - 1) // self.page_size + 2
+                cap[g] = self.max_entries * min(per_seq, per_seq_full)
+            else:
+                cap[g] = self.max_entries * per_seq_full
+        if opt.num_kv_blocks is not None:
+            pages = [opt.num_kv_blocks for _ in model.group_keys]
+        else:
+            free, _total = torch.cuda.mem_get_info(self.device)
+            budget = int(free * opt.gpu_memory_utilization) - self._activation_estimate()
+            for g, (kind, _w) in enumerate(model.group_keys):
+                if kind == "window":
+                    pages.append(cap[g])
+                    budget -= cap[g] * bytes_per_page(model.cache_instances, g, self.page_size, self.dtype)
+                else:
+                    pages.append(-1)
+            for g, (kind, _w) in enumerate(model.group_keys):
+                if pages[g] < 0:
+                    per = bytes_per_page(model.cache_instances, g, self.page_size, self.dtype)
+                    pages[g] = max(0, min(cap[g], budget // max(per, 1)))
+            if any(p <= 0 for p in pages):
+                raise RuntimeError("not enough free GPU memory for the cache pool")
+        specs = [GroupSpec(kind, self.page_size, pages[g], window)
+                 for g, (kind, window) in enumerate(model.group_keys)]
+        self.cache = CacheManager(specs, self.max_entries, self.max_seq_len)
+        self.cache_storage = CacheStorage(model.cache_instances, pages, self.page_size, self.dtype, self.device)
+        self.state_storage = StateStorage(model.state_needs, self.max_entries, self.device)
+
+    def _activation_estimate(self) -> int:
+        widest = 4 * self.spec.hidden_size * 8          # a generous guess of scratch columns per row
+        return self.options.max_num_batched_tokens * widest * 4 + (512 << 20)
+
+    def _init_buffers(self) -> None:
+        widths = [self.cache.table_width(g) for g in range(self.cache.num_groups)]
+        self.layout = lay = _MetaLayout(self.max_tokens, self.max_entries, self.max_rows, widths)
+        self._host_ring = [torch.zeros(lay.total, dtype=torch.int32).pin_memory() for _ in range(4)]
+        self._host_events = [None] * len(self._host_ring)
+        self._ring_at = 0
+        self.meta = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.resid = torch.zeros((self.max_tokens, self.hidden), dtype=torch.float32, device=self.device)
+        self.workspace = Workspace(self.max_tokens, self.device)
+        self._head_rows = None
+        self._logits = None
+
+        def dev(off, n):
+            return self.meta[off:off + n]
+
+        self._groups = {
+            g: GroupView(page_size=self.page_size,
+                         block_table=dev(lay.block_table[g], self.max_entries * widths[g]).view(self.max_entries, widths[g]),
+                         slot_map=dev(lay.slot_map[g], self.max_tokens),
+                         kind=self.cache.group_spec(g).kind, window=self.cache.group_spec(g).window)
+            for g in range(self.cache.num_groups)
+        }
+        self._views = []
+        for occ in self.model.occurrences:
+            view = LayerView(owns_cache=occ.owns_cache)
+            if occ.cache_instance is not None:
+                inst = self.model.cache_instances[occ.cache_instance]
+                view.group = self._groups[inst.group]
+                view.k_pages, view.v_pages = self.cache_storage.pages(occ.cache_instance)
+            if occ.state_instance is not None:
+                view.state = self.state_storage.tensor(occ.state_instance)
+            self._views.append(view)
+        self._ctx = StepContext(
+            n_tokens=0, n_entries=0, n_logit_rows=0,
+            token_ids=dev(lay.token_ids, self.max_tokens), positions=dev(lay.positions, self.max_tokens),
+            token_entry=dev(lay.token_entry, self.max_tokens), cu_tokens=dev(lay.cu_tokens, self.max_entries + 1),
+            kv_lens=dev(lay.kv_lens, self.max_entries), state_slots=dev(lay.state_slots, self.max_entries),
+            logit_rows=dev(lay.logit_rows, self.max_rows), status=self.status,
+            groups=self._groups, workspace=self.workspace)
+
+    def _logit_buffers(self, rows: int):
+        if self._logits is None or self._logits.shape[0] < rows:
+            n = max(rows, min(self.max_rows, 64))
+            self._head_rows = torch.zeros((n, self.hidden), dtype=torch.float32, device=self.device)
+            self._head_normed = torch.zeros((n, self.hidden), dtype=self.dtype, device=self.device)
+            self._logits = torch.zeros((n, self.vocab), dtype=torch.float32, device=self.device)
+            self._graphs.clear()         # captured graphs hold the old addresses
+        return self._head_rows, self._head_normed, self._logits
+
+    # ---- requests -----------------------------------------------------------
+    def release(self, request_id: Hashable) -> None:
+        """The request is finished: its pages and its state slot are given back."""
+        self.cache.release(request_id)
+
+    def is_live(self, request_id: Hashable) -> bool:
+        return self.cache.is_live(request_id)
+
+    # ---- the step -----------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run one batch; returns float32 logits [wanted rows, vocab] on the device, in
+        the order of the entries and of their `want`.  The tensor is a view of a buffer
+        that the next step overwrites."""
+        ctx = self._prepare(entries)
+        return self._run(ctx)
+
+    def _prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        if len(entries) > self.max_entries:
+            raise StepError(f"{len(entries)} entries exceed max_num_seqs {self.max_entries}")
+        seen = set()
+        n_tokens = n_rows = 0
+        for e in entries:
+            if e.request_id in seen:
+                raise StepError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.request_id!r} brings no tokens")
+            for w in e.want:
+                if not (0 <= w < n):
+                    raise StepError(f"request {e.request_id!r}: wanted place {w} is outside its {n} tokens")
+            if min(e.tokens) < 0 or max(e.tokens) >= self.vocab:
+                raise StepError(f"request {e.request_id!r}: token id outside [0, {self.vocab})")
+            n_tokens += n
+            n_rows += len(e.want)
+        if n_tokens > self.max_tokens:
+            raise StepError(f"{n_tokens} tokens exceed max_num_batched_tokens {self.max_tokens}")
+        if n_rows > self.max_rows:
+            raise StepError(f"{n_rows} wanted rows exceed the limit {self.max_rows}")
+
+        cache = self.cache
+        # All-or-nothing: see that every entry fits before any page moves.
+        new_ids = [e.request_id for e in entries if not cache.is_live(e.request_id)]
+        if len(new_ids) > cache.num_free_slots():
+            raise StepError(f"{len(new_ids)} new requests but only {cache.num_free_slots()} request slots free")
+        need = [0] * cache.num_groups
+        for e in entries:
+            live = cache.is_live(e.request_id)
+            cur = cache.length(e.request_id) if live else 0
+            if cur + len(e.tokens) > self.max_seq_len:
+                raise StepError(f"request {e.request_id!r}: {cur}+{len(e.tokens)} tokens exceed max_seq_len "
+                                f"{self.max_seq_len}")
+            for g, k in enumerate(cache.pages_needed(e.request_id if live else None, len(e.tokens))):
+                need[g] += k
+        for g in range(cache.num_groups):
+            if need[g] > cache.num_free_pages(g):
+                raise OutOfPages(f"cache group {g}: the step needs {need[g]} pages, {cache.num_free_pages(g)} free")
+
+        lay = self.layout
+        host_t = self._next_host_buffer()
+        host = host_t.numpy()
+        B = len(entries)
+        entry_tokens = np.zeros(B, dtype=np.int32)
+        entry_start = np.zeros(B, dtype=np.int32)
+        t0 = r0 = 0
+        host[lay.cu_tokens] = 0
+        for b, e in enumerate(entries):
+            if not cache.is_live(e.request_id):
+                cache.admit(e.request_id)
+            n = len(e.tokens)
+            start = cache.extend(e.request_id, n)
+            toks = np.asarray(e.tokens, dtype=np.int32)
+            pos = np.arange(start, start + n, dtype=np.int32)
+            host[lay.token_ids + t0: lay.token_ids + t0 + n] = toks
+            host[lay.positions + t0: lay.positions + t0 + n] = pos
+            host[lay.token_entry + t0: lay.token_entry + t0 + n] = b
+            host[lay.cu_tokens + b + 1] = t0 + n
+            host[lay.kv_lens + b] = start + n
+            host[lay.state_slots + b] = cache.slot(e.request_id)
+            for g in range(cache.num_groups):
+                ps = self.page_size
+                table = np.asarray(cache.table(g, e.request_id), dtype=np.int32)
+                w = cache.table_width(g)
+                row = lay.block_table[g] + b * w
+                host[row: row + len(table)] = table
+                host[lay.slot_map[g] + t0: lay.slot_map[g] + t0 + n] = table[pos // ps] * ps + pos % ps
+            for w_ in e.want:
+                host[lay.logit_rows + r0] = t0 + w_
+                r0 += 1
+            entry_tokens[b], entry_start[b] = n, start
+            t0 += n
+        fresh = cache.take_fresh_slots()
+        if fresh:
+            self.state_storage.zero_slots(fresh)
+        self.meta.copy_(host_t, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._host_events[self._ring_at] = ev
+
+        ctx = self._ctx
+        ctx.n_tokens, ctx.n_entries, ctx.n_logit_rows = n_tokens, B, n_rows
+        ctx.host_entry_tokens, ctx.host_entry_start = entry_tokens, entry_start
+        return ctx
+
+    def _next_host_buffer(self) -> torch.Tensor:
+        self._ring_at = (self._ring_at + 1) % len(self._host_ring)
+        ev = self._host_events[self._ring_at]
+        if ev is not None:
+            ev.synchronize()
+        return self._host_ring[self._ring_at]
+
+    def _forward(self, ctx: StepContext) -> None:
+        stream = ResidualStream(self.resid, ctx.n_tokens)
+        self.model.forward(ctx, stream, self._views)
+        R = ctx.n_logit_rows
+        if R:
+            rows, normed, logits = self._logit_buffers(R)
+            ops.gather_rows(rows, stream.resid, stream.pending, ctx.logit_rows, R)
+            self.model.final_norm.forward_rows(rows, R, normed)
+            self.model.head.forward(normed, R, logits)
+
+    def _run(self, ctx: StepContext) -> torch.Tensor:
+        R = ctx.n_logit_rows
+        if R:
+            self._logit_buffers(R)
+        self._forward(ctx)
+        self.counters["steps"] += 1
+        self.counters["tokens"] += ctx.n_tokens
+        return self._logits[:R] if R else torch.empty((0, self.vocab), dtype=torch.float32, device=self.device)
+
+    def check_status(self) -> None:
+        """Raise if a kernel flagged bad input since the last check (synchronises)."""
+        if int(self.status.item()) != 0:
+            self.status.zero_()
+            raise StepError("a kernel met a token id outside the vocabulary")
+
+    def memory_report(self) -> dict:
+        return {"weights": self.model.weight_bytes(), "cache": self.cache_storage.bytes(),
+                "workspace": self.workspace.bytes(),
+                "pages": [self.cache.group_spec(g).num_pages for g in range(self.cache.num_groups)]}

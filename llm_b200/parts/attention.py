@@ -1,0 +1,83 @@
+"""Grouped-query attention over the paged cache.
+
+One product gives q, k and v (the reference fuses the three weights the same way,
+model/modules/QKVLinear.h:20-33); q and k are rotated by the position part's table
+and k, v are stored in the layer's pages (kernel/Gemm/QKVGemm.h:27-63); every query
+head attends to the keys of kv head h // (NH/NKV) that are at or before its own
+position and inside the window, if there is one
+(kernel/attention/attention_NH_32_NKV_4_HS_64.h:169-172,228-232); then the output
+projection (model/modules/Attention.h:19).  Sizes, window and scale are parameters.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..csrc import ops
+from .base import CacheNeed, ParamInfo, Part, build_part, register_part
+from .linear import linear
+
+
+class PagedAttention(Part):
+    role = "mixer"
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, position=None,
+                 window=None, scale=None, shares_cache: bool = False, prefix: str = "", dtype=None,
+                 device=None):
+        super().__init__(prefix, dtype, device)
+        if num_heads % num_kv_heads:
+            raise ValueError(f"attention: {num_heads} heads do not divide into {num_kv_heads} kv heads")
+        if head_dim % 16 or head_dim > 256:
+            raise ValueError(f"attention: head_dim {head_dim} must be a multiple of 16 up to 256")
+        self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
+        self.window = int(window) if window else None
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.shares_cache = shares_cache          # reads another layer's pages: no k, v of its own
+        self.position = build_part("position", position, dtype, device) if position is not None else None
+        self.q_size = num_heads * head_dim
+        self.kv_size = 0 if shares_cache else num_kv_heads * head_dim
+        self.w_qkv = None
+        self.w_o = None
+
+    def parameters(self):
+        p = {self.name("q_proj.weight"): ParamInfo((self.q_size, self.hidden_size))}
+        if not self.shares_cache:
+            p[self.name("k_proj.weight")] = ParamInfo((self.kv_size, self.hidden_size))
+            p[self.name("v_proj.weight")] = ParamInfo((self.kv_size, self.hidden_size))
+        p[self.name("o_proj.weight")] = ParamInfo((self.hidden_size, self.q_size))
+        return p
+
+    def bind(self, tensors):
+        parts = [tensors[self.name("q_proj.weight")]]
+        if not self.shares_cache:
+            parts += [tensors[self.name("k_proj.weight")], tensors[self.name("v_proj.weight")]]
+        self.w_qkv = torch.cat(parts, dim=0).contiguous() if len(parts) > 1 else parts[0].contiguous()
+        self.w_o = tensors[self.name("o_proj.weight")].contiguous()
+
+    def cache_need(self):
+        if self.shares_cache:
+            return None
+        return CacheNeed("window" if self.window else "full", self.num_kv_heads, self.head_dim, self.window)
+
+    def state_need(self):
+        return None
+
+    def forward(self, x: torch.Tensor, ctx, view) -> torch.Tensor:
+        T = ctx.n_tokens
+        ws = ctx.workspace
+        qkv = linear(x, self.w_qkv, ws.get("qkv", T, self.q_size + 2 * self.kv_size, self.dtype), T)
+        cos = sin = None
+        if self.position is not None:
+            cos, sin = self.position.tables()
+        n_kv_written = 0 if self.shares_cache else self.num_kv_heads
+        k_pages, v_pages = view.k_pages, view.v_pages
+        ops.rope_kv_write(qkv, cos, sin, ctx.positions, view.group.slot_map, k_pages, v_pages, T,
+                          self.num_heads, n_kv_written, self.head_dim)
+        attn = ws.get("attn_out", T, self.q_size, self.dtype)
+        ops.paged_attention(attn, qkv, k_pages, v_pages, view.group, ctx, self.num_heads,
+                            k_pages.shape[1], self.head_dim, self.window or 0, self.scale)
+        return linear(attn, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T)
+
+
+register_part("mixer", "attention", PagedAttention)

@@ -1,0 +1,45 @@
+"""SwiGLU feed-forward: down( silu(gate(x)) * up(x) ).
+
+The reference runs gate and up as two products and the activation as a third kernel
+(model/modules/MLP.h:10-13, kernel/activation/SwiGLU.h:31-33); here gate and up are
+one product over a stacked weight.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .base import ParamInfo, Part, register_part
+from .linear import linear
+
+
+class SwiGLU(Part):
+    role = "ffn"
+
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = "", dtype=None, device=None):
+        super().__init__(prefix, dtype, device)
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.w_gate_up = None
+        self.w_down = None
+
+    def parameters(self):
+        return {
+            self.name("gate_proj.weight"): ParamInfo((self.intermediate_size, self.hidden_size)),
+            self.name("up_proj.weight"): ParamInfo((self.intermediate_size, self.hidden_size)),
+            self.name("down_proj.weight"): ParamInfo((self.hidden_size, self.intermediate_size)),
+        }
+
+    def bind(self, tensors):
+        self.w_gate_up = torch.cat([tensors[self.name("gate_proj.weight")],
+                                    tensors[self.name("up_proj.weight")]], dim=0).contiguous()
+        self.w_down = tensors[self.name("down_proj.weight")].contiguous()
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        T, ws = ctx.n_tokens, ctx.workspace
+        gate_up = linear(x, self.w_gate_up, ws.get("gate_up", T, 2 * self.intermediate_size, self.dtype), T)
+        act = ws.get("ffn_act", T, self.intermediate_size, self.dtype)
+        ops.silu_mul(act, gate_up, T)
+        return linear(act, self.w_down, ws.get("ffn_out", T, self.hidden_size, self.dtype), T)
+
+
+register_part("ffn", "swiglu", SwiGLU)

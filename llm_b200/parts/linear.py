@@ -1,0 +1,24 @@
+"""y = x W^T for a weight stored as in the checkpoint, [out, in].
+
+The reference transposes every projection at load (runtime/LLM.h:146-156) for its
+K x N kernels; the kernels here read [out, in] directly, which is already K-major
+for both operands, so nothing is repacked.  Float32 always runs on the CUDA cores
+with float32 accumulation (no tensor-core mode); bfloat16 runs on the tcgen05 kernel
+where the shape allows it and on the same CUDA-core kernel otherwise.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int) -> torch.Tensor:
+    """out[:rows] = x[:rows] @ weight.T; out may be float32 for bfloat16 inputs."""
+    if rows == 0:
+        return out
+    if x.dtype == torch.bfloat16 and ops.gemm_fast_available(x, weight, out, rows):
+        ops.gemm_fast(x, weight, out, rows)
+    else:
+        ops.gemm_simt(x, weight, out, rows)
+    return out

@@ -1,0 +1,132 @@
+"""Weights by tensor name, from model.safetensors or from a seed.
+
+The reference binds tensors by the names its modules register
+(runtime/LLM.h:75-89,101-190) and looks each up with `infos.at(name)`: a missing
+tensor is an out_of_range, extra tensors are ignored and neither dtype nor shape is
+checked.  Here everything that does not fit is collected and reported in one error:
+missing tensors, unexpected tensors, wrong shapes.  Matrices are kept in the compute
+dtype (bfloat16 or float32), small gain vectors in float32, integer tables in int32.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import warnings
+from typing import Dict, List
+
+import torch
+
+from ..parts.base import ParamInfo
+from .safetensors_io import SafetensorsError, SafetensorsFile, write_safetensors
+
+WEIGHTS_FILE = "model.safetensors"
+CONFIG_FILE = "config.json"
+
+
+class WeightError(ValueError):
+    """The checkpoint does not hold what the model expects."""
+
+    def __init__(self, path: str, missing: List[str], unexpected: List[str], wrong: List[str]):
+        self.missing, self.unexpected, self.wrong = missing, unexpected, wrong
+        lines = [f"{path} does not match the model:"]
+        if missing:
+            lines.append(f"  missing tensors ({len(missing)}): " + ", ".join(missing))
+        if unexpected:
+            lines.append(f"  unexpected tensors ({len(unexpected)}): " + ", ".join(unexpected))
+        if wrong:
+            lines.append(f"  wrong shape or dtype ({len(wrong)}): " + "; ".join(wrong))
+        super().__init__("\n".join(lines))
+
+
+def _target_dtype(info: ParamInfo, compute_dtype: torch.dtype) -> torch.dtype:
+    if info.kind == "matrix":
+        return compute_dtype
+    if info.kind == "gain":
+        return torch.float32
+    if info.kind == "int_table":
+        return torch.int32
+    raise ValueError(f"unknown parameter kind '{info.kind}'")
+
+
+def load_tensors(model_dir: str, expected: Dict[str, ParamInfo], compute_dtype: torch.dtype,
+                 device: torch.device) -> Dict[str, torch.Tensor]:
+    """Read, validate, convert and move every expected tensor."""
+    path = os.path.join(model_dir, WEIGHTS_FILE)
+    if not os.path.isfile(path):
+        raise SafetensorsError(f"{path}: no {WEIGHTS_FILE} in the model folder")
+    f = SafetensorsFile(path)
+    missing = sorted(n for n in expected if n not in f.entries)
+    unexpected = sorted(n for n in f.entries if n not in expected)
+    wrong = []
+    for name, info in expected.items():
+        e = f.entries.get(name)
+        if e is None:
+            continue
+        if tuple(e.shape) != tuple(info.shape):
+            wrong.append(f"{name}: file has {list(e.shape)}, model expects {list(info.shape)}")
+        elif info.kind == "int_table" and e.dtype.is_floating_point:
+            wrong.append(f"{name}: file has {e.dtype}, model expects an integer table")
+        elif info.kind != "int_table" and not e.dtype.is_floating_point:
+            wrong.append(f"{name}: file has {e.dtype}, model expects floating point")
+    if missing or unexpected or wrong:
+        f.close()
+        raise WeightError(path, missing, unexpected, wrong)
+    out = {}
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", UserWarning)     # read-only mapping: tensors are copied, never written
+        for name, info in expected.items():
+            t = f.tensor(name)
+            out[name] = t.to(device=device, dtype=_target_dtype(info, compute_dtype)).contiguous()
+    f.close()
+    return out
+
+
+def _tensor_seed(seed: int, name: str) -> int:
+    h = hashlib.sha256(f"{seed}:{name}".encode()).digest()
+    return int.from_bytes(h[:8], "little") >> 1
+
+
+def random_tensor(name: str, info: ParamInfo, seed: int) -> torch.Tensor:
+    """The seeded value of one tensor in float32: a function of (seed, name, shape) only."""
+    if info.kind == "int_table":
+        return torch.zeros(info.shape, dtype=torch.int32)
+    g = torch.Generator(device="cpu")
+    g.manual_seed(_tensor_seed(seed, name))
+    x = torch.randn(info.shape, generator=g, dtype=torch.float32)
+    if info.init == "normal":
+        return x * 0.02
+    if info.init == "ones_normal":
+        return 1.0 + x * 0.01
+    if info.init == "zeros":
+        return torch.zeros(info.shape, dtype=torch.float32)
+    raise ValueError(f"unknown init rule '{info.init}'")
+
+
+def expected_tensors(config_dict: dict) -> Dict[str, ParamInfo]:
+    """Names and shapes a model of this config.json expects, found by building its parts
+    without a device."""
+    from ..engine.model import collect_parameters
+    return collect_parameters(config_dict)
+
+
+def write_random_model(model_dir: str, config_dict: dict, seed: int, dtype: str = "bfloat16") -> str:
+    """Write config.json and model.safetensors with seeded random weights: matrices and
+    embeddings N(0, 0.02), norm gains 1 + N(0, 0.01).  `dtype` is the stored dtype of the
+    matrices ("bfloat16" or "float32"); gains are stored in float32."""
+    store = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype]
+    expected = expected_tensors(config_dict)
+    os.makedirs(model_dir, exist_ok=True)
+    tensors = {}
+    for name, info in expected.items():
+        t = random_tensor(name, info, seed)
+        if info.kind == "matrix":
+            t = t.to(store)
+        tensors[name] = t
+    cfg = dict(config_dict)
+    cfg.setdefault("torch_dtype", dtype)
+    with open(os.path.join(model_dir, CONFIG_FILE), "w", encoding="utf-8") as f:
+        json.dump(cfg, f, indent=2)
+    write_safetensors(os.path.join(model_dir, WEIGHTS_FILE), tensors,
+                      metadata={"format": "pt", "seed": str(seed)})
+    return model_dir

@@ -1,0 +1,92 @@
+"""GPU tests of the whole engine against the plain implementation: every way of
+cutting the work, in 32-bit and in bfloat16."""
+import pytest
+import torch
+
+import plain_llama
+import replay
+from tiny import CONFIGS, TOL, load_plain_weights, make_model_dir, max_err, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 40, 64, 97, 130], "C": [3, 50, 81, 120]}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    cache = {}
+
+    def get(name, dtype):
+        key = (name, dtype)
+        if key not in cache:
+            d = make_model_dir(root, name, dtype)
+            w = load_plain_weights(d)
+            cfg, page = CONFIGS[name]
+            reqs = {f"r{i}": random_tokens(n, cfg["vocab_size"], 100 + i) for i, n in enumerate(LENGTHS[name])}
+            ref = {rid: plain_llama.forward(cfg, w, toks) for rid, toks in reqs.items()}
+            cache[key] = (d, cfg, page, reqs, ref)
+        return cache[key]
+    return get
+
+
+def make_engine(model_dir, dtype, page, num_blocks, max_tokens=256, max_seqs=4):
+    from llm_b200.config import EngineOptions
+    from llm_b200.engine.engine import Engine
+    return Engine(model_dir, EngineOptions(dtype=dtype, kv_block_size=page, max_num_seqs=max_seqs,
+                                           max_num_batched_tokens=max_tokens, num_kv_blocks=num_blocks,
+                                           use_cuda_graphs=False))
+
+
+def compare(got, ref, dtype, what):
+    for rid, r in ref.items():
+        assert got[rid].shape == r.shape, f"{what}: {rid} shape {got[rid].shape} vs {r.shape}"
+        # the first wrong row, to point at the place (a page's edge, a portion's start, ...)
+        err_rows = (got[rid].double() - r).abs().max(dim=1).values / r.abs().max()
+        bad = torch.nonzero(err_rows > TOL[dtype])
+        assert bad.numel() == 0, (f"{what}: request {rid} first differs at position {int(bad[0])} "
+                                  f"(err {float(err_rows[int(bad[0])]):.3e}, limit {TOL[dtype]:.1e})")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_every_cut_matches_plain(models, name, dtype):
+    d, cfg, page, reqs, ref = models(name, dtype)
+    longest = max(len(t) for t in reqs.values())
+    pages_one = (longest + page - 1) // page
+    # whole, tail decode and portions: one request at a time, a pool barely larger than the longest
+    eng = make_engine(d, dtype, page, pages_one + 1)
+    compare(replay.run_steps(eng, replay.steps_whole(reqs)), ref, dtype, "whole")
+    compare(replay.run_steps(eng, replay.steps_tail_decode(reqs)), ref, dtype, "tail decode")
+    compare(replay.run_steps(eng, replay.steps_portions(reqs)), ref, dtype, "portions")
+    eng.cache.check()
+    assert all(eng.cache.num_free_pages(g) == eng.cache.group_spec(g).num_pages for g in range(eng.cache.num_groups))
+    # mixed: up to four live, so few pages that freed ones are used again
+    lens = sorted((len(t) for t in reqs.values()), reverse=True)
+    pool = sum((n + page - 1) // page for n in lens[:4]) + 1
+    eng = make_engine(d, dtype, page, pool)
+    compare(replay.run_steps(eng, replay.steps_mixed(reqs)), ref, dtype, "mixed")
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_matches_plain(models, dtype):
+    from llm_b200 import LLM
+    d, cfg, page, reqs, _ = models("A", dtype)
+    w = load_plain_weights(d)
+    prompts = [random_tokens(n, cfg["vocab_size"], 7 + n) for n in (5, 17, 33)]
+    llm = LLM(d, dtype=dtype, max_num_seqs=4, max_num_batched_tokens=24, kv_block_size=page,
+              num_kv_blocks=12, eos_token_id=-1, use_cuda_graphs=False)
+    got = llm.generate(prompts, max_new_tokens=16)
+    for p, g in zip(prompts, got):
+        assert len(g) == 16
+        if dtype == "float32":
+            assert g == plain_llama.greedy_generate(cfg, w, p, 16)
+        else:
+            # bfloat16 may flip near-ties: every chosen token must be within rounding of the best
+            ids = list(p)
+            for tok in g:
+                row = plain_llama.forward(cfg, w, ids)[-1]
+                assert float(row.max() - row[tok]) <= 2 * TOL[dtype] * float(row.abs().max())
+                ids.append(tok)
+    llm.engine.cache.check()

@@ -1,0 +1,55 @@
+"""Tiny configurations and helpers shared by the tests.  A and B are the two tiny
+configurations of the benchmark definition; C adds a sliding window, tied embeddings
+and plain multi-head attention.  They differ in every size and option."""
+from __future__ import annotations
+
+import os
+
+import numpy as np
+import torch
+
+CONFIG_A = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=172,
+                num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                vocab_size=256, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=128,
+                tie_word_embeddings=False, hidden_act="silu")
+CONFIG_B = dict(architectures=["LlamaForCausalLM"], hidden_size=96, intermediate_size=256,
+                num_hidden_layers=3, num_attention_heads=3, num_key_value_heads=1, head_dim=32,
+                vocab_size=384, rms_norm_eps=1e-6, rope_theta=500000.0, max_position_embeddings=256,
+                tie_word_embeddings=False, hidden_act="silu")
+CONFIG_C = dict(architectures=["LlamaForCausalLM"], hidden_size=80, intermediate_size=100,
+                num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=5, head_dim=48,
+                vocab_size=301, rms_norm_eps=1e-4, rope_theta=1000.0, max_position_embeddings=192,
+                tie_word_embeddings=True, sliding_window=37, hidden_act="silu")
+
+CONFIGS = {"A": (CONFIG_A, 16), "B": (CONFIG_B, 8), "C": (CONFIG_C, 32)}   # name -> (config, page size)
+
+
+def make_model_dir(tmp_root, name: str, dtype: str, seed: int = 1234, scale_far_key: bool = False) -> str:
+    from llm_b200.weights.loader import write_random_model
+    cfg, _ = CONFIGS[name]
+    d = os.path.join(str(tmp_root), f"tiny_{name}_{dtype}")
+    if not os.path.isdir(d):
+        write_random_model(d, cfg, seed, dtype)
+    return d
+
+
+def load_plain_weights(model_dir: str):
+    from llm_b200.weights.safetensors_io import SafetensorsFile
+    f = SafetensorsFile(os.path.join(model_dir, "model.safetensors"))
+    return {n: f.tensor(n).clone() for n in f.names()}
+
+
+def random_tokens(n: int, vocab: int, seed: int):
+    rng = np.random.default_rng(seed)
+    return [int(x) for x in rng.integers(0, vocab, size=n)]
+
+
+def max_err(a: torch.Tensor, b: torch.Tensor) -> float:
+    """Largest absolute difference relative to the largest reference magnitude."""
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+
+
+# Normalised error bounds: the 32-bit path differs from the float64 plain implementation by
+# rounding only; bfloat16 carries 8 bits of mantissa through every product.
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
