@@ -1,0 +1,236 @@
+"""CPU tests: the cache manager's invariants under random orders of requests, and the
+scheduler's decisions (portions, budget, reserve, what happens when pages run out).
+Scenarios follow the reference's host test runtime/test/test_scheduler_chunk.cpp."""
+import random
+
+import pytest
+
+from llm_b200.cache import CacheError, CacheManager, GroupSpec, OutOfPages
+from llm_b200.engine.scheduler import Scheduler, SchedulerConfig
+
+
+def full_pool(pages=8, page=16, max_req=4, max_len=256):
+    return CacheManager([GroupSpec("full", page, pages)], max_req, max_len)
+
+
+def test_extend_release_and_tables():
+    c = full_pool()
+    c.admit("a")
+    assert c.extend("a", 17) == 0 and c.length("a") == 17
+    assert len(c.table(0, "a")) == 2 and c.num_free_pages(0) == 6
+    assert c.extend("a", 15) == 17 and len(c.table(0, "a")) == 2      # 32 tokens: still two pages
+    assert c.extend("a", 1) == 32 and len(c.table(0, "a")) == 3
+    assert c.physical_slot(0, "a", 33) == c.table(0, "a")[2] * 16 + 1
+    c.check()
+    c.release("a")
+    assert c.num_free_pages(0) == 8 and c.num_free_slots() == 4
+    with pytest.raises(CacheError, match="not live"):
+        c.release("a")
+    with pytest.raises(CacheError):
+        c.extend("a", 1)
+    c.check()
+
+
+def test_out_of_pages_changes_nothing():
+    c = full_pool(pages=2)
+    c.admit("a")
+    c.extend("a", 20)
+    c.admit("b")
+    with pytest.raises(OutOfPages):
+        c.extend("b", 16)
+    assert c.length("b") == 0 and c.num_free_pages(0) == 0
+    assert not c.can_extend("b", 1) and c.can_extend("a", 12) and not c.can_extend("a", 13)
+    c.check()
+
+
+def test_window_group_gives_pages_back_and_reuses_them():
+    c = CacheManager([GroupSpec("full", 8, 40), GroupSpec("window", 8, 12, window=20)], 2, 300)
+    c.admit("a")
+    pos = 0
+    for n in (30, 1, 1, 7, 25, 2, 60, 1):
+        assert c.pages_needed("a", n)[1] <= c.num_free_pages(1)
+        assert c.extend("a", n) == pos
+        pos += n
+        c.check()
+        t = c.table(1, "a")
+        lowest_key = max(0, pos - n - 20 + 1)          # first key the first new token could see
+        for i, p in enumerate(t):
+            if (i + 1) * 8 <= lowest_key:
+                assert p == -1                         # out of every later window: given back
+            else:
+                assert p >= 0
+        assert all(p >= 0 for p in c.table(0, "a"))     # the full group keeps everything
+    # a window group never holds more than ceil((window + step) / page) + 1 pages per request
+    assert sum(p >= 0 for p in c.table(1, "a")) <= 4
+    c.release("a")
+    assert c.num_free_pages(1) == 12 and c.num_free_pages(0) == 40
+    c.check()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_keep_every_page_accounted(seed):
+    rng = random.Random(seed)
+    groups = [GroupSpec("full", 8, 30)] + ([GroupSpec("window", 8, 20, window=rng.choice([5, 16, 33]))] if seed % 2 else [])
+    c = CacheManager(groups, 5, 200)
+    live, next_id = {}, 0
+    for _ in range(600):
+        op = rng.random()
+        if op < 0.25 and c.num_free_slots():
+            c.admit(next_id); live[next_id] = 0; next_id += 1
+        elif op < 0.85 and live:
+            rid = rng.choice(list(live))
+            n = rng.choice([1, 1, 1, 2, 7, 16, 40])
+            if c.can_extend(rid, n):
+                assert c.extend(rid, n) == live[rid]
+                live[rid] += n
+            else:
+                before = [c.num_free_pages(g) for g in range(c.num_groups)]
+                with pytest.raises(CacheError):
+                    c.extend(rid, n)
+                assert before == [c.num_free_pages(g) for g in range(c.num_groups)]
+        elif live:
+            rid = rng.choice(list(live))
+            c.release(rid); del live[rid]
+        c.check()
+    for rid in list(live):
+        c.release(rid)
+    c.check()
+    assert all(c.num_free_pages(g) == c.group_spec(g).num_pages for g in range(c.num_groups))
+    assert c.num_free_slots() == 5
+
+
+# ---- scheduler ---------------------------------------------------------------
+
+def run_step(sched, cache, batch, token=7):
+    """What the engine does with a batch, as far as the cache is concerned."""
+    for e in batch.entries:
+        if not cache.is_live(e.request_id):
+            cache.admit(e.request_id)
+        assert cache.extend(e.request_id, len(e.tokens)) == e.start
+    cache.check()
+    return sched.update(batch, {e.request_id: token for e in batch.entries if e.samples})
+
+
+def test_prompt_is_cut_to_the_budget():
+    c = full_pool(pages=16)
+    s = Scheduler(c, SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=32))
+    rid = s.add_request(list(range(80)), 2)
+    sizes = []
+    for _ in range(3):
+        b = s.schedule()
+        sizes.append([len(e.tokens) for e in b.entries])
+        assert [e.samples for e in b.entries] == [len(sizes) == 3]
+        run_step(s, c, b)
+    assert sizes == [[32], [32], [16]]
+    b = s.schedule()                                     # now it decodes
+    assert [(e.request_id, len(e.tokens), e.start, e.samples) for e in b.entries] == [(rid, 1, 80, True)]
+    done = run_step(s, c, b)
+    assert [r.id for r in done] == [rid] and done[0].generated == [7, 7]
+    assert c.num_free_pages(0) == 16 and c.num_free_slots() == 4 and s.num_requests() == 0
+
+
+def test_short_prompts_share_a_batch_and_decode_rides_along():
+    c = full_pool(pages=16)
+    s = Scheduler(c, SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=32))
+    a = s.add_request([1] * 5, 4)
+    b_ = s.add_request([2] * 9, 4)
+    big = s.add_request([3] * 40, 4)
+    b = s.schedule()
+    assert [(e.request_id, len(e.tokens)) for e in b.entries] == [(a, 5), (b_, 9), (big, 18)]
+    assert [e.samples for e in b.entries] == [True, True, False]
+    run_step(s, c, b)
+    b = s.schedule()                                     # two decode tokens first, then the rest of the prompt
+    assert [(e.request_id, len(e.tokens)) for e in b.entries] == [(a, 1), (b_, 1), (big, 22)]
+    assert b.num_tokens <= 32
+    run_step(s, c, b)
+    b = s.schedule()
+    assert sorted(len(e.tokens) for e in b.entries) == [1, 1, 1]
+
+
+def test_rejects_what_can_never_run():
+    c = full_pool(pages=4, max_len=100)
+    s = Scheduler(c, SchedulerConfig(2, 32))
+    assert s.add_request([], 4) == -1
+    assert s.add_request([1] * 90, 20) == -1              # longer than max_seq_len
+    assert s.add_request([1] * 60, 10) == -1              # 5 pages, the pool has 4
+    assert s.add_request([1] * 60, 4) >= 0
+
+
+def test_prefill_waits_for_pages_and_reserve():
+    c = full_pool(pages=3)
+    s = Scheduler(c, SchedulerConfig(4, 64))
+    a = s.add_request([1] * 16, 8)                       # ends exactly on a page edge: needs its next page kept
+    b_ = s.add_request([2] * 20, 4)
+    b = s.schedule()
+    assert [e.request_id for e in b.entries] == [a]      # b would leave no page for a's first decoded token
+    run_step(s, c, b)
+    b = s.schedule()
+    assert [(e.request_id, len(e.tokens)) for e in b.entries] == [(a, 1)]
+    run_step(s, c, b)
+    for _ in range(6):
+        run_step(s, c, s.schedule())
+    assert s.num_requests() == 1 and c.num_free_pages(0) == 3
+    b = s.schedule()
+    assert [(e.request_id, len(e.tokens)) for e in b.entries] == [(b_, 20)]
+
+
+def test_decode_preempts_the_latest_and_recomputes():
+    c = full_pool(pages=4, page=16)
+    s = Scheduler(c, SchedulerConfig(4, 64))
+    a = s.add_request([1] * 30, 30)
+    b_ = s.add_request([2] * 30, 30)
+    run_step(s, c, s.schedule())                         # both prompts: 2 pages each, pool full
+    assert c.num_free_pages(0) == 0
+    for _ in range(2):                                    # positions 30 and 31 still fit in the held pages
+        b = s.schedule()
+        assert len(b.entries) == 2
+        run_step(s, c, b)
+    b = s.schedule()                                     # both need a third page and none is free
+    assert s.num_preemptions == 1
+    assert [(e.request_id, len(e.tokens)) for e in b.entries] == [(a, 1)]
+    run_step(s, c, b)
+    r = s.requests[b_]
+    assert r.cached_len == 0 and len(r.token_ids) == 33 and not c.is_live(b_)
+    b = s.schedule()                                     # a decodes; b's recompute needs 3 pages, 1 is free
+    assert [e.request_id for e in b.entries] == [a]
+    run_step(s, c, b)
+    steps = 0
+    finished = []
+    while s.num_requests():
+        b = s.schedule()
+        assert not b.empty()
+        finished += run_step(s, c, b)
+        steps += 1
+        assert steps < 200
+    assert sorted(r.id for r in finished) == [a, b_]
+    assert all(len(r.generated) == 30 for r in finished)
+    assert c.num_free_pages(0) == 4 and c.num_free_slots() == 4
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_random_load_finishes_and_frees_everything(seed):
+    rng = random.Random(seed)
+    page = rng.choice([8, 16])
+    groups = [GroupSpec("full", page, 12)] + ([GroupSpec("window", page, 10, window=24)] if seed % 2 else [])
+    c = CacheManager(groups, 4, 160)
+    s = Scheduler(c, SchedulerConfig(4, 24, eos_token_id=3))
+    want = {}
+    for _ in range(12):
+        n, m = rng.randint(1, 70), rng.randint(1, 30)
+        rid = s.add_request([rng.randint(4, 90) for _ in range(n)], m)
+        if rid >= 0:
+            want[rid] = m
+    done = {}
+    for _ in range(3000):
+        if not s.num_requests():
+            break
+        b = s.schedule()
+        assert not b.empty() and b.num_tokens <= 24 and len(b.entries) <= 4
+        for r in run_step(s, c, b, token=rng.choice([3, 5, 5, 5, 5, 5, 5, 5])):
+            done[r.id] = r
+    assert set(done) == set(want)
+    for rid, r in done.items():
+        assert 1 <= len(r.generated) <= want[rid]
+        assert r.generated[-1] == 3 or len(r.generated) == want[rid]
+    assert all(c.num_free_pages(g) == c.group_spec(g).num_pages for g in range(c.num_groups))
+    assert c.num_free_slots() == 4
