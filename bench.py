@@ -1,0 +1,255 @@
+"""Serving benchmark of the engine on one B200: decode tokens per second of a
+TinyLlama-1.1B-shaped model with seeded random weights (bfloat16), plus prefill
+throughput, the decode step's share of the HBM roofline and decode at batch 1 and 64.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+A "step" is one decode step of the whole batch.  One JSON line is printed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Layer sizes of the benchmark model (TinyLlama 1.1B).
+MODEL = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermediate_size=5632,
+             num_hidden_layers=22, num_attention_heads=32, num_key_value_heads=4, head_dim=64,
+             vocab_size=32000, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=2048,
+             tie_word_embeddings=False)
+FULL_LAYERS = 22
+PROMPT_LEN = 512          # decode starts from 512-token prompts
+NEW_TOKENS = 256          # and the benchmark definition generates 256 tokens
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.samples, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for p in self.samples:
+            try:
+                sm.append(int(float(p[0]))); mx.append(int(float(p[1])))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def matmul_params(cfg, layers):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    QN = cfg["num_attention_heads"] * cfg["head_dim"]
+    KN = cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = H * (QN + 2 * KN) + QN * H + 3 * H * I
+    return per_layer * layers, V * H
+
+
+def decode_bytes(cfg, layers, batch, ctx_tokens):
+    """Bytes a decode step has to read: every weight it uses once, and the cache of the live requests."""
+    body, head = matmul_params(cfg, layers)
+    norms = (2 * layers + 1) * cfg["hidden_size"] * 4
+    weights = (body + head) * 2 + norms + batch * cfg["hidden_size"] * 2      # embedding: one row per request
+    kv = 2 * layers * cfg["num_key_value_heads"] * cfg["head_dim"] * 2 * ctx_tokens
+    return weights + kv
+
+
+def prefill_flops(cfg, layers, tokens, head_rows=1):
+    body, head = matmul_params(cfg, layers)
+    QN = cfg["num_attention_heads"] * cfg["head_dim"]
+    attn = layers * 2 * 2 * QN * tokens * (tokens + 1) / 2        # QK^T and PV over the causal half
+    return 2.0 * body * tokens + 2.0 * head * head_rows + attn
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=NEW_TOKENS)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--no-points", action="store_true", help="skip prefill and the batch 1 / 64 points")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "zhan-wei-919/llm is a header-only C++/CUDA tree without setup.py or "
+                                         "pyproject.toml: pip cannot install it into baseline/_ref"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import numpy as np
+    import torch
+
+    from llm_b200.csrc import ops
+    from llm_b200.engine.engine import StepEntry
+    from llm_b200.engine.llm import LLM
+
+    peaks = load_peaks()
+    cfg = dict(MODEL, num_hidden_layers=args.layers)
+    max_batch = max(64, args.batch) if not args.no_points else args.batch
+    t_load = time.time()
+    llm = LLM(None, dtype="bfloat16", max_num_seqs=max_batch, max_num_batched_tokens=PREFILL_TOKENS,
+              max_seq_len=MODEL["max_position_embeddings"], eos_token_id=-1, kv_block_size=16,
+              random_config=cfg, random_seed=20240531)
+    eng = llm.engine
+    load_s = time.time() - t_load
+    rng = np.random.default_rng(1)
+
+    def prompt(n):
+        return [int(x) for x in rng.integers(0, cfg["vocab_size"], size=n)]
+
+    def prefill_requests(batch):
+        """Put `batch` requests of PROMPT_LEN tokens into the cache, a few per step."""
+        ids = [f"b{batch}_{i}" for i in range(batch)]
+        per_step = PREFILL_TOKENS // PROMPT_LEN
+        for i in range(0, batch, per_step):
+            eng.step([StepEntry(r, prompt(PROMPT_LEN), []) for r in ids[i:i + per_step]])
+        return ids
+
+    def timed_decode(batch, steps, warm):
+        """Device time of `steps` decode steps of `batch` requests (tokens are given, nothing is
+        read back inside the region).  Returns (ms per step, launches per step, context at the end)."""
+        ids = prefill_requests(batch)
+        toks = rng.integers(0, cfg["vocab_size"], size=(warm + steps, batch))
+        entries = lambda k: [StepEntry(r, [int(toks[k, j])], [0]) for j, r in enumerate(ids)]
+        for k in range(warm):
+            eng.step(entries(k))
+        torch.cuda.synchronize()
+        l0 = ops.launch_count()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for k in range(warm, warm + steps):
+            eng.step(entries(k))
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / steps
+        launches = (ops.launch_count() - l0) / steps
+        ctx_end = PROMPT_LEN + warm + steps
+        for r in ids:
+            eng.release(r)
+        return ms, launches, ctx_end
+
+    out = {"metric": "decode tok/s at batch 8 (TinyLlama 1.1B shape, bf16, random weights)", "unit": "tok/s",
+           "n_gpus": 1, "steps": args.steps, "warmup": warmup, "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "bf16", "data": "synthetic: seeded random weights and token ids",
+           "impl": "ours"}
+
+    # ---- headline: decode at the default batch, device-timed ----
+    sampler = ClockSampler()
+    sampler.start()
+    ms, launches, ctx_end = timed_decode(args.batch, args.steps, warmup)
+    clocks = sampler.stop()
+    value = args.batch / (ms / 1e3)
+    mean_ctx = PROMPT_LEN + warmup + (args.steps + 1) / 2.0
+    step_bytes = decode_bytes(cfg, args.layers, args.batch, args.batch * mean_ctx)
+    achieved = step_bytes / (ms / 1e3) / 1e9
+    out.update({"value": round(value, 1), "ms_per_step": round(ms, 4), "gpu_launches": int(round(launches * args.steps)),
+                "clocks": clocks,
+                "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
+                             "bytes_per_step": int(step_bytes)}})
+
+    # ---- end to end: the same decode through LLM.generate, host tokens in and out ----
+    prompts = [prompt(PROMPT_LEN) for _ in range(args.batch)]
+    llm.generate(prompts[:1], max_new_tokens=4)                      # warm the path
+    gen = llm.generate(prompts, max_new_tokens=args.steps + 1)
+    st = llm.last_stats
+    e2e_value = st["decode_tokens"] / st["decode_seconds"] if st["decode_seconds"] > 0 else None
+    out["e2e"] = {"value": round(e2e_value, 1) if e2e_value else None, "unit": "tok/s",
+                  "h2d_bytes_per_step": int(st["h2d_bytes_per_step"]), "d2h_bytes_per_step": int(st["d2h_bytes_per_step"]),
+                  "decode_steps": st["decode_steps"], "generated": sum(len(g) for g in gen)}
+
+    # ---- prefill of 2,048 tokens ----
+    if not args.no_points:
+        reps = []
+        for k in range(5):
+            rid = f"p{k}"
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            eng.step([StepEntry(rid, prompt(PREFILL_TOKENS), [PREFILL_TOKENS - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            reps.append(a.elapsed_time(b))
+            eng.release(rid)
+        pms = sorted(reps[2:])[len(reps[2:]) // 2]
+        fl = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
+        out["prefill"] = {"value": round(PREFILL_TOKENS / (pms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
+                          "frac": round(fl / (pms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4),
+                          "peak_tflops": peaks["bf16_tflops"], "peak_source": peaks["source"]}
+        points = {}
+        for b in (1, 64):
+            pm, _, _ = timed_decode(b, min(args.steps, 128), warmup)
+            points[f"decode_b{b}"] = round(b / (pm / 1e3), 1)
+        out["points"] = points
+
+    out["config"] = {"model": "TinyLlama-1.1B shape", "layers": args.layers, "layers_full": FULL_LAYERS,
+                     "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                     "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                     "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                     "global_batch": args.batch, "prompt_len": PROMPT_LEN, "new_tokens": args.steps,
+                     "seq_len": MODEL["max_position_embeddings"], "kv_block": 16, "parallelism": "none (1 GPU)",
+                     "l2": "inputs larger than L2 (2.2 GB of weights per step)", "cuda_graphs": eng.options.use_cuda_graphs,
+                     "load_s": round(load_s, 1)}
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -39,7 +39,22 @@ def _stream():
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Kernel launches issued through this module so far (graph replays included)."""
+    return _LAUNCHES
+
+
+def count_launches(n: int) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
 def _check(code: int) -> None:
+    global _LAUNCHES
+    _LAUNCHES += 1
     if code != 0:
         msg = load().llmk_last_error().decode("utf-8", "replace")
         raise KernelError(f"kernel call failed ({code}): {msg}")
@@ -111,7 +126,7 @@ def rope_kv_write(qkv: torch.Tensor, cos, sin, positions: torch.Tensor, slot_map
     _rows_contig(qkv, "qkv")
     assert k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == qkv.dtype
     assert positions.dtype == torch.int32 and slot_map.dtype == torch.int32
-    assert k_pages.shape[1] == n_kv and k_pages.shape[3] == head_dim
+    assert k_pages.shape[3] == head_dim and (n_kv == 0 or k_pages.shape[1] == n_kv)
     assert qkv.shape[1] >= (n_heads + 2 * n_kv) * head_dim
     if cos is not None:
         assert cos.dtype == torch.float32 and sin.dtype == torch.float32

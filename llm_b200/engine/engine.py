@@ -23,7 +23,7 @@ from ..config.model_config import load_config, parse_config
 from ..csrc import ops
 from ..csrc.build import load as load_kernels
 from ..parts.base import ResidualStream
-from ..weights.loader import load_tensors
+from ..weights.loader import load_tensors, random_tensors_on_device
 from .context import GroupView, LayerView, StepContext, Workspace
 from .model import Model
 
@@ -66,7 +66,11 @@ class _MetaLayout:
 
 
 class Engine:
-    def __init__(self, model_dir: str, options: Optional[EngineOptions] = None):
+    def __init__(self, model_dir: Optional[str], options: Optional[EngineOptions] = None, *,
+                 random_config: Optional[dict] = None, random_seed: int = 0):
+        """model_dir: a folder with config.json and model.safetensors.  Without a folder,
+        random_config (the contents of a config.json) and random_seed give the same seeded
+        random weights that write_random_model would have written, built in memory."""
         self.options = options = options or EngineOptions()
         options.validate()
         if not torch.cuda.is_available():
@@ -76,10 +80,20 @@ class Engine:
         torch.cuda.set_device(self.device)
         self.dtype = _TORCH_DTYPE[options.dtype]
 
-        self.arch, self.config = load_config(model_dir)
+        if model_dir is not None:
+            self.arch, self.config = load_config(model_dir)
+        elif random_config is not None:
+            self.arch, self.config = parse_config(random_config)
+        else:
+            raise ValueError("Engine needs a model folder or a random_config")
         self.spec = self.arch.build_spec(self.config)
         self.model = Model(self.spec, self.dtype, self.device)
-        self.model.bind(load_tensors(model_dir, self.model.parameters(), self.dtype, self.device))
+        if model_dir is not None:
+            tensors = load_tensors(model_dir, self.model.parameters(), self.dtype, self.device)
+        else:
+            tensors = random_tensors_on_device(self.model.parameters(), random_seed, self.dtype, self.device)
+        self.model.bind(tensors)
+        del tensors
 
         self.max_seq_len = options.max_seq_len or self.spec.max_position
         if self.max_seq_len > self.spec.max_position:
@@ -312,7 +326,30 @@ class Engine:
         R = ctx.n_logit_rows
         if R:
             self._logit_buffers(R)
-        self._forward(ctx)
+        # A step of single tokens has launch parameters that depend on the batch size alone
+        # (everything else is read from the metadata buffer), so it is captured once per
+        # (entries, rows) and replayed: the reference captures per GraphShape{batch, tokens}
+        # the same way (runtime/LLM.h:63-72,192-201).
+        graphable = (self.options.use_cuda_graphs and ctx.decode_only and R in (0, ctx.n_entries))
+        if graphable:
+            key = (ctx.n_entries, R)
+            entry = self._graphs.get(key)
+            if entry is not None:
+                entry[0].replay()
+                ops.count_launches(entry[1])
+                self.counters["graph_replays"] += 1
+            else:
+                self._forward(ctx)                       # this step's result; also sizes the scratch buffers
+                torch.cuda.synchronize(self.device)
+                before = ops.launch_count()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self._forward(ctx)                   # recorded only; same inputs, same result when replayed
+                self._graphs[key] = (graph, ops.launch_count() - before)
+                ops.count_launches(-(ops.launch_count() - before))
+                self.counters["graph_captures"] += 1
+        else:
+            self._forward(ctx)
         self.counters["steps"] += 1
         self.counters["tokens"] += ctx.n_tokens
         return self._logits[:R] if R else torch.empty((0, self.vocab), dtype=torch.float32, device=self.device)

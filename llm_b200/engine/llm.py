@@ -9,6 +9,7 @@ max_new_tokens (model/llm/tiny_llama.cpp:19-20).
 """
 from __future__ import annotations
 
+import time
 from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
@@ -24,12 +25,15 @@ class LLM:
                  max_num_batched_tokens: int = 512, max_seq_len: Optional[int] = None,
                  eos_token_id: Optional[int] = None, kv_block_size: int = 16,
                  num_kv_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.9,
-                 use_cuda_graphs: bool = True, device: str = "cuda:0"):
+                 use_cuda_graphs: bool = True, device: str = "cuda:0", random_config: Optional[dict] = None,
+                 random_seed: int = 0):
+        """model: a folder with config.json and model.safetensors, or None together with
+        random_config (a config.json's contents) for seeded random weights."""
         options = EngineOptions(dtype=dtype, kv_block_size=kv_block_size, max_num_seqs=max_num_seqs,
                                 max_num_batched_tokens=max_num_batched_tokens, max_seq_len=max_seq_len,
                                 num_kv_blocks=num_kv_blocks, gpu_memory_utilization=gpu_memory_utilization,
                                 max_logit_rows=max_num_seqs, use_cuda_graphs=use_cuda_graphs, device=device)
-        self.engine = Engine(model, options)
+        self.engine = Engine(model, options, random_config=random_config, random_seed=random_seed)
         if eos_token_id is None:
             eos_token_id = self.engine.spec.eos_token_id
         self.eos_token_id = eos_token_id
@@ -69,13 +73,27 @@ class LLM:
         return [results[rid] for rid in ids]
 
     def _run_to_idle(self, scheduler: Scheduler, on_finished: Callable[[Request], None]) -> None:
+        """Steps until no request is left.  Host-side times of the steps that only decode
+        (schedule, copy in, run, sample, copy out, update) are kept in last_stats, as the
+        reference's driver keeps sched/wait/update times per step (runtime/Driver.h:16,74-83)."""
+        stats = {"steps": 0, "decode_steps": 0, "decode_tokens": 0, "decode_seconds": 0.0,
+                 "h2d_bytes_per_step": self.engine.layout.total * 4, "d2h_bytes_per_step": 0}
         while scheduler.num_requests():
+            t0 = time.perf_counter()
             batch = scheduler.schedule()
             if batch.empty():
                 raise RuntimeError("the scheduler has requests but nothing can run: the cache pool is too "
                                    "small for the request at the head of the queue")
-            for r in scheduler.update(batch, self.inference(scheduler, batch)):
+            tokens = self.inference(scheduler, batch)       # ends with the device-to-host copy of the tokens
+            for r in scheduler.update(batch, tokens):
                 on_finished(r)
+            stats["steps"] += 1
+            if all(len(e.tokens) == 1 for e in batch.entries):
+                stats["decode_steps"] += 1
+                stats["decode_tokens"] += len(batch.entries)
+                stats["decode_seconds"] += time.perf_counter() - t0
+                stats["d2h_bytes_per_step"] = max(stats["d2h_bytes_per_step"], 4 * len(tokens))
+        self.last_stats = stats
         self.engine.check_status()
 
     def server(self, receive: Callable[[bool], Optional[List[int]]], emit: Callable[[int, List[int]], None],

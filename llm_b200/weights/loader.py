@@ -103,6 +103,20 @@ def random_tensor(name: str, info: ParamInfo, seed: int) -> torch.Tensor:
     raise ValueError(f"unknown init rule '{info.init}'")
 
 
+def random_tensors_on_device(expected: Dict[str, ParamInfo], seed: int, compute_dtype: torch.dtype,
+                             device: torch.device, stored_dtype: str = "bfloat16") -> Dict[str, torch.Tensor]:
+    """What load_tensors would return for the folder that write_random_model(seed,
+    stored_dtype) writes, without the folder."""
+    store = {"bfloat16": torch.bfloat16, "float32": torch.float32}[stored_dtype]
+    out = {}
+    for name, info in expected.items():
+        t = random_tensor(name, info, seed)
+        if info.kind == "matrix":
+            t = t.to(store)
+        out[name] = t.to(device=device, dtype=_target_dtype(info, compute_dtype)).contiguous()
+    return out
+
+
 def expected_tensors(config_dict: dict) -> Dict[str, ParamInfo]:
     """Names and shapes a model of this config.json expects, found by building its parts
     without a device."""
