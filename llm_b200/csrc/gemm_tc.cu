@@ -1,0 +1,395 @@
+// C[M,N] = A[M,K] * W[N,K]^T in bfloat16 on the tcgen05 tensor cores, float32
+// accumulation in tensor memory.
+//
+// Both operands are K-major, as activations and checkpoint weights ([out, in]) already
+// are, so nothing is transposed.  One CTA computes one tile: a producer thread moves
+// [rows x 64] boxes of both operands into a ring of 128-byte-swizzled stages with TMA,
+// one thread issues tcgen05.mma (M = 128, N = BNQ, K = 16, four per stage) and frees each
+// stage with tcgen05.commit, four warps read the accumulator back with tcgen05.ld and
+// store it.  The operand that supplies the 128 rows of the MMA's M side is called P, the
+// other Q:
+//   normal:  P = activations, Q = weights  (many tokens)
+//   swapped: P = weights, Q = activations  (few tokens: decode and short prompt portions;
+//            the token count becomes the MMA's N, 16 to 128, so no tensor-core row is
+//            spent on padding tokens up to 128)
+// Few-token products read every weight once and are bound by HBM; to keep all SMs
+// streaming, K is split over blockIdx.z and each split writes a float32 partial result
+// [split][M][N] that the consumer (or llmk_reduce_partials) sums in a fixed order.
+//
+// The reference's products are mma.sync kernels with cp.async double buffering
+// (kernel/Gemm/Gemm.h:143-247) and a special-case GEMV (kernel/Gemm/Gemm.h:249-280).
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace tc {
+
+// ---- tensor maps (host) -------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+int encode_tensor_map_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                           uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return llmk_fail(-2, "cuTensorMapEncodeTiled is not available from the driver");
+  if ((uintptr_t)base % 16 != 0 || (ld * 2) % 16 != 0)
+    return llmk_fail(-1, "tensor map: base and row pitch must be multiples of 16 bytes");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return llmk_fail(-2, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return 0;
+}
+
+}  // namespace tc
+
+namespace {
+
+using namespace tc;
+
+constexpr int BP = 128;            // rows of P per tile = M of the MMA
+constexpr int BK = 64;             // elements of K per stage = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;       // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
+constexpr int P_STAGE_BYTES = BP * BK * 2;
+
+__host__ __device__ constexpr int q_stage_bytes(int bnq) { return bnq * BK * 2; }
+__host__ __device__ constexpr int stages_for(int bnq) { return bnq >= 256 ? 4 : (bnq >= 128 ? 6 : 8); }
+__host__ __device__ constexpr int smem_bytes_for(int bnq) {
+  return stages_for(bnq) * (P_STAGE_BYTES + q_stage_bytes(bnq)) + 1024 /* alignment */ + 256 /* barriers */;
+}
+__host__ __device__ constexpr uint32_t tmem_cols_for(int bnq) { return bnq < 32 ? 32 : bnq; }
+
+template <typename TOut>
+__device__ __forceinline__ void store_one(TOut* p, float v) { *p = from_f32<TOut>(v); }
+
+// error codes written to *err_flag: which wait gave up
+enum : int { ERR_PRODUCER = 1, ERR_MMA = 2, ERR_EPILOGUE = 3 };
+
+template <int BNQ, bool SWAP, typename TOut>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+               TOut* __restrict__ C, long long ldc, long long split_stride, int M, int N, int K,
+               int kblocks_per_split, int* __restrict__ err_flag) {
+  constexpr int STAGES = stages_for(BNQ);
+  constexpr int Q_STAGE_BYTES = q_stage_bytes(BNQ);
+  constexpr uint32_t TMEM_COLS = tmem_cols_for(BNQ);
+  constexpr uint32_t IDESC = idesc_bf16_f32(BP, BNQ);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem_p = smem;
+  uint8_t* smem_q = smem + STAGES * P_STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * (P_STAGE_BYTES + Q_STAGE_BYTES));
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* accum_bar = empty_bar + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int p0 = blockIdx.x * BP, q0 = blockIdx.y * BNQ;
+  const int total_kb = (K + BK - 1) / BK;
+  const int kb_begin = blockIdx.z * kblocks_per_split;
+  const int kb_end = min(total_kb, kb_begin + kblocks_per_split);
+  const int nkb = max(0, kb_end - kb_begin);
+  C += (long long)blockIdx.z * split_stride;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(accum_bar, 1);
+    fence_mbar_init();
+    prefetch_tensormap(&map_p);
+    prefetch_tensormap(&map_q);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- producer: TMA loads into the ring ----
+      int issued = 0;
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (i / STAGES) & 1;
+        ok = mbar_wait(&empty_bar[s], phase ^ 1);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&full_bar[s], P_STAGE_BYTES + Q_STAGE_BYTES);
+        const int k = (kb_begin + i) * BK;
+        tma_load_2d(smem_p + s * P_STAGE_BYTES, &map_p, k, p0, &full_bar[s]);
+        tma_load_2d(smem_q + s * Q_STAGE_BYTES, &map_q, k, q0, &full_bar[s]);
+        issued = i + 1;
+      }
+      if (!ok) {
+        atomicExch(err_flag, ERR_PRODUCER);
+        // loads already in flight must land before the CTA may go: wait for them (bounded)
+        for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(&full_bar[i % STAGES], (i / STAGES) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer ----
+      bool ok = true;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (i / STAGES) & 1;
+        ok = mbar_wait(&full_bar[s], phase);
+        if (!ok) break;
+        fence_after_sync();
+        const uint64_t desc_p = smem_desc_sw128(smem_u32(smem_p + s * P_STAGE_BYTES));
+        const uint64_t desc_q = smem_desc_sw128(smem_u32(smem_q + s * Q_STAGE_BYTES));
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          // 16 elements of K = 32 bytes further along the swizzled row: +2 in units of 16 bytes
+          mma_bf16(tmem_base, desc_p + 2 * k, desc_q + 2 * k, IDESC, (i | k) != 0);
+        }
+        mma_commit(&empty_bar[s]);
+      }
+      if (!ok) atomicExch(err_flag, ERR_MMA);
+      mma_commit(accum_bar);          // arrives when everything issued above has finished
+    }
+  } else {
+    // ---- epilogue: tensor memory -> registers -> global ----
+    const int quad = warp & 3;                       // the lanes this warp may read: 32*quad ..
+    const int p = p0 + quad * 32 + lane;             // row of P that this thread holds
+    bool ok = mbar_wait(accum_bar, 0);
+    if (!ok && lane == 0) atomicExch(err_flag, ERR_EPILOGUE);
+    fence_after_sync();
+    constexpr int CHUNK = BNQ >= 32 ? 32 : 16;
+    const int p_limit = SWAP ? N : M, q_limit = SWAP ? M : N;
+#pragma unroll 1
+    for (int c = 0; c < BNQ; c += CHUNK) {
+      float v[CHUNK];
+      if (nkb > 0 && ok) {
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c;
+        if (CHUNK == 32) {
+          uint32_t r[32];
+          tmem_ld_x32(taddr, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < CHUNK; ++j) v[j] = __uint_as_float(r[j]);
+        } else {
+          uint32_t r[16];
+          tmem_ld_x16(taddr, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < CHUNK; ++j) v[j] = __uint_as_float(r[j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < CHUNK; ++j) v[j] = 0.f;
+      }
+      if (p >= p_limit) continue;
+      const int q = q0 + c;
+      if (SWAP) {
+        // thread holds C[m = q + j][n = p]: neighbouring lanes are neighbouring n
+#pragma unroll
+        for (int j = 0; j < CHUNK; ++j)
+          if (q + j < q_limit) store_one(C + (long long)(q + j) * ldc + p, v[j]);
+      } else {
+        // thread holds C[m = p][n = q .. q + CHUNK)
+        TOut* row = C + (long long)p * ldc + q;
+        const bool vec_ok = (q + CHUNK <= q_limit) && ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
+        if (vec_ok) {
+          if (sizeof(TOut) == 2) {
+#pragma unroll
+            for (int j = 0; j < CHUNK; j += 8) {
+              uint4 u;
+              __nv_bfloat162 b0 = __floats2bfloat162_rn(v[j], v[j + 1]), b1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+              __nv_bfloat162 b2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), b3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+              u.x = *reinterpret_cast<uint32_t*>(&b0); u.y = *reinterpret_cast<uint32_t*>(&b1);
+              u.z = *reinterpret_cast<uint32_t*>(&b2); u.w = *reinterpret_cast<uint32_t*>(&b3);
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(row) + j) = u;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < CHUNK; j += 4)
+              *reinterpret_cast<float4*>(reinterpret_cast<float*>(row) + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < CHUNK; ++j)
+            if (q + j < q_limit) store_one(row + j, v[j]);
+        }
+      }
+    }
+  }
+
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side ----------------------------------------------------------------
+struct MapKey {
+  const void* base; uint64_t rows, cols, ld; uint32_t box;
+  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box == o.box; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.base;
+    h = h * 1000003u ^ k.rows; h = h * 1000003u ^ k.cols; h = h * 1000003u ^ k.ld; h = h * 1000003u ^ k.box;
+    return h;
+  }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+std::mutex g_maps_mutex;
+
+int get_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box) {
+  MapKey key{base, rows, cols, ld, box};
+  std::lock_guard<std::mutex> lock(g_maps_mutex);
+  auto it = g_maps.find(key);
+  if (it == g_maps.end()) {
+    CUtensorMap m;
+    int rc = encode_tensor_map_bf16(&m, base, rows, cols, ld, box);
+    if (rc) return rc;
+    if (g_maps.size() > 4096) g_maps.clear();
+    it = g_maps.emplace(key, m).first;
+  }
+  *out = it->second;
+  return 0;
+}
+
+int* g_err_flag = nullptr;      // device word; one per process
+
+int ensure_err_flag() {
+  if (g_err_flag) return 0;
+  cudaError_t e = cudaMalloc(&g_err_flag, sizeof(int));
+  if (e != cudaSuccess) return llmk_fail((int)e, "gemm_tc: cannot allocate the error word");
+  cudaMemset(g_err_flag, 0, sizeof(int));
+  return 0;
+}
+
+template <int BNQ, bool SWAP, typename TOut>
+int launch_cfg(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long ldc, long long split_stride, int M,
+               int N, int K, int splits, int kb_per_split, cudaStream_t stream) {
+  auto kern = gemm_tc_kernel<BNQ, SWAP, TOut>;
+  constexpr int smem = smem_bytes_for(BNQ);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return llmk_fail((int)e, "gemm_tc: cannot set %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int p_rows = SWAP ? N : M, q_rows = SWAP ? M : N;
+  dim3 grid((p_rows + BP - 1) / BP, (q_rows + BNQ - 1) / BNQ, splits);
+  kern<<<grid, THREADS, smem, stream>>>(mp, mq, (TOut*)C, ldc, split_stride, M, N, K, kb_per_split, g_err_flag);
+  LLMK_LAUNCH_CHECK("gemm_tc");
+}
+
+template <typename TOut>
+int launch_out(bool swap, int bnq, const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long ldc,
+               long long split_stride, int M, int N, int K, int splits, int kbps, cudaStream_t s) {
+  if (swap) {
+    switch (bnq) {
+      case 16: return launch_cfg<16, true, TOut>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+      case 32: return launch_cfg<32, true, TOut>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+      case 64: return launch_cfg<64, true, TOut>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+      case 128: return launch_cfg<128, true, TOut>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+    }
+  } else {
+    switch (bnq) {
+      case 128: return launch_cfg<128, false, TOut>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+      case 256: return launch_cfg<256, false, TOut>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+    }
+  }
+  return llmk_fail(-1, "gemm_tc: no kernel for swap=%d tile=%d", (int)swap, bnq);
+}
+
+}  // namespace
+
+// Whether the tensor-core product takes this problem: bf16 operands with 16-byte aligned
+// rows (K and both pitches multiples of 8 elements).
+LLMK_API int llmk_gemm_tc_supported(const void* A, const void* W, int M, int N, int K, long long lda, long long ldw) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % 8 || lda % 8 || ldw % 8) return 0;
+  if ((uintptr_t)A % 16 || (uintptr_t)W % 16) return 0;
+  return 1;
+}
+
+// A [M,K] and W [N,K] bf16.  splits == 1: C (bf16 if out_dtype == 1, else float32) [M, ldc].
+// splits > 1: C must be float32 and is written as [splits][M][ldc] partial sums
+// (split_stride = M * ldc elements) over kblocks_per_split blocks of 64 along K each.
+// swap != 0 puts the weights on the 128-row side of the MMA; tile is the other side's width.
+LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
+                          long long ldc, int out_dtype, int swap, int tile, int splits, int kblocks_per_split,
+                          cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  LLMK_REQUIRE(llmk_gemm_tc_supported(A, W, M, N, K, lda, ldw), "gemm_tc: K=%d and the row pitches must be multiples of 8 and the bases 16-byte aligned", K);
+  LLMK_REQUIRE(splits >= 1 && kblocks_per_split >= 1 && (long long)splits * kblocks_per_split * BK >= K,
+               "gemm_tc: %d splits of %d k-blocks do not cover K=%d", splits, kblocks_per_split, K);
+  LLMK_REQUIRE(splits == 1 || out_dtype == LLMK_F32, "gemm_tc: split-K needs a float32 output");
+  LLMK_REQUIRE(splits <= 65535, "gemm_tc: too many splits");
+  int rc = ensure_err_flag();
+  if (rc) return rc;
+  CUtensorMap mp, mq;
+  const void* P = swap ? W : A; const void* Q = swap ? A : W;
+  const long long ldp = swap ? ldw : lda, ldq = swap ? lda : ldw;
+  const int p_rows = swap ? N : M, q_rows = swap ? M : N;
+  if ((rc = get_map(&mp, P, p_rows, K, ldp, BP))) return rc;
+  if ((rc = get_map(&mq, Q, q_rows, K, ldq, tile))) return rc;
+  const long long split_stride = splits > 1 ? (long long)M * ldc : 0;
+  if (out_dtype == LLMK_F32) return launch_out<float>(swap != 0, tile, mp, mq, C, ldc, split_stride, M, N, K, splits, kblocks_per_split, stream);
+  if (out_dtype == LLMK_BF16) return launch_out<__nv_bfloat16>(swap != 0, tile, mp, mq, C, ldc, split_stride, M, N, K, splits, kblocks_per_split, stream);
+  return llmk_fail(-1, "gemm_tc: unsupported output kind %d", out_dtype);
+}
+
+// Reads and clears the error word that a kernel sets when one of its waits gave up
+// (1 = producer, 2 = MMA issuer, 3 = epilogue).  Synchronises the device.
+LLMK_API int llmk_gemm_tc_take_error() {
+  if (!g_err_flag) return 0;
+  int v = 0;
+  cudaMemcpy(&v, g_err_flag, sizeof(int), cudaMemcpyDeviceToHost);
+  if (v) cudaMemset(g_err_flag, 0, sizeof(int));
+  return v;
+}
+
+// out[m, n] = sum over s of partials[s][m][n], in the order s = 0, 1, ...
+template <typename TOut>
+__global__ void reduce_partials_kernel(TOut* __restrict__ out, const float* __restrict__ partials, size_t mn, int splits) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < mn; i += (size_t)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += partials[(size_t)s * mn + i];
+    out[i] = from_f32<TOut>(acc);
+  }
+}
+
+LLMK_API int llmk_reduce_partials(void* out, const float* partials, long long mn, int splits, int out_dtype,
+                                  cudaStream_t stream) {
+  if (mn == 0) return 0;
+  size_t blocks = ((size_t)mn + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  return dispatch_dtype(out_dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    reduce_partials_kernel<T><<<(int)blocks, 256, 0, stream>>>((T*)out, partials, (size_t)mn, splits);
+    LLMK_LAUNCH_CHECK("reduce_partials");
+  });
+}

@@ -173,9 +173,85 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
                             ctx.n_tokens, n_heads, n_kv, head_dim, window, scale)
 
 
-def gemm_fast_available(a, w, out, rows: int) -> bool:
-    return False
+# ---- tensor-core product ------------------------------------------------------------
+
+_SMS = 148
+_PARTIALS = {}      # device -> float32 scratch for split-K partial sums
+_PARTIAL_BYTES = 64 << 20
 
 
-def gemm_fast(a, w, out, rows: int) -> None:
-    raise KernelError("no tensor-core product is built")
+def _ceil_div(a: int, b: int) -> int:
+    return -(-a // b)
+
+
+def plan_gemm(M: int, N: int, K: int):
+    """(swap, tile, splits, k-blocks per split) for the tensor-core product.
+
+    Up to 128 rows the weights take the 128-row side of the MMA and the rows become its N
+    (16 to 128); above that the rows take the 128-row side and the tile is 128 or 256 weight
+    rows wide.  K (in blocks of 64) is split over CTAs when there are too few tiles to keep
+    all SMs streaming; the cost model counts k-blocks per CTA plus a fixed per-CTA cost,
+    times the number of waves."""
+    kb = _ceil_div(K, 64)
+    if M <= 128:
+        options = [(True, 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128, _ceil_div(N, 128))]
+    else:
+        options = [(False, t, _ceil_div(M, 128) * _ceil_div(N, t)) for t in (256, 128)]
+    best = None
+    for swap, tile, tiles in options:
+        width = 1.0 if swap else tile / 128.0
+        for s in range(1, min(kb, 32) + 1):
+            per = _ceil_div(kb, s)
+            if _ceil_div(kb, per) != s:
+                continue
+            if s > 1 and s * M * N * 4 > _PARTIAL_BYTES:
+                break
+            waves = _ceil_div(tiles * s, _SMS)
+            cost = waves * (per * width + 4.0) + (0.5 * s if s > 1 else 0.0)
+            if best is None or cost < best[0] - 1e-9:
+                best = (cost, swap, tile, s, per)
+    return best[1:]
+
+
+def _partials(device) -> torch.Tensor:
+    buf = _PARTIALS.get(device)
+    if buf is None:
+        buf = torch.empty(_PARTIAL_BYTES // 4, dtype=torch.float32, device=device)
+        _PARTIALS[device] = buf
+    return buf
+
+
+def gemm_fast_available(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int) -> bool:
+    """Whether the tcgen05 product takes this problem (bfloat16, rows of 16-byte multiples)."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    n, k = w.shape
+    return bool(load().llmk_gemm_tc_supported(_ptr(a), _ptr(w), c_int(rows), c_int(n), c_int(k),
+                                              c_longlong(a.stride(0)), c_longlong(w.stride(0))))
+
+
+def gemm_fast(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, plan=None) -> None:
+    """out[:rows] = a[:rows] @ w.T on the tensor cores (bfloat16 in, float32 accumulation)."""
+    _rows_contig(a, "a"); _rows_contig(w, "w"); _rows_contig(out, "out")
+    n, k = w.shape
+    assert a.shape[1] == k and out.shape[1] == n
+    swap, tile, splits, per = plan or plan_gemm(rows, n, k)
+    lib = load()
+    if splits == 1:
+        _check(lib.llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
+                                c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
+                                c_int(_kind(out.dtype)), c_int(int(swap)), c_int(tile), c_int(1), c_int(per),
+                                _stream()))
+        return
+    assert out.is_contiguous()
+    part = _partials(a.device)
+    _check(lib.llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(part), c_int(rows), c_int(n), c_int(k),
+                            c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(n), c_int(_F32),
+                            c_int(int(swap)), c_int(tile), c_int(splits), c_int(per), _stream()))
+    _check(lib.llmk_reduce_partials(_ptr(out), _ptr(part), c_longlong(rows * n), c_int(splits),
+                                    c_int(_kind(out.dtype)), _stream()))
+
+
+def gemm_tc_take_error() -> int:
+    """The code a tensor-core kernel left when one of its bounded waits gave up (0 = none)."""
+    return int(load().llmk_gemm_tc_take_error())

@@ -1,0 +1,279 @@
+"""Each kernel alone against a plain float32/float64 torch reference of the same
+operation, at sizes other than the engine's tiny models (odd widths, tails, several
+head shapes)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return 1e-5 if dtype == torch.float32 else 1.6e-2
+
+
+def rel_err(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from llm_b200.csrc import ops as o
+    return o
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_bad_id(ops, dtype):
+    torch.manual_seed(0)
+    table = torch.randn(301, 72, device=DEV).to(dtype)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    resid = torch.full((8, 72), 7.0, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.embedding(resid, table, ids, 5, status)
+    assert torch.equal(resid[:5], table[ids.long()].float()) and float(resid[5:].min()) == 7.0
+    assert int(status.item()) == 0
+    ops.embedding(resid, table, torch.tensor([3, 301], dtype=torch.int32, device=DEV), 2, status)
+    assert int(status.item()) == 1 and float(resid[1].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,eps", [(72, 1e-5), (1000, 1e-6), (2048, 1e-2), (8961, 1e-5)])
+def test_add_rmsnorm(ops, dtype, hidden, eps):
+    torch.manual_seed(1)
+    rows = 7
+    resid = torch.randn(rows + 1, hidden, device=DEV) * 3
+    delta = torch.randn(rows, hidden, device=DEV).to(dtype)
+    gain = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    ref_resid = resid[:rows].double() + delta.double()
+    ref = ref_resid / torch.sqrt((ref_resid ** 2).mean(-1, keepdim=True) + eps) * gain.double()
+    keep = resid[rows].clone()
+    out = torch.zeros(rows, hidden, device=DEV, dtype=dtype)
+    ops.add_rmsnorm(resid, delta, gain, out, rows, eps)
+    assert rel_err(resid[:rows], ref_resid) < 1e-6 and torch.equal(resid[rows], keep)
+    assert rel_err(out, ref) < tol(dtype)
+    # without a pending term the residual is left alone
+    before = resid.clone()
+    ops.add_rmsnorm(resid, None, gain, out, rows, eps)
+    assert torch.equal(resid, before) and rel_err(out, ref) < tol(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gather_rows_and_silu_mul(ops, dtype):
+    torch.manual_seed(2)
+    resid = torch.randn(20, 130, device=DEV)
+    delta = torch.randn(20, 130, device=DEV).to(dtype)
+    rows = torch.tensor([19, 0, 7, 7], dtype=torch.int32, device=DEV)
+    out = torch.zeros(4, 130, device=DEV)
+    ops.gather_rows(out, resid, delta, rows, 4)
+    assert rel_err(out, resid[rows.long()].double() + delta[rows.long()].double()) < 1e-6
+    ops.gather_rows(out, resid, None, rows, 3)
+    assert torch.equal(out[:3], resid[rows.long()[:3]])
+    inter = 8961 if dtype == torch.float32 else 173
+    gu = (torch.randn(5, 2 * inter, device=DEV) * 4).to(dtype)
+    act = torch.zeros(5, inter, device=DEV, dtype=dtype)
+    ops.silu_mul(act, gu, 5)
+    g, u = gu[:, :inter].double(), gu[:, inter:].double()
+    assert rel_err(act, g / (1 + torch.exp(-g)) * u) < tol(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (5, 172, 64), (33, 65, 172), (130, 257, 96), (64, 64, 17), (3, 1000, 2048)])
+def test_gemm_simt(ops, dtype, M, N, K):
+    torch.manual_seed(3)
+    a = torch.randn(M + 2, K, device=DEV).to(dtype)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(dtype)
+    out = torch.full((M + 2, N), 5.0, device=DEV, dtype=dtype)
+    ops.gemm_simt(a, w, out, M)
+    ref = a[:M].double() @ w.double().T
+    assert rel_err(out[:M], ref) < tol(dtype)
+    assert float(out[M:].float().min()) == 5.0                  # rows beyond M untouched
+    if dtype == torch.bfloat16:
+        out32 = torch.zeros(M, N, device=DEV)
+        ops.gemm_simt(a, w, out32, M)
+        assert rel_err(out32, ref) < 1e-5                       # float32 output of a bfloat16 product
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch(ops):
+    torch.manual_seed(4)
+    a = torch.randn(150, 200, device=DEV)
+    w = torch.randn(77, 200, device=DEV)
+    full = torch.zeros(150, 77, device=DEV)
+    ops.gemm_simt(a, w, full, 150)
+    one = torch.zeros(1, 77, device=DEV)
+    for r in (0, 63, 64, 149):
+        ops.gemm_simt(a[r:r + 1].contiguous(), w, one, 1)
+        assert torch.equal(one[0], full[r])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 256, 512), (16, 2048, 2048), (17, 384, 192), (50, 1000, 320),
+                                   (128, 128, 128), (100, 136, 72), (129, 256, 128), (300, 520, 264), (512, 2560, 2048)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tensor_core(ops, M, N, K, out_dtype):
+    torch.manual_seed(5)
+    a = torch.randn(M + 1, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    out = torch.full((M + 1, N), 3.0, device=DEV, dtype=out_dtype)
+    assert ops.gemm_fast_available(a, w, out, M)
+    ops.gemm_fast(a, w, out, M)
+    torch.cuda.synchronize()
+    assert ops.gemm_tc_take_error() == 0
+    ref = a[:M].double() @ w.double().T
+    assert rel_err(out[:M], ref) < (1e-5 if out_dtype == torch.float32 else 1e-2)
+    assert float(out[M:].float().min()) == 3.0
+
+
+@pytest.mark.parametrize("swap,tile,splits", [(True, 16, 1), (True, 16, 4), (True, 32, 2), (True, 64, 3), (True, 128, 1),
+                                              (False, 128, 1), (False, 256, 1), (False, 256, 2), (False, 128, 5)])
+def test_gemm_tensor_core_every_configuration(ops, swap, tile, splits):
+    torch.manual_seed(6)
+    M = {16: 9, 32: 30, 64: 64, 128: 77}[tile] if swap else 200
+    N, K = 392, 5 * 64 + 24
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    out = torch.zeros(M, N, device=DEV)
+    kb = -(-K // 64)
+    per = -(-kb // splits)
+    ops.gemm_fast(a, w, out, M, plan=(swap, tile, -(-kb // per), per))
+    torch.cuda.synchronize()
+    assert ops.gemm_tc_take_error() == 0
+    assert rel_err(out, a.double() @ w.double().T) < 1e-5
+
+
+def test_gemm_tensor_core_refuses_unaligned_rows(ops):
+    a = torch.zeros(4, 172, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(64, 172, device=DEV, dtype=torch.bfloat16)
+    assert not ops.gemm_fast_available(a, w, torch.zeros(4, 64, device=DEV, dtype=torch.bfloat16), 4)
+    assert not ops.gemm_fast_available(a.float(), w.float(), torch.zeros(4, 64, device=DEV), 4)
+
+
+def paged_reference(q, k, v, window, scale):
+    """q [T, NH, HS], k/v [T, NKV, HS] of one sequence -> [T, NH*HS], float64."""
+    T, NH, HS = q.shape
+    G = NH // k.shape[1]
+    out = torch.zeros(T, NH, HS, dtype=torch.float64)
+    for t in range(T):
+        lo = max(0, t - window + 1) if window else 0
+        for h in range(NH):
+            s = (k[lo:t + 1, h // G].double() @ q[t, h].double()) * scale
+            out[t, h] = torch.softmax(s, 0) @ v[lo:t + 1, h // G].double()
+    return out.reshape(T, NH * HS)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("NH,NKV,HS,page,window", [(4, 2, 16, 16, 0), (3, 1, 32, 8, 0), (6, 3, 48, 32, 19),
+                                                   (8, 8, 64, 16, 40), (2, 1, 128, 64, 0), (5, 5, 256, 16, 0)])
+def test_rope_write_and_paged_attention(ops, dtype, NH, NKV, HS, page, window):
+    """Two requests in one batch with reversed, interleaved pages: rope + cache write, then
+    attention of a prompt portion beside a single decoded token."""
+    torch.manual_seed(7)
+    lens = [45, 70]
+    n_pages = 24
+    W = 12
+    kp = torch.zeros(n_pages, NKV, page, HS, device=DEV, dtype=dtype)
+    vp = torch.zeros_like(kp)
+    half = HS // 2
+    inv = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / HS)
+    ang = torch.arange(128, dtype=torch.float64)[:, None] * inv[None]
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    need = [-(-n // page) for n in lens]
+    pages = list(range(n_pages - 1, -1, -1))                       # reversed physical order
+    tables = [[pages[2 * i + r] for i in range(need[r])] for r in range(2)] if 2 * max(need) <= n_pages else None
+    if tables is None:
+        pytest.skip("pool too small for this page size")
+    bt = torch.zeros(2, W, dtype=torch.int32)
+    for r in range(2):
+        bt[r, :need[r]] = torch.tensor(tables[r], dtype=torch.int32)
+    bt = bt.to(DEV)
+    width = (NH + 2 * NKV) * HS
+    seqs = [torch.randn(n, width) for n in lens]
+    scale = 1.0 / math.sqrt(HS)
+    refs = []
+    for s in seqs:
+        q = s[:, :NH * HS].reshape(-1, NH, HS).to(dtype).double()
+        k = s[:, NH * HS:(NH + NKV) * HS].reshape(-1, NKV, HS).to(dtype).double()
+        v = s[:, (NH + NKV) * HS:].reshape(-1, NKV, HS).to(dtype)
+        c, sn = cos[:len(s)].double().cpu()[:, None], sin[:len(s)].double().cpu()[:, None]
+        rot = lambda x: torch.cat([x[..., :half] * c - x[..., half:] * sn, x[..., :half] * sn + x[..., half:] * c], -1)
+        refs.append(paged_reference(rot(q).to(dtype), rot(k).to(dtype), v, window, scale))
+
+    # steps: request 0 in portions 30 + 15, request 1 in 69 + a single token beside request 0's second portion
+    plan = [[(0, 0, 30), (1, 0, 69)], [(0, 30, 15), (1, 69, 1)]]
+    got = [torch.zeros(n, NH * HS, dtype=torch.float64) for n in lens]
+    for step in plan:
+        rows = torch.cat([seqs[r][a:a + n] for r, a, n in step]).to(dtype).to(DEV).contiguous()
+        pos = torch.cat([torch.arange(a, a + n) for r, a, n in step]).to(torch.int32)
+        ent = torch.cat([torch.full((n,), i) for i, (r, a, n) in enumerate(step)]).to(torch.int32)
+        slot = torch.tensor([tables[r][p // page] * page + p % page for r, a, n in step for p in range(a, a + n)],
+                            dtype=torch.int32)
+        T = rows.shape[0]
+        ops.rope_kv_write(rows, cos, sin, pos.to(DEV), slot.to(DEV), kp, vp, T, NH, NKV, HS)
+        out = torch.zeros(T, NH * HS, device=DEV, dtype=dtype)
+        ops.paged_attention_generic(out, rows, kp, vp, bt, ent.to(DEV), pos.to(DEV), T, NH, NKV, HS, window, scale)
+        at = 0
+        for r, a, n in step:
+            got[r][a:a + n] = out[at:at + n].double().cpu()
+            at += n
+    for r in range(2):
+        assert rel_err(got[r], refs[r]) < (2e-6 if dtype == torch.float32 else 1.6e-2)
+
+
+def test_attention_finds_a_far_key_and_respects_the_window_edge(ops):
+    """One key far back gets a score that dominates: its value must come through, and must
+    vanish exactly when the window no longer reaches it."""
+    NH = NKV = 1
+    HS, page, n = 32, 16, 300
+    kp = torch.zeros(20, 1, page, HS, device=DEV)
+    vp = torch.zeros_like(kp)
+    torch.manual_seed(8)
+    k = torch.randn(n, HS) * 0.1
+    v = torch.randn(n, HS)
+    far = 37
+    k[far] = 0
+    k[far, 0] = 50.0
+    table = list(range(19, 0, -1))
+    for p in range(n):
+        kp[table[p // page], 0, p % page] = k[p].to(DEV)
+        vp[table[p // page], 0, p % page] = v[p].to(DEV)
+    bt = torch.tensor([table + [0]], dtype=torch.int32, device=DEV)
+    q = torch.zeros(1, HS, device=DEV)
+    q[0, 0] = 50.0
+    out = torch.zeros(1, HS, device=DEV)
+    pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+    ent = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for window, sees in ((0, True), (n - far, True), (n - far - 1, False)):
+        ops.paged_attention_generic(out, q, kp, vp, bt, ent, pos, 1, 1, 1, HS, window, 1.0)
+        close = float((out[0].cpu() - v[far]).abs().max()) < 1e-4
+        assert close == sees, (window, sees)
+
+
+def test_sampling_kernel(ops):
+    import plain_llama
+    torch.manual_seed(9)
+    V = 1003
+    logits = torch.randn(6, V, device=DEV) * 3
+    logits[1, 3] = logits[1, 9] = 50.0          # a tie: the lowest id wins
+    logits[2, V - 1] = 60.0                     # the last id
+    out = torch.zeros(6, dtype=torch.int32, device=DEV)
+    ops.sample_rows(out, logits, 6)
+    want = [plain_llama.argmax_lowest(logits[r].cpu()) for r in range(6)]
+    assert out.tolist() == want and want[1] == 3 and want[2] == V - 1
+    temps = torch.tensor([0.8, 0.0, 1.5, 0.3, 1.0, 0.8], device=DEV)
+    for trial in range(20):
+        u = torch.rand(6)
+        ops.sample_rows(out, logits, 6, temps, u.to(DEV))
+        got = out.tolist()
+        for r in range(6):
+            if float(temps[r]) <= 0:
+                assert got[r] == want[r]
+                continue
+            p = torch.softmax(logits[r].double().cpu() / float(temps[r]), -1)
+            c = torch.cumsum(p, -1)
+            ref = plain_llama.sample_temperature(logits[r].cpu(), float(temps[r]), float(u[r]))
+            if got[r] != ref:       # only a draw that lands within rounding of a boundary may differ by one id
+                lo = float(c[got[r] - 1]) if got[r] > 0 else 0.0
+                assert abs(got[r] - ref) == 1 and min(abs(float(u[r]) - lo), abs(float(u[r]) - float(c[got[r]]))) < 1e-5
