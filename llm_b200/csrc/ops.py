@@ -165,10 +165,53 @@ def sample_rows(out: torch.Tensor, logits: torch.Tensor, rows: int, temperature=
                                    c_int(logits.shape[1]), _ptr(temperature), _ptr(uniform), _stream()))
 
 
+_ATTN_PARTIALS = {}
+
+
+def _attn_partials(device, n_floats: int) -> torch.Tensor:
+    buf = _ATTN_PARTIALS.get(device)
+    if buf is None or buf.numel() < n_floats:
+        buf = torch.empty(max(n_floats, 1 << 20), dtype=torch.float32, device=device)
+        _ATTN_PARTIALS[device] = buf
+    return buf
+
+
+def decode_splits(n_entries: int, n_kv: int, max_keys: int) -> int:
+    """How many ranges the keys of one request are cut into: enough CTAs to fill the GPU,
+    no range shorter than 64 keys at the longest context, at most 32."""
+    return max(1, min(32, _ceil_div(max_keys, 64), (_SMS * 6) // max(1, n_entries * n_kv)))
+
+
+def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                           block_table: torch.Tensor, kv_lens: torch.Tensor, n_entries: int, n_heads: int,
+                           n_kv: int, head_dim: int, window: int, scale: float, splits=None) -> None:
+    """One query token per entry (row e of q), attending to its request's kv_lens[e] keys."""
+    _rows_contig(out, "out"); _rows_contig(q, "q")
+    assert block_table.dim() == 2 and block_table.is_contiguous() and block_table.dtype == torch.int32
+    assert kv_lens.dtype == torch.int32 and k_pages.is_contiguous() and v_pages.is_contiguous()
+    assert q.dtype == k_pages.dtype == out.dtype
+    page = k_pages.shape[2]
+    if splits is None:
+        splits = decode_splits(n_entries, n_kv, block_table.shape[1] * page)
+    n_o = n_entries * n_heads * splits * head_dim
+    buf = _attn_partials(q.device, n_o + n_entries * n_heads * splits * 2)
+    _check(load().llmk_paged_attention_decode(
+        _ptr(out), c_longlong(out.stride(0)), _ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
+        _ptr(block_table), c_int(block_table.shape[1]), _ptr(kv_lens), c_int(n_entries), c_int(n_heads),
+        c_int(n_kv), c_int(head_dim), c_int(page), c_int(window or 0), c_float(scale), c_int(splits),
+        c_void_p(buf.data_ptr()), c_void_p(buf.data_ptr() + 4 * n_o), c_int(_kind(q.dtype)), _stream()))
+    count_launches(1)        # the split kernel and the merge are two launches
+
+
 def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: int, head_dim: int,
                     window: int, scale: float) -> None:
     """Attention of the step's tokens over their requests' pages; q is the first
-    n_heads * head_dim columns of qkv.  Chooses the kernel for the batch."""
+    n_heads * head_dim columns of qkv.  Chooses the kernel for the batch: the split-key
+    decode kernel when every entry brings one token (bfloat16), else the general kernel."""
+    if ctx.decode_only and qkv.dtype == torch.bfloat16:
+        paged_attention_decode(out, qkv, k_pages, v_pages, group.block_table, ctx.kv_lens, ctx.n_entries,
+                               n_heads, n_kv, head_dim, window, scale)
+        return
     paged_attention_generic(out, qkv, k_pages, v_pages, group.block_table, ctx.token_entry, ctx.positions,
                             ctx.n_tokens, n_heads, n_kv, head_dim, window, scale)
 

@@ -277,3 +277,46 @@ def test_sampling_kernel(ops):
             if got[r] != ref:       # only a draw that lands within rounding of a boundary may differ by one id
                 lo = float(c[got[r] - 1]) if got[r] > 0 else 0.0
                 assert abs(got[r] - ref) == 1 and min(abs(float(u[r]) - lo), abs(float(u[r]) - float(c[got[r]]))) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("NH,NKV,HS,page,window,splits", [(4, 2, 16, 16, 0, 3), (3, 1, 32, 8, 0, 1), (6, 3, 48, 32, 19, 4),
+                                                          (32, 4, 64, 16, 0, 7), (2, 1, 128, 64, 100, 32), (12, 1, 256, 16, 0, 5),
+                                                          (10, 10, 80, 16, 0, 2)])
+def test_decode_attention_matches_the_general_kernel_and_plain(ops, dtype, NH, NKV, HS, page, window, splits):
+    """Requests of very different lengths in one decode batch, pages in shuffled order."""
+    torch.manual_seed(11)
+    lens = [1, 2, 33, 257, 140]
+    B = len(lens)
+    W = -(-max(lens) // page) + 1
+    n_pages = sum(-(-n // page) for n in lens) + 3
+    perm = torch.randperm(n_pages).tolist()
+    kp = torch.randn(n_pages, NKV, page, HS, device=DEV).to(dtype)
+    vp = torch.randn(n_pages, NKV, page, HS, device=DEV).to(dtype)
+    bt = torch.zeros(B, W, dtype=torch.int32)
+    at = 0
+    for b, n in enumerate(lens):
+        k = -(-n // page)
+        bt[b, :k] = torch.tensor(perm[at:at + k], dtype=torch.int32)
+        at += k
+    bt = bt.to(DEV)
+    q = torch.randn(B, NH * HS + 8, device=DEV).to(dtype)       # a row pitch wider than the heads
+    kv_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 0.7 / math.sqrt(HS)
+    out = torch.zeros(B, NH * HS, device=DEV, dtype=dtype)
+    ops.paged_attention_decode(out, q, kp, vp, bt, kv_lens, B, NH, NKV, HS, window, scale, splits=splits)
+    ref = torch.zeros(B, NH * HS, dtype=torch.float64)
+    G = NH // NKV
+    for b, n in enumerate(lens):
+        lo = max(0, n - window) if window else 0
+        keys = [(int(bt[b, j // page]), j % page) for j in range(lo, n)]
+        for h in range(NH):
+            K = torch.stack([kp[pg, h // G, o].double().cpu() for pg, o in keys])
+            V = torch.stack([vp[pg, h // G, o].double().cpu() for pg, o in keys])
+            s = (K @ q[b, h * HS:(h + 1) * HS].double().cpu()) * scale
+            ref[b, h * HS:(h + 1) * HS] = torch.softmax(s, 0) @ V
+    assert rel_err(out, ref) < (2e-6 if dtype == torch.float32 else 1e-2)
+    gen = torch.zeros_like(out)
+    ent = torch.arange(B, dtype=torch.int32, device=DEV)
+    ops.paged_attention_generic(gen, q, kp, vp, bt, ent, kv_lens - 1, B, NH, NKV, HS, window, scale)
+    assert rel_err(out, gen.double()) < (2e-6 if dtype == torch.float32 else 1e-2)
