@@ -243,3 +243,54 @@ LLMK_API int llmk_paged_attention_decode(void* out, long long out_stride, const 
     LLMK_LAUNCH_CHECK("attention_decode_combine");
   });
 }
+
+// ---- the variant that allocates nothing (declared in no_alloc.h) ----------------
+#include "no_alloc.h"
+
+namespace {
+
+// The key ranges' partial results for the static variant.  In host code this name is only
+// a stand-in for the symbol: the device address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_decode_static_scratch[LLMK_DECODE_STATIC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* g_decode_static_ptr[kMaxDevices] = {};
+
+// Device address of the scratch array on the current device, looked up once per device.
+int decode_static_scratch(float** ptr) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return llmk_fail((int)e, "attention_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return llmk_fail(-1, "attention_decode_static: device %d out of range", dev);
+  if (!g_decode_static_ptr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_decode_static_scratch);
+    if (e != cudaSuccess || !p)
+      return llmk_fail(e != cudaSuccess ? (int)e : -2, "attention_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_decode_static_ptr[dev] = p;
+  }
+  *ptr = g_decode_static_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+
+LLMK_API int llmk_paged_attention_decode_static(void* out, long long out_stride, const void* q, long long q_stride,
+                                                const void* k_pages, const void* v_pages, const int* block_table,
+                                                int table_width, const int* kv_lens, int n_entries, int n_heads,
+                                                int n_kv, int head_dim, int page_size, int window, float scale,
+                                                int splits, int dtype, cudaStream_t stream) {
+  if (n_entries == 0) return 0;
+  LLMK_REQUIRE(n_entries > 0 && n_heads > 0 && splits >= 1 && head_dim > 0, "attention_decode_static: bad sizes");
+  const long long n_o = (long long)n_entries * n_heads * splits * head_dim;
+  const long long n_ml = (long long)n_entries * n_heads * splits * 2;
+  LLMK_REQUIRE(n_o + n_ml <= (long long)LLMK_DECODE_STATIC_SCRATCH_FLOATS,
+               "attention_decode_static: %d entries x %d heads x %d splits x (%d + 2) = %lld floats of scratch exceed "
+               "the built-in %d", n_entries, n_heads, splits, head_dim, n_o + n_ml, (int)LLMK_DECODE_STATIC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  const int rc = decode_static_scratch(&scratch);
+  if (rc) return rc;
+  return llmk_paged_attention_decode(out, out_stride, q, q_stride, k_pages, v_pages, block_table, table_width, kv_lens,
+                                     n_entries, n_heads, n_kv, head_dim, page_size, window, scale, splits, scratch,
+                                     scratch + n_o, dtype, stream);
+}
