@@ -55,6 +55,8 @@ decode_split_kernel(float* __restrict__ partial_o, float* __restrict__ partial_m
   __shared__ float m_s[GT], l_s[GT], alpha_s[GT];
   __shared__ long long row_s[SUB];
 
+  pdl_wait();
+  pdl_launch_dependents();
   const int split = blockIdx.x, g = blockIdx.y, e = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = n_heads / n_kv;
@@ -194,6 +196,8 @@ decode_split_kernel(float* __restrict__ partial_o, float* __restrict__ partial_m
 template <typename T>
 __global__ void decode_combine_kernel(T* __restrict__ out, long long out_stride, const float* __restrict__ partial_o,
                                       const float* __restrict__ partial_ml, int n_heads, int head_dim, int splits) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int h = blockIdx.x, e = blockIdx.y;
   const size_t base = ((size_t)e * n_heads + h) * splits;
   float m = -INFINITY;
@@ -233,13 +237,13 @@ LLMK_API int llmk_paged_attention_decode(void* out, long long out_stride, const 
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     dim3 grid(splits, n_kv, n_entries);
-    decode_split_kernel<T><<<grid, THREADS, 0, stream>>>(partial_o, partial_ml, (const T*)q, q_stride, (const T*)k_pages,
+    launch_kernel(decode_split_kernel<T>, grid, dim3(THREADS), 0, stream, partial_o, partial_ml, (const T*)q, q_stride, (const T*)k_pages,
                                                         (const T*)v_pages, block_table, table_width, kv_lens, n_heads,
                                                         n_kv, head_dim, page_size, window, scale, splits);
     cudaError_t e1 = cudaPeekAtLastError();
     if (e1 != cudaSuccess) { cudaGetLastError(); return llmk_fail((int)e1, "attention_decode: %s", cudaGetErrorString(e1)); }
     dim3 grid2(n_heads, n_entries);
-    decode_combine_kernel<T><<<grid2, 64, 0, stream>>>((T*)out, out_stride, partial_o, partial_ml, n_heads, head_dim, splits);
+    launch_kernel(decode_combine_kernel<T>, grid2, dim3(64), 0, stream, (T*)out, out_stride, partial_o, partial_ml, n_heads, head_dim, splits);
     LLMK_LAUNCH_CHECK("attention_decode_combine");
   });
 }

@@ -59,6 +59,8 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
                                const int* __restrict__ positions, int n_tokens, int n_heads, int n_kv,
                                int head_dim, int page_size, int window, float scale) {
   __shared__ float q_s[WARPS][MAX_HEAD_DIM];
+  pdl_wait();
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * WARPS + warp;
   if (item >= (long long)n_tokens * n_heads) return;
@@ -138,7 +140,7 @@ LLMK_API int llmk_paged_attention_generic(void* out, long long out_stride, const
   LLMK_REQUIRE(blocks < (1ll << 31), "paged_attention: too many (token, head) items");
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
-    paged_attention_generic_kernel<T><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
+    launch_kernel(paged_attention_generic_kernel<T>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
         (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
         table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, page_size, window, scale);
     LLMK_LAUNCH_CHECK("paged_attention_generic");

@@ -71,6 +71,52 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return t;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------
+// Kernels of a step are launched back to back on one stream.  With the attribute below the
+// next kernel may be scheduled while the previous one still runs; it then does what does
+// not depend on earlier kernels (barrier set-up, tensor-memory allocation, weight loads) and
+// blocks in pdl_wait() until the previous kernel has completed and its writes are visible.
+// Every kernel launched this way calls pdl_wait() before it touches data of other kernels.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool llmk_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = llmk_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// A value that is either an element of a tensor of T or the sum, in the order s = 0, 1, ...,
+// of `splits` float32 partial results laid out [split][row][col] (split-K products).
+template <typename T>
+struct MaybePartial {
+  const T* direct;
+  const float* parts;
+  int splits;
+  long long split_stride;
+  __device__ __forceinline__ bool present() const { return direct != nullptr || parts != nullptr; }
+  __device__ __forceinline__ float at(size_t idx) const {
+    if (parts) {
+      float a = 0.f;
+      for (int s = 0; s < splits; ++s) a += parts[(size_t)s * split_stride + idx];
+      return a;
+    }
+    return to_f32(direct[idx]);
+  }
+};
+
 #define LLMK_ELEM(tag) typename std::remove_pointer<decltype(tag)>::type
 
 template <typename F>

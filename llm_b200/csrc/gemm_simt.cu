@@ -38,6 +38,8 @@ gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ W, TC* __restric
                  long long lda, long long ldw, long long ldc) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
+  pdl_wait();
+  pdl_launch_dependents();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int lrow = tid >> 2, lk = (tid & 3) * 4;
@@ -94,9 +96,9 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, long long
   const bool vec = (K % 4 == 0) && (lda % 4 == 0) && (ldw % 4 == 0) &&
                    ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0);
   if (vec)
-    gemm_simt_kernel<T, TC, 4><<<grid, THREADS, 0, stream>>>((const T*)A, (const T*)W, (TC*)C, M, N, K, lda, ldw, ldc);
+    launch_kernel(gemm_simt_kernel<T, TC, 4>, grid, dim3(THREADS), 0, stream, (const T*)A, (const T*)W, (TC*)C, M, N, K, lda, ldw, ldc);
   else
-    gemm_simt_kernel<T, TC, 1><<<grid, THREADS, 0, stream>>>((const T*)A, (const T*)W, (TC*)C, M, N, K, lda, ldw, ldc);
+    launch_kernel(gemm_simt_kernel<T, TC, 1>, grid, dim3(THREADS), 0, stream, (const T*)A, (const T*)W, (TC*)C, M, N, K, lda, ldw, ldc);
   LLMK_LAUNCH_CHECK("gemm_simt");
 }
 

@@ -74,7 +74,9 @@ constexpr int THREADS = 192;       // warp 0: TMA, warp 1: MMA + tensor memory, 
 constexpr int P_STAGE_BYTES = BP * BK * 2;
 
 __host__ __device__ constexpr int q_stage_bytes(int bnq) { return bnq * BK * 2; }
-__host__ __device__ constexpr int stages_for(int bnq) { return bnq >= 256 ? 4 : (bnq >= 128 ? 6 : 8); }
+// Narrow tiles keep the ring at six stages so that two CTAs fit on an SM: the CTAs of the next
+// product can then stage their weights while this one drains.
+__host__ __device__ constexpr int stages_for(int bnq) { return bnq >= 256 ? 4 : 6; }
 __host__ __device__ constexpr int smem_bytes_for(int bnq) {
   return stages_for(bnq) * (P_STAGE_BYTES + q_stage_bytes(bnq)) + 1024 /* alignment */ + 256 /* barriers */;
 }
@@ -129,20 +131,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  pdl_launch_dependents();
   if (warp == 0) {
     if (lane == 0) {
       // ---- producer: TMA loads into the ring ----
-      int issued = 0;
+      // The weights do not depend on earlier kernels: their tiles of the first pass over the
+      // ring are requested before waiting for the previous kernel, the activations after.
+      uint8_t* smem_w = SWAP ? smem_p : smem_q;
+      uint8_t* smem_a = SWAP ? smem_q : smem_p;
+      const CUtensorMap* map_w = SWAP ? &map_p : &map_q;
+      const CUtensorMap* map_a = SWAP ? &map_q : &map_p;
+      constexpr int W_STAGE = SWAP ? P_STAGE_BYTES : Q_STAGE_BYTES;
+      constexpr int A_STAGE = SWAP ? Q_STAGE_BYTES : P_STAGE_BYTES;
+      const int w0 = SWAP ? p0 : q0, a0 = SWAP ? q0 : p0;
+      const int pre = min(nkb, STAGES);
+      for (int i = 0; i < pre; ++i) {
+        mbar_arrive_expect_tx(&full_bar[i], P_STAGE_BYTES + Q_STAGE_BYTES);
+        tma_load_2d(smem_w + i * W_STAGE, map_w, (kb_begin + i) * BK, w0, &full_bar[i]);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem_a + i * A_STAGE, map_a, (kb_begin + i) * BK, a0, &full_bar[i]);
+      int issued = pre;
       bool ok = true;
-      for (int i = 0; i < nkb && ok; ++i) {
+      for (int i = pre; i < nkb && ok; ++i) {
         const int s = i % STAGES;
         const uint32_t phase = (i / STAGES) & 1;
         ok = mbar_wait(&empty_bar[s], phase ^ 1);
         if (!ok) break;
         mbar_arrive_expect_tx(&full_bar[s], P_STAGE_BYTES + Q_STAGE_BYTES);
         const int k = (kb_begin + i) * BK;
-        tma_load_2d(smem_p + s * P_STAGE_BYTES, &map_p, k, p0, &full_bar[s]);
-        tma_load_2d(smem_q + s * Q_STAGE_BYTES, &map_q, k, q0, &full_bar[s]);
+        tma_load_2d(smem_w + s * W_STAGE, map_w, k, w0, &full_bar[s]);
+        tma_load_2d(smem_a + s * A_STAGE, map_a, k, a0, &full_bar[s]);
         issued = i + 1;
       }
       if (!ok) {
@@ -301,7 +321,7 @@ int launch_cfg(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long 
   }
   const int p_rows = SWAP ? N : M, q_rows = SWAP ? M : N;
   dim3 grid((p_rows + BP - 1) / BP, (q_rows + BNQ - 1) / BNQ, splits);
-  kern<<<grid, THREADS, smem, stream>>>(mp, mq, (TOut*)C, ldc, split_stride, M, N, K, kb_per_split, g_err_flag);
+  launch_kernel(kern, grid, dim3(THREADS), (size_t)smem, stream, mp, mq, (TOut*)C, ldc, split_stride, M, N, K, kb_per_split, g_err_flag);
   LLMK_LAUNCH_CHECK("gemm_tc");
 }
 
@@ -375,6 +395,8 @@ LLMK_API int llmk_gemm_tc_take_error() {
 // out[m, n] = sum over s of partials[s][m][n], in the order s = 0, 1, ...
 template <typename TOut>
 __global__ void reduce_partials_kernel(TOut* __restrict__ out, const float* __restrict__ partials, size_t mn, int splits) {
+  pdl_wait();
+  pdl_launch_dependents();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < mn; i += (size_t)gridDim.x * blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < splits; ++s) acc += partials[(size_t)s * mn + i];
@@ -389,7 +411,7 @@ LLMK_API int llmk_reduce_partials(void* out, const float* partials, long long mn
   if (blocks > 148 * 8) blocks = 148 * 8;
   return dispatch_dtype(out_dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
-    reduce_partials_kernel<T><<<(int)blocks, 256, 0, stream>>>((T*)out, partials, (size_t)mn, splits);
+    launch_kernel(reduce_partials_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, partials, (size_t)mn, splits);
     LLMK_LAUNCH_CHECK("reduce_partials");
   });
 }

@@ -19,6 +19,27 @@ class KernelError(RuntimeError):
     pass
 
 
+class PartialSum:
+    """The result of a split-K product that has not been summed yet: float32
+    [splits, rows, cols] in the shared scratch buffer.  The kernels that take one sum it on
+    the fly, in the order of the splits.  It lives in one buffer per device and is valid only
+    until the next product runs: consume it first."""
+
+    def __init__(self, buf: torch.Tensor, splits: int, rows: int, cols: int, dtype: torch.dtype):
+        self.buf, self.splits, self.rows, self.cols, self.dtype = buf, splits, rows, cols, dtype
+
+    @property
+    def split_stride(self) -> int:
+        return self.rows * self.cols
+
+
+def _split_args(x):
+    """(direct pointer, partials pointer, splits, split stride) of a tensor, a PartialSum or None."""
+    if isinstance(x, PartialSum):
+        return c_void_p(0), c_void_p(x.buf.data_ptr()), c_int(x.splits), c_longlong(x.split_stride)
+    return _ptr(x), c_void_p(0), c_int(0), c_longlong(0)
+
+
 def _kind(dtype: torch.dtype) -> int:
     if dtype == torch.float32:
         return _F32
@@ -76,36 +97,45 @@ def embedding(resid: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, n_tok
 
 
 def add_rmsnorm(resid: torch.Tensor, delta, gamma: torch.Tensor, out, rows: int, eps: float) -> None:
-    """resid[:rows] += delta (if given); out[:rows] = rmsnorm(resid) * gamma (if out given)."""
+    """resid[:rows] += delta (a tensor or a PartialSum, if given); out[:rows] = rmsnorm(resid) * gamma
+    (if out given)."""
     assert resid.dtype == torch.float32 and gamma.dtype == torch.float32 and resid.is_contiguous()
     hidden = resid.shape[-1]
     ref = out if out is not None else delta
     if ref is None:
         return
-    if delta is not None:
+    if isinstance(delta, PartialSum):
+        assert delta.cols == hidden and delta.rows == rows
+    elif delta is not None:
         assert delta.is_contiguous() and delta.shape[-1] == hidden
     if out is not None:
         assert out.is_contiguous() and out.shape[-1] == hidden
         if delta is not None:
             assert delta.dtype == out.dtype
-    _check(load().llmk_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(gamma), _ptr(out), c_int(rows),
+    d, parts, splits, stride = _split_args(delta)
+    _check(load().llmk_add_rmsnorm(_ptr(resid), d, parts, splits, stride, _ptr(gamma), _ptr(out), c_int(rows),
                                    c_int(hidden), c_float(eps), c_int(_kind(ref.dtype)), _stream()))
 
 
 def gather_rows(out: torch.Tensor, resid: torch.Tensor, delta, rows: torch.Tensor, n_rows: int) -> None:
-    """out[r] = resid[rows[r]] (+ delta[rows[r]]), float32."""
+    """out[r] = resid[rows[r]] (+ delta[rows[r]], a tensor or a PartialSum), float32."""
     assert out.dtype == torch.float32 and resid.dtype == torch.float32 and rows.dtype == torch.int32
     kind = _kind(delta.dtype) if delta is not None else _F32
-    _check(load().llmk_gather_rows(_ptr(out), _ptr(resid), _ptr(delta), _ptr(rows), c_int(n_rows),
+    d, parts, splits, stride = _split_args(delta)
+    _check(load().llmk_gather_rows(_ptr(out), _ptr(resid), d, parts, splits, stride, _ptr(rows), c_int(n_rows),
                                    c_int(resid.shape[-1]), c_int(kind), _stream()))
 
 
-def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, rows: int) -> None:
-    """out[:rows, :I] = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+def silu_mul(out: torch.Tensor, gate_up, rows: int) -> None:
+    """out[:rows, :I] = silu(gate_up[:, :I]) * gate_up[:, I:]; gate_up a tensor or a PartialSum."""
     inter = out.shape[-1]
-    assert gate_up.shape[-1] == 2 * inter and out.is_contiguous() and gate_up.is_contiguous()
-    assert out.dtype == gate_up.dtype
-    _check(load().llmk_silu_mul(_ptr(out), _ptr(gate_up), c_int(rows), c_int(inter),
+    assert out.is_contiguous() and out.dtype == gate_up.dtype
+    if isinstance(gate_up, PartialSum):
+        assert gate_up.cols == 2 * inter and gate_up.rows == rows
+    else:
+        assert gate_up.shape[-1] == 2 * inter and gate_up.is_contiguous()
+    d, parts, splits, stride = _split_args(gate_up)
+    _check(load().llmk_silu_mul(_ptr(out), d, parts, splits, stride, c_int(rows), c_int(inter),
                                 c_int(_kind(out.dtype)), _stream()))
 
 
@@ -119,22 +149,38 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int) ->
                                  c_int(_kind(a.dtype)), c_int(_kind(out.dtype)), _stream()))
 
 
-def rope_kv_write(qkv: torch.Tensor, cos, sin, positions: torch.Tensor, slot_map: torch.Tensor,
-                  k_pages: torch.Tensor, v_pages: torch.Tensor, n_tokens: int, n_heads: int, n_kv: int,
-                  head_dim: int) -> None:
-    """Rotate q (in place) and k by the tables, store k and v at slot_map in the pages."""
-    _rows_contig(qkv, "qkv")
-    assert k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == qkv.dtype
+def rope_kv_write(qkv, cos, sin, positions: torch.Tensor, slot_map: torch.Tensor,
+                  k_pages, v_pages, n_tokens: int, n_heads: int, n_kv: int,
+                  head_dim: int, q_out=None) -> torch.Tensor:
+    """Rotate q and k by the tables, store k and v at slot_map in the pages.  qkv is a tensor
+    [T, >= (n_heads + 2 n_kv) head_dim] (q is then rotated in place unless q_out is given) or a
+    PartialSum of that shape (q_out is then required).  Returns the tensor that holds rotated q."""
     assert positions.dtype == torch.int32 and slot_map.dtype == torch.int32
-    assert k_pages.shape[3] == head_dim and (n_kv == 0 or k_pages.shape[1] == n_kv)
-    assert qkv.shape[1] >= (n_heads + 2 * n_kv) * head_dim
+    if isinstance(qkv, PartialSum):
+        assert q_out is not None and qkv.cols >= (n_heads + 2 * n_kv) * head_dim
+        src_stride = qkv.cols
+    else:
+        _rows_contig(qkv, "qkv")
+        assert qkv.shape[1] >= (n_heads + 2 * n_kv) * head_dim
+        src_stride = qkv.stride(0)
+        if q_out is None:
+            q_out = qkv
+    _rows_contig(q_out, "q_out")
+    assert q_out.dtype == qkv.dtype
+    if n_kv:
+        assert k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == qkv.dtype
+        assert k_pages.shape[3] == head_dim and k_pages.shape[1] == n_kv
+    page = k_pages.shape[2] if k_pages is not None else 1
     if cos is not None:
         assert cos.dtype == torch.float32 and sin.dtype == torch.float32
         assert cos.shape[1] == head_dim // 2 and cos.is_contiguous() and sin.is_contiguous()
-    _check(load().llmk_rope_kv_write(_ptr(qkv), c_longlong(qkv.stride(0)), _ptr(cos), _ptr(sin),
+    d, parts, splits, stride = _split_args(qkv)
+    _check(load().llmk_rope_kv_write(d, parts, splits, stride, c_longlong(src_stride), _ptr(q_out),
+                                     c_longlong(q_out.stride(0)), _ptr(cos), _ptr(sin),
                                      _ptr(positions), _ptr(slot_map), _ptr(k_pages), _ptr(v_pages),
                                      c_int(n_tokens), c_int(n_heads), c_int(n_kv), c_int(head_dim),
-                                     c_int(k_pages.shape[2]), c_int(_kind(qkv.dtype)), _stream()))
+                                     c_int(page), c_int(_kind(qkv.dtype)), _stream()))
+    return q_out
 
 
 def paged_attention_generic(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -227,14 +273,15 @@ def _ceil_div(a: int, b: int) -> int:
     return -(-a // b)
 
 
-def plan_gemm(M: int, N: int, K: int):
+def plan_gemm(M: int, N: int, K: int, fused_reduce: bool = False):
     """(swap, tile, splits, k-blocks per split) for the tensor-core product.
 
     Up to 128 rows the weights take the 128-row side of the MMA and the rows become its N
     (16 to 128); above that the rows take the 128-row side and the tile is 128 or 256 weight
     rows wide.  K (in blocks of 64) is split over CTAs when there are too few tiles to keep
-    all SMs streaming; the cost model counts k-blocks per CTA plus a fixed per-CTA cost,
-    times the number of waves."""
+    all SMs streaming.  The estimate, in microseconds: per CTA a fixed cost plus, per k-block,
+    the larger of its tensor-core time and its share of HBM time; times the number of waves;
+    plus what summing the partial results costs (less when the consumer sums them itself)."""
     kb = _ceil_div(K, 64)
     if M <= 128:
         options = [(True, 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128, _ceil_div(N, 128))]
@@ -242,7 +289,9 @@ def plan_gemm(M: int, N: int, K: int):
         options = [(False, t, _ceil_div(M, 128) * _ceil_div(N, t)) for t in (256, 128)]
     best = None
     for swap, tile, tiles in options:
-        width = 1.0 if swap else tile / 128.0
+        t_mma = 128 * tile * 64 * 2 / 15.2e6                       # us per k-block at one SM's tensor peak
+        t_mem = (128 + tile) * 128 / 45e3 if swap else 0.0          # us per k-block at one SM's HBM share
+        t_kb = max(t_mma, t_mem)
         for s in range(1, min(kb, 32) + 1):
             per = _ceil_div(kb, s)
             if _ceil_div(kb, per) != s:
@@ -250,7 +299,10 @@ def plan_gemm(M: int, N: int, K: int):
             if s > 1 and s * M * N * 4 > _PARTIAL_BYTES:
                 break
             waves = _ceil_div(tiles * s, _SMS)
-            cost = waves * (per * width + 4.0) + (0.5 * s if s > 1 else 0.0)
+            cost = waves * (per * t_kb + 2.5)
+            if s > 1:
+                traffic = (2 * s + 1) * M * N * 4 / 4e6               # partials written and read back, us
+                cost += traffic + (0.5 if fused_reduce else 3.0)
             if best is None or cost < best[0] - 1e-9:
                 best = (cost, swap, tile, s, per)
     return best[1:]
@@ -273,26 +325,36 @@ def gemm_fast_available(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, row
                                               c_longlong(a.stride(0)), c_longlong(w.stride(0))))
 
 
-def gemm_fast(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, plan=None) -> None:
-    """out[:rows] = a[:rows] @ w.T on the tensor cores (bfloat16 in, float32 accumulation)."""
+def gemm_fast(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, plan=None, allow_partial: bool = False):
+    """out[:rows] = a[:rows] @ w.T on the tensor cores (bfloat16 in, float32 accumulation).
+    Returns out; or, with allow_partial and a split-K plan, a PartialSum that the caller hands to
+    a kernel that sums it (out is then not written)."""
     _rows_contig(a, "a"); _rows_contig(w, "w"); _rows_contig(out, "out")
     n, k = w.shape
     assert a.shape[1] == k and out.shape[1] == n
-    swap, tile, splits, per = plan or plan_gemm(rows, n, k)
+    swap, tile, splits, per = plan or plan_gemm(rows, n, k, fused_reduce=allow_partial)
     lib = load()
     if splits == 1:
         _check(lib.llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
                                 c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
                                 c_int(_kind(out.dtype)), c_int(int(swap)), c_int(tile), c_int(1), c_int(per),
                                 _stream()))
-        return
-    assert out.is_contiguous()
+        return out
     part = _partials(a.device)
     _check(lib.llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(part), c_int(rows), c_int(n), c_int(k),
                             c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(n), c_int(_F32),
                             c_int(int(swap)), c_int(tile), c_int(splits), c_int(per), _stream()))
+    if allow_partial:
+        return PartialSum(part, splits, rows, n, out.dtype)
+    assert out.is_contiguous()
     _check(lib.llmk_reduce_partials(_ptr(out), _ptr(part), c_longlong(rows * n), c_int(splits),
                                     c_int(_kind(out.dtype)), _stream()))
+    return out
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch between the kernels of a step (on by default)."""
+    load().llmk_set_pdl(c_int(int(on)))
 
 
 def gemm_tc_take_error() -> int:

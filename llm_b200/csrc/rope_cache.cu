@@ -11,30 +11,34 @@
 namespace {
 
 template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long qkv_stride,
+__global__ void rope_kv_write_kernel(MaybePartial<T> src, long long src_stride, T* __restrict__ q_out,
+                                     long long q_out_stride,
                                      const float* __restrict__ cos_table, const float* __restrict__ sin_table,
                                      int rot_half, const int* __restrict__ positions,
                                      const int* __restrict__ slot_map, T* __restrict__ k_pages,
                                      T* __restrict__ v_pages, int n_heads, int n_kv, int head_dim,
                                      int page_size) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int slot = slot_map[t];
   const int page = slot / page_size, off = slot % page_size;
-  T* row = qkv + (size_t)t * qkv_stride;
+  const size_t row = (size_t)t * src_stride;
+  T* q_row = q_out + (size_t)t * q_out_stride;
   const int half = head_dim / 2;
   const float* cs = cos_table ? cos_table + (size_t)pos * rot_half : nullptr;
   const float* sn = cos_table ? sin_table + (size_t)pos * rot_half : nullptr;
   const int rot_items = (n_heads + n_kv) * half;
   for (int idx = threadIdx.x; idx < rot_items; idx += blockDim.x) {
     const int head = idx / half, i = idx % half;
-    T* h = row + (size_t)head * head_dim;
-    const float a = to_f32(h[i]), b = to_f32(h[i + half]);
+    const size_t h = row + (size_t)head * head_dim;
+    const float a = src.at(h + i), b = src.at(h + i + half);
     const float c = cs ? cs[i] : 1.f, s = cs ? sn[i] : 0.f;
     const T ya = from_f32<T>(a * c - b * s), yb = from_f32<T>(a * s + b * c);
     if (head < n_heads) {
-      h[i] = ya;
-      h[i + half] = yb;
+      q_row[(size_t)head * head_dim + i] = ya;
+      q_row[(size_t)head * head_dim + i + half] = yb;
     } else {
       const int g = head - n_heads;
       T* dst = k_pages + (((size_t)page * n_kv + g) * page_size + off) * head_dim;
@@ -42,29 +46,35 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long qkv_stride,
       dst[i + half] = yb;
     }
   }
-  const T* v = row + (size_t)(n_heads + n_kv) * head_dim;
+  const size_t v = row + (size_t)(n_heads + n_kv) * head_dim;
   for (int idx = threadIdx.x; idx < n_kv * head_dim; idx += blockDim.x) {
     const int g = idx / head_dim, d = idx % head_dim;
-    v_pages[(((size_t)page * n_kv + g) * page_size + off) * head_dim + d] = v[idx];
+    v_pages[(((size_t)page * n_kv + g) * page_size + off) * head_dim + d] = from_f32<T>(src.at(v + idx));
   }
 }
 
 }  // namespace
 
-// qkv [n_tokens, qkv_stride]: q heads, then k heads, then v heads in a row.  q is rotated in
-// place; rotated k and plain v go to the pages.  Tables are [max_position, head_dim/2]; without
-// tables (null) nothing is rotated and k, v are only stored.
-LLMK_API int llmk_rope_kv_write(void* qkv, long long qkv_stride, const float* cos_table,
+// A row of the source holds q heads, then k heads, then v heads; the source is qkv
+// [n_tokens, src_stride] of the element kind, or the float32 partial results
+// [splits][n_tokens][src_stride] of a split-K product.  Rotated q goes to q_out (which may be
+// the source itself: every pair is read and written by one thread), rotated k and plain v go
+// to the pages.  Tables are [max_position, head_dim/2]; without tables (null) nothing is
+// rotated and k, v are only stored.
+LLMK_API int llmk_rope_kv_write(const void* qkv, const float* partials, int splits, long long split_stride,
+                                long long src_stride, void* q_out, long long q_out_stride, const float* cos_table,
                                 const float* sin_table, const int* positions, const int* slot_map,
                                 void* k_pages, void* v_pages, int n_tokens, int n_heads, int n_kv,
                                 int head_dim, int page_size, int dtype, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   LLMK_REQUIRE(head_dim % 2 == 0, "rope_kv_write: head_dim %d must be even", head_dim);
+  LLMK_REQUIRE((qkv != nullptr) != (partials != nullptr), "rope_kv_write: give qkv or partials");
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
-    rope_kv_write_kernel<T><<<n_tokens, 128, 0, stream>>>((T*)qkv, qkv_stride, cos_table, sin_table,
-                                                         head_dim / 2, positions, slot_map, (T*)k_pages,
-                                                         (T*)v_pages, n_heads, n_kv, head_dim, page_size);
+    MaybePartial<T> src{(const T*)qkv, partials, splits, split_stride};
+    launch_kernel(rope_kv_write_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, src, src_stride, (T*)q_out,
+                  q_out_stride, cos_table, sin_table, head_dim / 2, positions, slot_map, (T*)k_pages, (T*)v_pages,
+                  n_heads, n_kv, head_dim, page_size);
     LLMK_LAUNCH_CHECK("rope_kv_write");
   });
 }

@@ -1,13 +1,16 @@
 // Row-wise kernels: embedding gather, residual add fused with RMSNorm, row gather
 // for the LM head, SiLU(gate) * up.  The residual stream is float32 in every mode;
-// sums, the reciprocal root and the scaling are float32 as well.
+// sums, the reciprocal root and the scaling are float32 as well.  An input that comes
+// from a split-K product may be given as its float32 partial results, which are summed
+// here in a fixed order instead of by a kernel of their own.
 #include <stdarg.h>
 #include <stdio.h>
 
 #include "common.cuh"
 
-// ---- error channel ----------------------------------------------------------
+// ---- error channel and switches ----------------------------------------------
 static thread_local char g_last_error[512] = "";
+static bool g_pdl = true;
 
 int llmk_fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -17,8 +20,12 @@ int llmk_fail(int code, const char* fmt, ...) {
   return code;
 }
 
+bool llmk_pdl_enabled() { return g_pdl; }
+
 LLMK_API const char* llmk_last_error() { return g_last_error; }
-LLMK_API int llmk_abi_version() { return 1; }
+LLMK_API int llmk_abi_version() { return 2; }
+// Programmatic dependent launch between the kernels of a step (on by default).
+LLMK_API void llmk_set_pdl(int on) { g_pdl = on != 0; }
 
 // ---- embedding --------------------------------------------------------------
 // resid[t, :] = table[ids[t], :]   (the reference copies rows without scaling,
@@ -27,6 +34,8 @@ template <typename T>
 __global__ void embedding_kernel(float* __restrict__ resid, const T* __restrict__ table,
                                  const int* __restrict__ ids, int hidden, int vocab,
                                  int* __restrict__ status) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int id = ids[t];
   if (id < 0 || id >= vocab) {
@@ -43,7 +52,7 @@ LLMK_API int llmk_embedding(float* resid, const void* table, const int* ids, int
   if (n_tokens == 0) return 0;
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
-    embedding_kernel<T><<<n_tokens, 256, 0, stream>>>(resid, (const T*)table, ids, hidden, vocab, status);
+    launch_kernel(embedding_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, resid, (const T*)table, ids, hidden, vocab, status);
     LLMK_LAUNCH_CHECK("embedding");
   });
 }
@@ -53,16 +62,19 @@ LLMK_API int llmk_embedding(float* resid, const void* table, const int* ids, int
 // The reference runs the add and the norm as two kernels (kernel/residual/Residual.h:17-19,
 // kernel/LayerNorm/RMSNorm.h:13-30,40-42); here they share one pass over the row.
 template <typename T>
-__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, MaybePartial<T> delta,
                                    const float* __restrict__ gamma, T* __restrict__ out, int hidden,
                                    float eps) {
   __shared__ float scratch[32];
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t base = (size_t)blockIdx.x * hidden;
+  const bool has_delta = delta.present();
   float ss = 0.f;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float v = resid[base + c];
-    if (delta) {
-      v += to_f32(delta[base + c]);
+    if (has_delta) {
+      v += delta.at(base + c);
       resid[base + c] = v;
     }
     ss += v * v;
@@ -75,31 +87,18 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
   }
 }
 
-LLMK_API int llmk_add_rmsnorm(float* resid, const void* delta, const float* gamma, void* out, int rows,
-                              int hidden, float eps, int dtype, cudaStream_t stream) {
+// delta: [rows, hidden] of the element kind, or null; partials: [splits][rows][hidden] float32
+// (split_stride elements apart), or null.  At most one of the two is given.
+LLMK_API int llmk_add_rmsnorm(float* resid, const void* delta, const float* partials, int splits,
+                              long long split_stride, const float* gamma, void* out, int rows, int hidden,
+                              float eps, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
+  LLMK_REQUIRE(!(delta && partials), "add_rmsnorm: give delta or partials, not both");
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
-    add_rmsnorm_kernel<T><<<rows, 256, 0, stream>>>(resid, (const T*)delta, gamma, (T*)out, hidden, eps);
+    MaybePartial<T> d{(const T*)delta, partials, splits, split_stride};
+    launch_kernel(add_rmsnorm_kernel<T>, dim3(rows), dim3(256), 0, stream, resid, d, gamma, (T*)out, hidden, eps);
     LLMK_LAUNCH_CHECK("add_rmsnorm");
-  });
-}
-
-// ---- residual add without a norm (the stream's pending term folded in) ------
-template <typename T>
-__global__ void add_kernel(float* __restrict__ resid, const T* __restrict__ delta, size_t n) {
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-    resid[i] += to_f32(delta[i]);
-}
-
-LLMK_API int llmk_add(float* resid, const void* delta, long long n, int dtype, cudaStream_t stream) {
-  if (n == 0) return 0;
-  return dispatch_dtype(dtype, [&](auto* tag) {
-    using T = LLMK_ELEM(tag);
-    int blocks = (int)((n + 255) / 256);
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    add_kernel<T><<<blocks, 256, 0, stream>>>(resid, (const T*)delta, (size_t)n);
-    LLMK_LAUNCH_CHECK("add");
   });
 }
 
@@ -108,21 +107,27 @@ LLMK_API int llmk_add(float* resid, const void* delta, long long n, int dtype, c
 // on every row (model/modules/Linear.h:25); gathering first leaves only wanted rows.
 template <typename T>
 __global__ void gather_rows_kernel(float* __restrict__ out, const float* __restrict__ resid,
-                                   const T* __restrict__ delta, const int* __restrict__ rows, int hidden) {
+                                   MaybePartial<T> delta, const int* __restrict__ rows, int hidden) {
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t src = (size_t)rows[blockIdx.x] * hidden, dst = (size_t)blockIdx.x * hidden;
+  const bool has_delta = delta.present();
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float v = resid[src + c];
-    if (delta) v += to_f32(delta[src + c]);
+    if (has_delta) v += delta.at(src + c);
     out[dst + c] = v;
   }
 }
 
-LLMK_API int llmk_gather_rows(float* out, const float* resid, const void* delta, const int* rows,
-                              int n_rows, int hidden, int dtype, cudaStream_t stream) {
+LLMK_API int llmk_gather_rows(float* out, const float* resid, const void* delta, const float* partials,
+                              int splits, long long split_stride, const int* rows, int n_rows, int hidden,
+                              int dtype, cudaStream_t stream) {
   if (n_rows == 0) return 0;
+  LLMK_REQUIRE(!(delta && partials), "gather_rows: give delta or partials, not both");
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
-    gather_rows_kernel<T><<<n_rows, 256, 0, stream>>>(out, resid, (const T*)delta, rows, hidden);
+    MaybePartial<T> d{(const T*)delta, partials, splits, split_stride};
+    launch_kernel(gather_rows_kernel<T>, dim3(n_rows), dim3(256), 0, stream, out, resid, d, rows, hidden);
     LLMK_LAUNCH_CHECK("gather_rows");
   });
 }
@@ -131,24 +136,28 @@ LLMK_API int llmk_gather_rows(float* out, const float* resid, const void* delta,
 // in [rows, 2*inter]: gate in the first half of a row, up in the second.
 // act = g / (1 + exp(-g)) * u in float32 (kernel/activation/SwiGLU.h:31-33).
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ in, int inter, size_t total) {
+__global__ void silu_mul_kernel(T* __restrict__ out, MaybePartial<T> in, int inter, size_t total) {
+  pdl_wait();
+  pdl_launch_dependents();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t r = i / inter, c = i % inter;
-    const float g = to_f32(in[r * 2 * inter + c]);
-    const float u = to_f32(in[r * 2 * inter + inter + c]);
+    const float g = in.at(r * 2 * inter + c);
+    const float u = in.at(r * 2 * inter + inter + c);
     out[i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
   }
 }
 
-LLMK_API int llmk_silu_mul(void* out, const void* gate_up, int rows, int inter, int dtype,
-                           cudaStream_t stream) {
+LLMK_API int llmk_silu_mul(void* out, const void* gate_up, const float* partials, int splits,
+                           long long split_stride, int rows, int inter, int dtype, cudaStream_t stream) {
   const size_t total = (size_t)rows * inter;
   if (total == 0) return 0;
+  LLMK_REQUIRE((gate_up != nullptr) != (partials != nullptr), "silu_mul: give gate_up or partials");
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     size_t blocks = (total + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
-    silu_mul_kernel<T><<<(int)blocks, 256, 0, stream>>>((T*)out, (const T*)gate_up, inter, total);
+    MaybePartial<T> in{(const T*)gate_up, partials, splits, split_stride};
+    launch_kernel(silu_mul_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, in, inter, total);
     LLMK_LAUNCH_CHECK("silu_mul");
   });
 }

@@ -17,6 +17,8 @@ sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, long
   __shared__ float vals[THREADS];
   __shared__ int idxs[THREADS];
   __shared__ float sums[THREADS];
+  pdl_wait();
+  pdl_launch_dependents();
   const int r = blockIdx.x, tid = threadIdx.x;
   const float* row = logits + (size_t)r * row_stride;
 
@@ -85,6 +87,6 @@ LLMK_API int llmk_sample_rows(int* out, const float* logits, long long row_strid
   if (rows == 0) return 0;
   LLMK_REQUIRE(vocab > 0 && row_stride >= vocab, "sample_rows: bad vocab %d / stride %lld", vocab, row_stride);
   LLMK_REQUIRE(temperature == nullptr || uniform != nullptr, "sample_rows: temperatures need uniforms");
-  sample_rows_kernel<<<rows, THREADS, 0, stream>>>(out, logits, row_stride, vocab, temperature, uniform);
+  launch_kernel(sample_rows_kernel, dim3(rows), dim3(THREADS), 0, stream, out, logits, row_stride, vocab, temperature, uniform);
   LLMK_LAUNCH_CHECK("sample_rows");
 }

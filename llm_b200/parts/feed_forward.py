@@ -36,10 +36,11 @@ class SwiGLU(Part):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         T, ws = ctx.n_tokens, ctx.workspace
-        gate_up = linear(x, self.w_gate_up, ws.get("gate_up", T, 2 * self.intermediate_size, self.dtype), T)
+        gate_up = linear(x, self.w_gate_up, ws.get("gate_up", T, 2 * self.intermediate_size, self.dtype), T,
+                         allow_partial=True)
         act = ws.get("ffn_act", T, self.intermediate_size, self.dtype)
         ops.silu_mul(act, gate_up, T)
-        return linear(act, self.w_down, ws.get("ffn_out", T, self.hidden_size, self.dtype), T)
+        return linear(act, self.w_down, ws.get("ffn_out", T, self.hidden_size, self.dtype), T, allow_partial=True)
 
 
 register_part("ffn", "swiglu", SwiGLU)

@@ -13,12 +13,15 @@ import torch
 from ..csrc import ops
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int) -> torch.Tensor:
-    """out[:rows] = x[:rows] @ weight.T; out may be float32 for bfloat16 inputs."""
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int, allow_partial: bool = False):
+    """out[:rows] = x[:rows] @ weight.T; out may be float32 for bfloat16 inputs.
+
+    With allow_partial the result may come back as an ops.PartialSum (a split-K product whose
+    partial results are still to be summed) instead of in `out`: pass it straight to a kernel
+    that takes one (add_rmsnorm, silu_mul, rope_kv_write, gather_rows), before any other product."""
     if rows == 0:
         return out
     if x.dtype == torch.bfloat16 and ops.gemm_fast_available(x, weight, out, rows):
-        ops.gemm_fast(x, weight, out, rows)
-    else:
-        ops.gemm_simt(x, weight, out, rows)
+        return ops.gemm_fast(x, weight, out, rows, allow_partial=allow_partial)
+    ops.gemm_simt(x, weight, out, rows)
     return out

@@ -320,3 +320,51 @@ def test_decode_attention_matches_the_general_kernel_and_plain(ops, dtype, NH, N
     ent = torch.arange(B, dtype=torch.int32, device=DEV)
     ops.paged_attention_generic(gen, q, kp, vp, bt, ent, kv_lens - 1, B, NH, NKV, HS, window, scale)
     assert rel_err(out, gen.double()) < (2e-6 if dtype == torch.float32 else 1e-2)
+
+
+def test_consumers_sum_split_k_partials_themselves(ops):
+    """add_rmsnorm, silu_mul, gather_rows and rope_kv_write given the float32 partial results
+    of a split-K product give what they give for the summed tensor."""
+    torch.manual_seed(12)
+    rows, hidden, splits = 6, 200, 3
+    parts = torch.randn(splits, rows, hidden, device=DEV)
+    summed = parts.sum(0)
+    ps = ops.PartialSum(parts.reshape(-1), splits, rows, hidden, torch.bfloat16)
+    gain = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    r1 = torch.randn(rows, hidden, device=DEV)
+    r2 = r1.clone()
+    o1 = torch.zeros(rows, hidden, device=DEV, dtype=torch.bfloat16)
+    o2 = torch.zeros_like(o1)
+    ops.add_rmsnorm(r1, ps, gain, o1, rows, 1e-5)
+    ref_resid = r2.double() + summed.double()
+    assert rel_err(r1, ref_resid) < 1e-6
+    ref = ref_resid / torch.sqrt((ref_resid ** 2).mean(-1, keepdim=True) + 1e-5) * gain.double()
+    assert rel_err(o1, ref) < 1e-2
+    # gather
+    idx = torch.tensor([5, 0, 3], dtype=torch.int32, device=DEV)
+    g = torch.zeros(3, hidden, device=DEV)
+    ops.gather_rows(g, r2, ps, idx, 3)
+    assert rel_err(g, (r2.double() + summed.double())[idx.long()]) < 1e-6
+    # silu
+    inter = hidden // 2
+    act = torch.zeros(rows, inter, device=DEV, dtype=torch.bfloat16)
+    ops.silu_mul(act, ps, rows)
+    gg, uu = summed[:, :inter].double(), summed[:, inter:].double()
+    assert rel_err(act, gg / (1 + torch.exp(-gg)) * uu) < 1e-2
+    # rope + store: the partial source against the summed bf16 source
+    NH, NKV, HS, page = 3, 1, 40, 8
+    width = (NH + 2 * NKV) * HS
+    assert width == hidden
+    cos = torch.cos(torch.rand(16, HS // 2, device=DEV) * 6)
+    sin = torch.sqrt(1 - cos * cos)
+    pos = torch.arange(rows, dtype=torch.int32, device=DEV)
+    slot = torch.tensor([8, 9, 10, 3, 4, 5], dtype=torch.int32, device=DEV)
+    kp1 = torch.zeros(3, NKV, page, HS, device=DEV, dtype=torch.bfloat16); vp1 = torch.zeros_like(kp1)
+    kp2 = torch.zeros_like(kp1); vp2 = torch.zeros_like(kp1)
+    q1 = torch.zeros(rows, NH * HS, device=DEV, dtype=torch.bfloat16)
+    ops.rope_kv_write(ps, cos, sin, pos, slot, kp1, vp1, rows, NH, NKV, HS, q_out=q1)
+    src = summed.clone()          # float32 source through the same kernel, then compare in bf16 terms
+    q2 = torch.zeros(rows, NH * HS, device=DEV)
+    kp2f = torch.zeros(3, NKV, page, HS, device=DEV); vp2f = torch.zeros_like(kp2f)
+    ops.rope_kv_write(src, cos, sin, pos, slot, kp2f, vp2f, rows, NH, NKV, HS, q_out=q2)
+    assert rel_err(q1, q2) < 1e-2 and rel_err(kp1, kp2f) < 1e-2 and rel_err(vp1, vp2f) < 1e-2
