@@ -109,8 +109,15 @@ struct MaybePartial {
   __device__ __forceinline__ bool present() const { return direct != nullptr || parts != nullptr; }
   __device__ __forceinline__ float at(size_t idx) const {
     if (parts) {
+      // loads of four splits are issued together; the additions keep the order of the splits
       float a = 0.f;
-      for (int s = 0; s < splits; ++s) a += parts[(size_t)s * split_stride + idx];
+      int s = 0;
+      for (; s + 4 <= splits; s += 4) {
+        const float v0 = parts[(size_t)s * split_stride + idx], v1 = parts[(size_t)(s + 1) * split_stride + idx];
+        const float v2 = parts[(size_t)(s + 2) * split_stride + idx], v3 = parts[(size_t)(s + 3) * split_stride + idx];
+        a += v0; a += v1; a += v2; a += v3;
+      }
+      for (; s < splits; ++s) a += parts[(size_t)s * split_stride + idx];
       return a;
     }
     return to_f32(direct[idx]);

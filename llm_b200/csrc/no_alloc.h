@@ -16,7 +16,7 @@ extern "C" {
 #endif
 
 // Most scratch the static variant can use, in floats (4 MiB).  A call needs
-// n_entries * n_heads * splits * (head_dim + 2) floats.
+// 4096 + n_entries * n_heads * splits * (head_dim + 2) floats.
 #define LLMK_DECODE_STATIC_SCRATCH_FLOATS (1 << 20)
 
 // Same computation and arguments as llmk_paged_attention_decode, without the two scratch
@@ -28,10 +28,12 @@ extern "C" {
 //   that device current).  Make that first call before any stream capture.
 // * Sizes whose scratch would exceed LLMK_DECODE_STATIC_SCRATCH_FLOATS are refused with a
 //   negative return code and a message for llmk_last_error(); nothing is launched.
-// * All calls share the one array and it keeps the last call's contents.  Nothing in it has
-//   to start at zero: every range writes its slot before the merge reads it.  Two calls that
-//   overlap on the GPU (different streams, no ordering between them) race on the array; order
-//   them on one stream or with events.
+// * All calls share the one array and it keeps the last call's contents.  Only its first 4096
+//   words (arrival counters of the key ranges) have to be zero when a call starts: the array
+//   is zero when the library is loaded and every call sets the counters it used back to zero
+//   before it ends; the partial results behind them are written before they are read.  Two
+//   calls that overlap on the GPU (different streams, no ordering between them) race on the
+//   array; order them on one stream or with events.
 // Returns 0, a cudaError_t (> 0), or a negative code for refused arguments.
 int llmk_paged_attention_decode_static(void* out, long long out_stride, const void* q, long long q_stride,
                                        const void* k_pages, const void* v_pages, const int* block_table,

@@ -215,17 +215,20 @@ _ATTN_PARTIALS = {}
 
 
 def _attn_partials(device, n_floats: int) -> torch.Tensor:
+    """Scratch of the decode attention; zeroed, because its first words are arrival counters
+    that the kernel expects to be zero and leaves zero."""
     buf = _ATTN_PARTIALS.get(device)
     if buf is None or buf.numel() < n_floats:
-        buf = torch.empty(max(n_floats, 1 << 20), dtype=torch.float32, device=device)
+        buf = torch.zeros(max(n_floats, 1 << 20), dtype=torch.float32, device=device)
         _ATTN_PARTIALS[device] = buf
     return buf
 
 
 def decode_splits(n_entries: int, n_kv: int, max_keys: int) -> int:
-    """How many ranges the keys of one request are cut into: enough CTAs to fill the GPU,
-    no range shorter than 64 keys at the longest context, at most 32."""
-    return max(1, min(32, _ceil_div(max_keys, 64), (_SMS * 6) // max(1, n_entries * n_kv)))
+    """How many ranges the keys of one request are cut into: many short ranges while the batch
+    is small (the kernel is bound by latency then), no range shorter than one round of 32 keys
+    at the longest context, all CTAs resident at once (about five per SM), at most 64."""
+    return max(1, min(64, _ceil_div(max_keys, 32), (_SMS * 5) // max(1, n_entries * n_kv)))
 
 
 def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -239,14 +242,15 @@ def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Te
     page = k_pages.shape[2]
     if splits is None:
         splits = decode_splits(n_entries, n_kv, block_table.shape[1] * page)
-    n_o = n_entries * n_heads * splits * head_dim
-    buf = _attn_partials(q.device, n_o + n_entries * n_heads * splits * 2)
-    _check(load().llmk_paged_attention_decode(
+    lib = load()
+    lib.llmk_paged_attention_decode_scratch.restype = c_longlong
+    need = lib.llmk_paged_attention_decode_scratch(c_int(n_entries), c_int(n_heads), c_int(head_dim), c_int(splits))
+    buf = _attn_partials(q.device, int(need))
+    _check(lib.llmk_paged_attention_decode(
         _ptr(out), c_longlong(out.stride(0)), _ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
         _ptr(block_table), c_int(block_table.shape[1]), _ptr(kv_lens), c_int(n_entries), c_int(n_heads),
         c_int(n_kv), c_int(head_dim), c_int(page), c_int(window or 0), c_float(scale), c_int(splits),
-        c_void_p(buf.data_ptr()), c_void_p(buf.data_ptr() + 4 * n_o), c_int(_kind(q.dtype)), _stream()))
-    count_launches(1)        # the split kernel and the merge are two launches
+        c_void_p(buf.data_ptr()), c_int(_kind(q.dtype)), _stream()))
 
 
 def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: int, head_dim: int,
@@ -255,8 +259,12 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
     n_heads * head_dim columns of qkv.  Chooses the kernel for the batch: the split-key
     decode kernel when every entry brings one token (bfloat16), else the general kernel."""
     if ctx.decode_only and qkv.dtype == torch.bfloat16:
+        max_keys = min(ctx.kv_bucket or 1 << 30, group.block_table.shape[1] * k_pages.shape[2])
+        if window:
+            max_keys = min(max_keys, window)
         paged_attention_decode(out, qkv, k_pages, v_pages, group.block_table, ctx.kv_lens, ctx.n_entries,
-                               n_heads, n_kv, head_dim, window, scale)
+                               n_heads, n_kv, head_dim, window, scale,
+                               splits=decode_splits(ctx.n_entries, n_kv, max_keys))
         return
     paged_attention_generic(out, qkv, k_pages, v_pages, group.block_table, ctx.token_entry, ctx.positions,
                             ctx.n_tokens, n_heads, n_kv, head_dim, window, scale)

@@ -82,6 +82,7 @@ class StepContext:
     groups: Dict[int, GroupView] = field(default_factory=dict)
     workspace: Workspace = None
     capturing: bool = False
+    kv_bucket: int = 0                         # longest request of the step, rounded up to 256 keys
 
     @property
     def max_entry_tokens(self) -> int:

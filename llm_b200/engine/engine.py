@@ -303,6 +303,7 @@ class Engine:
         ctx = self._ctx
         ctx.n_tokens, ctx.n_entries, ctx.n_logit_rows = n_tokens, B, n_rows
         ctx.host_entry_tokens, ctx.host_entry_start = entry_tokens, entry_start
+        ctx.kv_bucket = (int((entry_start + entry_tokens).max()) + 255) // 256 * 256
         return ctx
 
     def _next_host_buffer(self) -> torch.Tensor:
@@ -327,12 +328,12 @@ class Engine:
         if R:
             self._logit_buffers(R)
         # A step of single tokens has launch parameters that depend on the batch size alone
-        # (everything else is read from the metadata buffer), so it is captured once per
-        # (entries, rows) and replayed: the reference captures per GraphShape{batch, tokens}
+        # and on the bucket of the longest context (everything else is read from the metadata
+        # buffer), so it is captured once per (entries, rows, bucket) and replayed: the reference captures per GraphShape{batch, tokens}
         # the same way (runtime/LLM.h:63-72,192-201).
         graphable = (self.options.use_cuda_graphs and ctx.decode_only and R in (0, ctx.n_entries))
         if graphable:
-            key = (ctx.n_entries, R)
+            key = (ctx.n_entries, R, ctx.kv_bucket)     # kernels size their grids by the bucket
             entry = self._graphs.get(key)
             if entry is not None:
                 entry[0].replay()

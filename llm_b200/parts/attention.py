@@ -16,7 +16,7 @@ import torch
 
 from ..csrc import ops
 from .base import CacheNeed, ParamInfo, Part, build_part, register_part
-from .linear import linear
+from .linear import FUSE_PARTIALS, linear
 
 
 class PagedAttention(Part):
@@ -67,7 +67,7 @@ class PagedAttention(Part):
         T = ctx.n_tokens
         ws = ctx.workspace
         width = self.q_size + 2 * self.kv_size
-        qkv = linear(x, self.w_qkv, ws.get("qkv", T, width, self.dtype), T, allow_partial=True)
+        qkv = linear(x, self.w_qkv, ws.get("qkv", T, width, self.dtype), T, allow_partial=FUSE_PARTIALS)
         cos = sin = None
         if self.position is not None:
             cos, sin = self.position.tables()
@@ -79,7 +79,7 @@ class PagedAttention(Part):
         attn = ws.get("attn_out", T, self.q_size, self.dtype)
         ops.paged_attention(attn, q, k_pages, v_pages, view.group, ctx, self.num_heads,
                             k_pages.shape[1], self.head_dim, self.window or 0, self.scale)
-        return linear(attn, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=True)
+        return linear(attn, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
 
 
 register_part("mixer", "attention", PagedAttention)

@@ -10,7 +10,7 @@ import torch
 
 from ..csrc import ops
 from .base import ParamInfo, Part, register_part
-from .linear import linear
+from .linear import FUSE_PARTIALS, linear
 
 
 class SwiGLU(Part):
@@ -37,10 +37,10 @@ class SwiGLU(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         T, ws = ctx.n_tokens, ctx.workspace
         gate_up = linear(x, self.w_gate_up, ws.get("gate_up", T, 2 * self.intermediate_size, self.dtype), T,
-                         allow_partial=True)
+                         allow_partial=FUSE_PARTIALS)
         act = ws.get("ffn_act", T, self.intermediate_size, self.dtype)
         ops.silu_mul(act, gate_up, T)
-        return linear(act, self.w_down, ws.get("ffn_out", T, self.hidden_size, self.dtype), T, allow_partial=True)
+        return linear(act, self.w_down, ws.get("ffn_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
 
 
 register_part("ffn", "swiglu", SwiGLU)

@@ -13,6 +13,12 @@ import torch
 from ..csrc import ops
 
 
+# Whether the built-in parts hand split-K partial results to the next kernel instead of summing
+# them with a kernel of their own.  Measured on B200 at batch 8 the consumers (a few CTAs, one
+# per row) sum them more slowly than the wide reduction kernel does, so it is off.
+FUSE_PARTIALS = False
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int, allow_partial: bool = False):
     """out[:rows] = x[:rows] @ weight.T; out may be float32 for bfloat16 inputs.
 
