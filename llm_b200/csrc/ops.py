@@ -253,11 +253,42 @@ def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Te
         c_void_p(buf.data_ptr()), c_int(_kind(q.dtype)), _stream()))
 
 
+def attention_tc_supported(dtype, n_heads: int, n_kv: int, head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 attention takes these sizes (bfloat16, head size 64 or 128, pages
+    of 16 to 128 tokens, at most 128 query heads per kv head)."""
+    if dtype != torch.bfloat16:
+        return False
+    return bool(load().llmk_attention_tc_supported(c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(page_size)))
+
+
+def attention_tc(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                 block_table: torch.Tensor, cu_tokens: torch.Tensor, kv_lens: torch.Tensor, n_tokens: int,
+                 n_entries: int, n_heads: int, n_kv: int, head_dim: int, window: int, scale: float) -> None:
+    """Flash attention on the tensor cores for entries of any length: rows of entry e are
+    cu_tokens[e] .. cu_tokens[e+1], its keys (new tokens included) number kv_lens[e]."""
+    _rows_contig(out, "out"); _rows_contig(q, "q")
+    assert q.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert block_table.dim() == 2 and block_table.is_contiguous() and block_table.dtype == torch.int32
+    assert cu_tokens.dtype == torch.int32 and kv_lens.dtype == torch.int32
+    assert k_pages.is_contiguous() and v_pages.is_contiguous()
+    _check(load().llmk_attention_tc(
+        _ptr(out), c_longlong(out.stride(0)), _ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
+        c_int(k_pages.shape[0]), _ptr(block_table), c_int(block_table.shape[1]), _ptr(cu_tokens), _ptr(kv_lens),
+        c_int(n_tokens), c_int(n_entries), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(k_pages.shape[2]),
+        c_int(window or 0), c_float(scale), _stream()))
+
+
+def attention_tc_take_error() -> int:
+    """The code the tensor-core attention left when one of its bounded waits gave up (0 = none)."""
+    return int(load().llmk_attention_tc_take_error())
+
+
 def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: int, head_dim: int,
                     window: int, scale: float) -> None:
     """Attention of the step's tokens over their requests' pages; q is the first
-    n_heads * head_dim columns of qkv.  Chooses the kernel for the batch: the split-key
-    decode kernel when every entry brings one token (bfloat16), else the general kernel."""
+    n_heads * head_dim columns of qkv.  Chooses the kernel for the batch: in bfloat16 the
+    split-key decode kernel when every entry brings one token and the tcgen05 kernel otherwise,
+    where it takes the sizes; the general kernel for float32 and for all other sizes."""
     if ctx.decode_only and qkv.dtype == torch.bfloat16:
         max_keys = min(ctx.kv_bucket or 1 << 30, group.block_table.shape[1] * k_pages.shape[2])
         if window:
@@ -265,6 +296,10 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
         paged_attention_decode(out, qkv, k_pages, v_pages, group.block_table, ctx.kv_lens, ctx.n_entries,
                                n_heads, n_kv, head_dim, window, scale,
                                splits=decode_splits(ctx.n_entries, n_kv, max_keys))
+        return
+    if attention_tc_supported(qkv.dtype, n_heads, n_kv, head_dim, k_pages.shape[2]) and qkv.stride(0) % 8 == 0:
+        attention_tc(out, qkv, k_pages, v_pages, group.block_table, ctx.cu_tokens, ctx.kv_lens, ctx.n_tokens,
+                     ctx.n_entries, n_heads, n_kv, head_dim, window, scale)
         return
     paged_attention_generic(out, qkv, k_pages, v_pages, group.block_table, ctx.token_entry, ctx.positions,
                             ctx.n_tokens, n_heads, n_kv, head_dim, window, scale)

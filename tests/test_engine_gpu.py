@@ -9,7 +9,8 @@ from tiny import CONFIGS, TOL, load_plain_weights, make_model_dir, max_err, rand
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 40, 64, 97, 130], "C": [3, 50, 81, 120]}
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 40, 64, 97, 130], "C": [3, 50, 81, 120],
+           "D": [2, 129, 300, 47, 260], "E": [33, 290, 131, 380]}
 
 
 @pytest.fixture(scope="module")
@@ -30,7 +31,7 @@ def models(tmp_path_factory):
     return get
 
 
-def make_engine(model_dir, dtype, page, num_blocks, max_tokens=256, max_seqs=4):
+def make_engine(model_dir, dtype, page, num_blocks, max_tokens=512, max_seqs=4):
     from llm_b200.config import EngineOptions
     from llm_b200.engine.engine import Engine
     return Engine(model_dir, EngineOptions(dtype=dtype, kv_block_size=page, max_num_seqs=max_seqs,
@@ -49,7 +50,7 @@ def compare(got, ref, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_every_cut_matches_plain(models, name, dtype):
     d, cfg, page, reqs, ref = models(name, dtype)
     longest = max(len(t) for t in reqs.values())

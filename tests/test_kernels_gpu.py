@@ -368,3 +368,51 @@ def test_consumers_sum_split_k_partials_themselves(ops):
     kp2f = torch.zeros(3, NKV, page, HS, device=DEV); vp2f = torch.zeros_like(kp2f)
     ops.rope_kv_write(src, cos, sin, pos, slot, kp2f, vp2f, rows, NH, NKV, HS, q_out=q2)
     assert rel_err(q1, q2) < 1e-2 and rel_err(kp1, kp2f) < 1e-2 and rel_err(vp1, vp2f) < 1e-2
+
+
+@pytest.mark.parametrize("NH,NKV,HS,page,window", [(8, 1, 64, 16, 0), (32, 4, 64, 16, 0), (4, 2, 64, 32, 150), (3, 3, 64, 64, 0),
+                                                   (6, 2, 64, 16, 37), (2, 1, 128, 16, 0), (8, 2, 128, 32, 200), (5, 1, 128, 128, 0)])
+def test_tensor_core_attention_matches_the_general_kernel(ops, NH, NKV, HS, page, window):
+    """A ragged batch: a long prompt portion that starts deep in its request, short portions,
+    single tokens, shuffled pages; compared with the general kernel on the same cache."""
+    torch.manual_seed(13)
+    # (keys already cached, new tokens) per entry
+    plan = [(300, 150), (0, 37), (511, 1), (129, 1), (0, 1), (250, 6)]
+    B = len(plan)
+    total = [a + n for a, n in plan]
+    W = -(-max(total) // page) + 1
+    n_pages = sum(-(-t // page) for t in total) + 2
+    perm = torch.randperm(n_pages).tolist()
+    kp = (torch.randn(n_pages, NKV, page, HS, device=DEV)).to(torch.bfloat16)
+    vp = (torch.randn(n_pages, NKV, page, HS, device=DEV)).to(torch.bfloat16)
+    bt = torch.full((B, W), -1, dtype=torch.int32)
+    at = 0
+    for b, t in enumerate(total):
+        k = -(-t // page)
+        bt[b, :k] = torch.tensor(perm[at:at + k], dtype=torch.int32)
+        at += k
+    bt = bt.to(DEV)
+    T = sum(n for _, n in plan)
+    q = (torch.randn(T, NH * HS + 16, device=DEV) * 1.5).to(torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor([n for _, n in plan]).cumsum(0)), dtype=torch.int32, device=DEV)
+    kv_lens = torch.tensor(total, dtype=torch.int32, device=DEV)
+    pos = torch.cat([torch.arange(a, a + n) for a, n in plan]).to(torch.int32).to(DEV)
+    ent = torch.cat([torch.full((n,), i) for i, (_, n) in enumerate(plan)]).to(torch.int32).to(DEV)
+    scale = 1.0 / math.sqrt(HS)
+    assert ops.attention_tc_supported(torch.bfloat16, NH, NKV, HS, page)
+    out = torch.zeros(T, NH * HS, device=DEV, dtype=torch.bfloat16)
+    ops.attention_tc(out, q, kp, vp, bt, cu, kv_lens, T, B, NH, NKV, HS, window, scale)
+    torch.cuda.synchronize()
+    assert ops.attention_tc_take_error() == 0
+    ref = torch.zeros_like(out)
+    ops.paged_attention_generic(ref, q, kp, vp, bt.clamp_min(0), ent, pos, T, NH, NKV, HS, window, scale)
+    err_rows = (out.double() - ref.double()).abs().max(dim=1).values / ref.double().abs().max()
+    bad = torch.nonzero(err_rows > 1.2e-2)
+    assert bad.numel() == 0, f"first differing row {int(bad[0])} (entry {int(ent[int(bad[0])])}, pos {int(pos[int(bad[0])])}): {float(err_rows[int(bad[0])]):.3e}"
+
+
+def test_tensor_core_attention_refuses_other_sizes(ops):
+    assert not ops.attention_tc_supported(torch.bfloat16, 4, 2, 48, 16)
+    assert not ops.attention_tc_supported(torch.bfloat16, 4, 2, 64, 8)
+    assert not ops.attention_tc_supported(torch.float32, 4, 2, 64, 16)
+    assert not ops.attention_tc_supported(torch.bfloat16, 256, 1, 64, 16)

@@ -21,7 +21,19 @@ CONFIG_C = dict(architectures=["LlamaForCausalLM"], hidden_size=80, intermediate
                 vocab_size=301, rms_norm_eps=1e-4, rope_theta=1000.0, max_position_embeddings=192,
                 tie_word_embeddings=True, sliding_window=37, hidden_act="silu")
 
-CONFIGS = {"A": (CONFIG_A, 16), "B": (CONFIG_B, 8), "C": (CONFIG_C, 32)}   # name -> (config, page size)
+# D and E have sizes that the tensor-core kernels take (head size 64 / 128, rows of 16-byte
+# multiples), so the bfloat16 engine runs its tcgen05 products and attention on them.
+CONFIG_D = dict(architectures=["LlamaForCausalLM"], hidden_size=128, intermediate_size=344,
+                num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                vocab_size=520, rms_norm_eps=1e-5, rope_theta=20000.0, max_position_embeddings=512,
+                tie_word_embeddings=False, hidden_act="silu")
+CONFIG_E = dict(architectures=["LlamaForCausalLM"], hidden_size=96, intermediate_size=200,
+                num_hidden_layers=3, num_attention_heads=2, num_key_value_heads=1, head_dim=128,
+                vocab_size=333, rms_norm_eps=1e-6, rope_theta=300000.0, max_position_embeddings=400,
+                tie_word_embeddings=False, sliding_window=150, hidden_act="silu")
+
+CONFIGS = {"A": (CONFIG_A, 16), "B": (CONFIG_B, 8), "C": (CONFIG_C, 32),
+           "D": (CONFIG_D, 16), "E": (CONFIG_E, 32)}   # name -> (config, page size)
 
 
 def make_model_dir(tmp_root, name: str, dtype: str, seed: int = 1234, scale_far_key: bool = False) -> str:
