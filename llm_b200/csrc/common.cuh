@@ -98,6 +98,34 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Eight consecutive elements as float32 (two 16-byte loads of float32, one of bfloat16).
+template <typename T> struct Vec8;
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[2 * i] = __low2float(h[i]); v[2 * i + 1] = __high2float(h[i]); }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+
 // A value that is either an element of a tensor of T or the sum, in the order s = 0, 1, ...,
 // of `splits` float32 partial results laid out [split][row][col] (split-K products).
 template <typename T>
@@ -121,6 +149,24 @@ struct MaybePartial {
       return a;
     }
     return to_f32(direct[idx]);
+  }
+  // eight consecutive values starting at idx (idx a multiple of 8, the bases 16-byte aligned)
+  __device__ __forceinline__ void at8(size_t idx, float (&v)[8]) const {
+    if (parts) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+      for (int s = 0; s < splits; ++s) {
+        float t[8];
+        Vec8<float>::load(parts + (size_t)s * split_stride + idx, t);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += t[i];
+      }
+      return;
+    }
+    Vec8<T>::load(direct + idx, v);
+  }
+  __host__ bool vector_ok() const {
+    return ((uintptr_t)direct % 16 == 0) && ((uintptr_t)parts % 16 == 0) && (split_stride % 4 == 0);
   }
 };
 

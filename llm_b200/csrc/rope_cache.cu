@@ -10,7 +10,7 @@
 
 namespace {
 
-template <typename T>
+template <typename T, bool VEC>
 __global__ void rope_kv_write_kernel(MaybePartial<T> src, long long src_stride, T* __restrict__ q_out,
                                      long long q_out_stride,
                                      const float* __restrict__ cos_table, const float* __restrict__ sin_table,
@@ -29,6 +29,38 @@ __global__ void rope_kv_write_kernel(MaybePartial<T> src, long long src_stride, 
   const int half = head_dim / 2;
   const float* cs = cos_table ? cos_table + (size_t)pos * rot_half : nullptr;
   const float* sn = cos_table ? sin_table + (size_t)pos * rot_half : nullptr;
+  if (VEC) {
+    // eight pairs per thread: half is a multiple of 8 because head_dim is a multiple of 16
+    const int per_head = half / 8;
+    for (int idx = threadIdx.x; idx < (n_heads + n_kv) * per_head; idx += blockDim.x) {
+      const int head = idx / per_head, i = (idx % per_head) * 8;
+      const size_t h = row + (size_t)head * head_dim;
+      float a[8], b[8], c[8], s[8], ya[8], yb[8];
+      src.at8(h + i, a);
+      src.at8(h + i + half, b);
+      if (cs) {
+        Vec8<float>::load(cs + i, c);
+        Vec8<float>::load(sn + i, s);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { c[k] = 1.f; s[k] = 0.f; }
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { ya[k] = a[k] * c[k] - b[k] * s[k]; yb[k] = a[k] * s[k] + b[k] * c[k]; }
+      T* dst = head < n_heads ? q_row + (size_t)head * head_dim
+                              : k_pages + (((size_t)page * n_kv + (head - n_heads)) * page_size + off) * head_dim;
+      Vec8<T>::store(dst + i, ya);
+      Vec8<T>::store(dst + i + half, yb);
+    }
+    const size_t v = row + (size_t)(n_heads + n_kv) * head_dim;
+    for (int idx = threadIdx.x * 8; idx < n_kv * head_dim; idx += blockDim.x * 8) {
+      const int g = idx / head_dim, d = idx % head_dim;
+      float x[8];
+      src.at8(v + idx, x);
+      Vec8<T>::store(v_pages + (((size_t)page * n_kv + g) * page_size + off) * head_dim + d, x);
+    }
+    return;
+  }
   const int rot_items = (n_heads + n_kv) * half;
   for (int idx = threadIdx.x; idx < rot_items; idx += blockDim.x) {
     const int head = idx / half, i = idx % half;
@@ -72,7 +104,11 @@ LLMK_API int llmk_rope_kv_write(const void* qkv, const float* partials, int spli
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     MaybePartial<T> src{(const T*)qkv, partials, splits, split_stride};
-    launch_kernel(rope_kv_write_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, src, src_stride, (T*)q_out,
+    const bool vec = head_dim % 16 == 0 && src.vector_ok() && src_stride % 8 == 0 && q_out_stride % 8 == 0 &&
+                     (uintptr_t)q_out % 16 == 0 && (uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0 &&
+                     (uintptr_t)cos_table % 16 == 0 && (uintptr_t)sin_table % 16 == 0;
+    auto kern = vec ? rope_kv_write_kernel<T, true> : rope_kv_write_kernel<T, false>;
+    launch_kernel(kern, dim3(n_tokens), dim3(128), 0, stream, src, src_stride, (T*)q_out,
                   q_out_stride, cos_table, sin_table, head_dim / 2, positions, slot_map, (T*)k_pages, (T*)v_pages,
                   n_heads, n_kv, head_dim, page_size);
     LLMK_LAUNCH_CHECK("rope_kv_write");

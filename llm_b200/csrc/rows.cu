@@ -61,7 +61,7 @@ LLMK_API int llmk_embedding(float* resid, const void* table, const int* ids, int
 // resid += delta (if delta); out = resid * rsqrt(mean(resid^2) + eps) * gamma.
 // The reference runs the add and the norm as two kernels (kernel/residual/Residual.h:17-19,
 // kernel/LayerNorm/RMSNorm.h:13-30,40-42); here they share one pass over the row.
-template <typename T>
+template <typename T, bool VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, MaybePartial<T> delta,
                                    const float* __restrict__ gamma, T* __restrict__ out, int hidden,
                                    float eps) {
@@ -71,6 +71,42 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, MaybePartial<T> de
   const size_t base = (size_t)blockIdx.x * hidden;
   const bool has_delta = delta.present();
   float ss = 0.f;
+  if (VEC) {
+    // eight elements per thread and pass; a row of up to 8 * blockDim stays in registers
+    float keep[8];
+    const bool single = hidden <= 8 * (int)blockDim.x;
+    for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+      float v[8];
+      Vec8<float>::load(resid + base + c, v);
+      if (has_delta) {
+        float d[8];
+        delta.at8(base + c, d);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += d[i];
+        Vec8<float>::store(resid + base + c, v);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { ss += v[i] * v[i]; keep[i] = v[i]; }
+    }
+    const float total = block_sum(ss, scratch);
+    const float rstd = rsqrtf(total / (float)hidden + eps);
+    if (out) {
+      for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+        float v[8], g[8];
+        if (single) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = keep[i];
+        } else {
+          Vec8<float>::load(resid + base + c, v);
+        }
+        Vec8<float>::load(gamma + c, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = v[i] * rstd * g[i];
+        Vec8<T>::store(out + base + c, v);
+      }
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float v = resid[base + c];
     if (has_delta) {
@@ -97,7 +133,12 @@ LLMK_API int llmk_add_rmsnorm(float* resid, const void* delta, const float* part
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     MaybePartial<T> d{(const T*)delta, partials, splits, split_stride};
-    launch_kernel(add_rmsnorm_kernel<T>, dim3(rows), dim3(256), 0, stream, resid, d, gamma, (T*)out, hidden, eps);
+    const bool vec = hidden % 8 == 0 && d.vector_ok() && (uintptr_t)resid % 16 == 0 && (uintptr_t)gamma % 16 == 0 &&
+                     (uintptr_t)out % 16 == 0;
+    if (vec)
+      launch_kernel(add_rmsnorm_kernel<T, true>, dim3(rows), dim3(256), 0, stream, resid, d, gamma, (T*)out, hidden, eps);
+    else
+      launch_kernel(add_rmsnorm_kernel<T, false>, dim3(rows), dim3(256), 0, stream, resid, d, gamma, (T*)out, hidden, eps);
     LLMK_LAUNCH_CHECK("add_rmsnorm");
   });
 }
@@ -135,10 +176,25 @@ LLMK_API int llmk_gather_rows(float* out, const float* resid, const void* delta,
 // ---- SiLU(gate) * up --------------------------------------------------------
 // in [rows, 2*inter]: gate in the first half of a row, up in the second.
 // act = g / (1 + exp(-g)) * u in float32 (kernel/activation/SwiGLU.h:31-33).
-template <typename T>
+template <typename T, bool VEC>
 __global__ void silu_mul_kernel(T* __restrict__ out, MaybePartial<T> in, int inter, size_t total) {
   pdl_wait();
   pdl_launch_dependents();
+  if (VEC) {
+    const unsigned per_row = inter / 8;
+    const size_t n_vec = total / 8;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
+      const size_t r = i / per_row;
+      const unsigned c = (unsigned)(i - r * per_row) * 8;
+      float g[8], u[8];
+      in.at8(r * 2 * inter + c, g);
+      in.at8(r * 2 * inter + inter + c, u);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) g[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
+      Vec8<T>::store(out + r * inter + c, g);
+    }
+    return;
+  }
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t r = i / inter, c = i % inter;
     const float g = in.at(r * 2 * inter + c);
@@ -154,10 +210,14 @@ LLMK_API int llmk_silu_mul(void* out, const void* gate_up, const float* partials
   LLMK_REQUIRE((gate_up != nullptr) != (partials != nullptr), "silu_mul: give gate_up or partials");
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
-    size_t blocks = (total + 255) / 256;
-    if (blocks > 148 * 32) blocks = 148 * 32;
     MaybePartial<T> in{(const T*)gate_up, partials, splits, split_stride};
-    launch_kernel(silu_mul_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, in, inter, total);
+    const bool vec = inter % 8 == 0 && in.vector_ok() && (uintptr_t)out % 16 == 0;
+    size_t blocks = ((vec ? total / 8 : total) + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (vec)
+      launch_kernel(silu_mul_kernel<T, true>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, in, inter, total);
+    else
+      launch_kernel(silu_mul_kernel<T, false>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, in, inter, total);
     LLMK_LAUNCH_CHECK("silu_mul");
   });
 }

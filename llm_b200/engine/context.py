@@ -79,6 +79,7 @@ class StepContext:
     # host copies for planning (not read by kernels)
     host_entry_tokens: np.ndarray = None      # [entries] tokens per entry
     host_entry_start: np.ndarray = None       # [entries] first position of each entry
+    host_state_slots: np.ndarray = None       # [entries] state slot of each entry's request
     groups: Dict[int, GroupView] = field(default_factory=dict)
     workspace: Workspace = None
     capturing: bool = False

@@ -265,6 +265,7 @@ class Engine:
         B = len(entries)
         entry_tokens = np.zeros(B, dtype=np.int32)
         entry_start = np.zeros(B, dtype=np.int32)
+        entry_slots = np.zeros(B, dtype=np.int32)
         t0 = r0 = 0
         host[lay.cu_tokens] = 0
         for b, e in enumerate(entries):
@@ -290,7 +291,7 @@ class Engine:
             for w_ in e.want:
                 host[lay.logit_rows + r0] = t0 + w_
                 r0 += 1
-            entry_tokens[b], entry_start[b] = n, start
+            entry_tokens[b], entry_start[b], entry_slots[b] = n, start, cache.slot(e.request_id)
             t0 += n
         fresh = cache.take_fresh_slots()
         if fresh:
@@ -302,7 +303,7 @@ class Engine:
 
         ctx = self._ctx
         ctx.n_tokens, ctx.n_entries, ctx.n_logit_rows = n_tokens, B, n_rows
-        ctx.host_entry_tokens, ctx.host_entry_start = entry_tokens, entry_start
+        ctx.host_entry_tokens, ctx.host_entry_start, ctx.host_state_slots = entry_tokens, entry_start, entry_slots
         ctx.kv_bucket = (int((entry_start + entry_tokens).max()) + 255) // 256 * 256
         return ctx
 

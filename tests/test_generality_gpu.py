@@ -1,0 +1,164 @@
+"""The parts are general: a toy mixer with per-request state of its own, defined here, is
+registered, built and stepped without a change to the package; a layer order that names a
+layer twice and a layer that reads another layer's cache run through the same engine.  None of
+this is a model of the reference or of anyone: the plain computations are written out below."""
+import json
+import math
+import os
+
+import pytest
+import torch
+
+from tiny import TOL, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+# ---- a toy mixer with state: y_t = W * (mean of x_0..x_t) ---------------------------------
+def _register_toy():
+    from llm_b200.config.model_config import register_architecture
+    from llm_b200.models.spec import LayerSpec, ModelSpec, PartSpec
+    from llm_b200.parts.base import ParamInfo, Part, StateNeed, register_part
+    from llm_b200.parts.linear import linear
+
+    class RunningMeanMixer(Part):
+        role = "mixer"
+
+        def __init__(self, hidden_size, prefix="", dtype=None, device=None):
+            super().__init__(prefix, dtype, device)
+            self.hidden_size = hidden_size
+            self.w = None
+
+        def parameters(self):
+            return {self.name("mix.weight"): ParamInfo((self.hidden_size, self.hidden_size))}
+
+        def bind(self, tensors):
+            self.w = tensors[self.name("mix.weight")].contiguous()
+
+        def cache_need(self):
+            return None
+
+        def state_need(self):
+            return StateNeed((self.hidden_size + 1,), torch.float32)     # running sum and count
+
+        def forward(self, x, ctx, view):
+            T = ctx.n_tokens
+            means = torch.empty((T, self.hidden_size), dtype=torch.float32, device=x.device)
+            at = 0
+            for n, slot in zip(ctx.host_entry_tokens.tolist(), ctx.host_state_slots.tolist()):
+                st = view.state[slot]
+                sums = st[:-1] + torch.cumsum(x[at:at + n].float(), dim=0)
+                counts = st[-1] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+                means[at:at + n] = sums / counts[:, None]
+                st[:-1] = sums[-1]
+                st[-1] = counts[-1]
+                at += n
+            out = ctx.workspace.get("toy_out", T, self.hidden_size, self.dtype)
+            return linear(means.to(self.dtype).contiguous(), self.w, out, T)
+
+    register_part("mixer", "running_mean", RunningMeanMixer)
+
+    class ToyConfig:
+        def __init__(self, d):
+            self.d = d
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+    def build_spec(cfg):
+        d = cfg.d
+        H, V = d["hidden_size"], d["vocab_size"]
+        norm = lambda p: PartSpec("rmsnorm", {"size": H, "eps": d["eps"]}, p)
+        rope = PartSpec("rope", {"head_dim": d["head_dim"], "theta": 5000.0, "max_position": d["max_position"]})
+        layers = []
+        for i, kind in enumerate(d["mixers"]):
+            p = f"toy.layers.{i}"
+            if kind == "mean":
+                mixer = PartSpec("running_mean", {"hidden_size": H}, p + ".mixer")
+                cache_of = None
+            else:
+                shares = kind.startswith("share:")
+                mixer = PartSpec("attention", {"hidden_size": H, "num_heads": d["heads"], "num_kv_heads": d["kv_heads"],
+                                               "head_dim": d["head_dim"], "position": rope,
+                                               "window": d.get("window") if kind == "window" else None,
+                                               "shares_cache": shares}, p + ".attn")
+                cache_of = int(kind.split(":")[1]) if shares else None
+            ffn = PartSpec("swiglu", {"hidden_size": H, "intermediate_size": d["inter"]}, p + ".ffn")
+            layers.append(LayerSpec("prenorm", {"norm1": norm(p + ".n1"), "mixer": mixer, "norm2": norm(p + ".n2"),
+                                                "ffn": ffn}, cache_of=cache_of))
+        return ModelSpec(hidden_size=H, vocab_size=V, max_position=d["max_position"],
+                         embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, "toy.embed"),
+                         layers=tuple(layers), order=tuple(d["order"]), final_norm=norm("toy.norm"),
+                         head=PartSpec("lm_head", {"hidden_size": H, "vocab_size": V}, "toy.head"))
+
+    register_architecture("ToyForTest", ToyConfig, build_spec)
+
+
+TOY = dict(architectures=["ToyForTest"], hidden_size=48, vocab_size=97, eps=1e-5, head_dim=16, heads=3, kv_heads=1,
+           inter=80, max_position=128, window=9,
+           # layer 0: attention; 1: the toy mixer; 2: windowed attention; 3: attention that reads layer 0's cache
+           mixers=["full", "mean", "window", "share:0"],
+           order=[0, 1, 2, 3, 1, 0])           # layers 1 and 0 run twice
+
+
+def plain_toy(cfg, w, ids):
+    """Whole sequence, float64, no cache; every occurrence of a layer in the order keeps keys of
+    its own, and the sharing layer attends over the keys of layer 0's latest earlier run."""
+    import plain_llama as pl
+    H, HS, NH, NKV = cfg["hidden_size"], cfg["head_dim"], cfg["heads"], cfg["kv_heads"]
+    T = len(ids)
+    f = lambda n: w[n].double()
+    x = f("toy.embed.weight")[torch.tensor(ids)]
+    cos, sin = pl.rope_tables(list(range(T)), HS, 5000.0)
+    latest_kv = {}
+    for li in cfg["order"]:
+        p = f"toy.layers.{li}"
+        kind = cfg["mixers"][li]
+        n = pl.rmsnorm(x, f(p + ".n1.weight"), cfg["eps"])
+        if kind == "mean":
+            means = torch.cumsum(n, 0) / torch.arange(1, T + 1, dtype=torch.float64)[:, None]
+            a = means @ f(p + ".mixer.mix.weight").T
+        else:
+            q = pl.apply_rope((n @ f(p + ".attn.q_proj.weight").T).view(T, NH, HS), cos, sin)
+            if kind.startswith("share:"):
+                k, v = latest_kv[int(kind.split(":")[1])]
+            else:
+                k = pl.apply_rope((n @ f(p + ".attn.k_proj.weight").T).view(T, NKV, HS), cos, sin)
+                v = (n @ f(p + ".attn.v_proj.weight").T).view(T, NKV, HS)
+                latest_kv[li] = (k, v)
+            o = pl.attention(q, k, v, window=cfg["window"] if kind == "window" else None)
+            a = o.reshape(T, NH * HS) @ f(p + ".attn.o_proj.weight").T
+        x = x + a
+        m = pl.rmsnorm(x, f(p + ".n2.weight"), cfg["eps"])
+        x = x + pl.swiglu_mlp(m, {k_: v_ for k_, v_ in w.items()}, p + ".ffn")
+    return pl.rmsnorm(x, f("toy.norm.weight"), cfg["eps"]) @ f("toy.head.weight").T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_repeated_layers_and_shared_cache(tmp_path, dtype):
+    import replay
+    from llm_b200.config import EngineOptions
+    from llm_b200.engine.engine import Engine
+    from llm_b200.weights.loader import write_random_model
+    from tiny import load_plain_weights
+    _register_toy()
+    d = write_random_model(str(tmp_path / "toy"), TOY, 11, dtype)
+    w = load_plain_weights(d)
+    # ffn tensors follow the swiglu part's names under the toy prefix
+    w_ffn = {k.replace(".ffn.", ".ffn."): v for k, v in w.items()}
+    reqs = {f"t{i}": random_tokens(n, TOY["vocab_size"], 300 + i) for i, n in enumerate([4, 31, 19, 50])}
+    ref = {rid: plain_toy(TOY, w_ffn, toks) for rid, toks in reqs.items()}
+    eng = Engine(d, EngineOptions(dtype=dtype, kv_block_size=8, max_num_seqs=4, max_num_batched_tokens=64,
+                                  num_kv_blocks=24, use_cuda_graphs=False))
+    model = eng.model
+    assert len(model.state_needs) == 2                      # the toy layer runs twice: two states
+    assert len(model.cache_instances) == 3                  # layer 0 twice, layer 2 once, none for the sharer
+    assert sorted(set(model.group_keys)) == [("full", None), ("window", 9)]
+    for what, steps in (("whole", replay.steps_whole(reqs)), ("portions", replay.steps_portions(reqs)),
+                        ("tail", replay.steps_tail_decode(reqs, tail=6)), ("mixed", replay.steps_mixed(reqs))):
+        got = replay.run_steps(eng, steps)
+        for rid in reqs:
+            err = float((got[rid].double() - ref[rid]).abs().max() / ref[rid].abs().max())
+            assert err < TOL[dtype], (what, rid, err)
+        eng.cache.check()
