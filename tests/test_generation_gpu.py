@@ -1,0 +1,126 @@
+"""Generation through the Python entry point and the command line: long decoding, the first
+tokens of a sequence, temperature sampling against the plain sampler, running out of pages,
+CUDA graphs on and off."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_llama as pl
+from tiny import CONFIGS, TOL, load_plain_weights, make_model_dir, random_tokens
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("gen")
+    return lambda name, dtype: make_model_dir(root, name, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_long_decode_and_first_tokens(folders, name, dtype):
+    """Three prompt tokens, then 180 tokens decoded one by one across many pages; every step's
+    logits against the plain implementation, the first positions included."""
+    from llm_b200.config import EngineOptions
+    from llm_b200.engine.engine import Engine, StepEntry
+    cfg, page = CONFIGS[name]
+    d = folders(name, dtype)
+    w = load_plain_weights(d)
+    toks = random_tokens(183, cfg["vocab_size"], 77)
+    ref = pl.forward(cfg, w, toks)
+    eng = Engine(d, EngineOptions(dtype=dtype, kv_block_size=page, max_num_seqs=2, max_num_batched_tokens=64,
+                                  num_kv_blocks=-(-183 // page) + 1, use_cuda_graphs=True))
+    rows = [eng.step([StepEntry("x", toks[:3], [0, 1, 2])]).double().cpu().clone()]
+    for t in toks[3:]:
+        rows.append(eng.step([StepEntry("x", [t], [0])]).double().cpu().clone())
+    got = torch.cat(rows)
+    err = (got - ref).abs().max(dim=1).values / ref.abs().max()
+    bad = torch.nonzero(err > TOL[dtype])
+    assert bad.numel() == 0, f"first differing position {int(bad[0])}: {float(err[int(bad[0])]):.3e}"
+    assert eng.counters["graph_replays"] > 100
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_temperature_sampling_matches_plain_sampler(folders, dtype):
+    from llm_b200 import LLM
+    cfg, page = CONFIGS["B"]
+    d = folders("B", dtype)
+    w = load_plain_weights(d)
+    prompts = [random_tokens(n, cfg["vocab_size"], 900 + n) for n in (1, 40, 64, 97)]
+    llm = LLM(d, dtype=dtype, max_num_seqs=4, max_num_batched_tokens=24, kv_block_size=page, num_kv_blocks=64,
+              eos_token_id=-1)
+    got = llm.generate(prompts, max_new_tokens=12, temperature=0.8, seed=5)
+    again = llm.generate(prompts, max_new_tokens=12, temperature=0.8, seed=5)
+    other = llm.generate(prompts, max_new_tokens=12, temperature=0.8, seed=6)
+    assert got == again and got != other
+    for rid, (p, g) in enumerate(zip(prompts, got)):
+        ids = list(p)
+        for tok in g:
+            row = pl.forward(cfg, w, ids)[-1]
+            u = pl.uniform_for(5, rid, len(ids))
+            want = pl.sample_temperature(row, 0.8, u)
+            if tok != want:
+                # only a draw within rounding of a boundary of the cumulative distribution may differ
+                c = torch.cumsum(torch.softmax(row / 0.8, -1), -1)
+                edge = min(abs(u - float(c[min(tok, want)])), abs(u - float(c[max(tok, want) - 1])))
+                assert abs(tok - want) == 1 and edge < (1e-5 if dtype == "float32" else 2e-2), (rid, len(ids), tok, want)
+            ids.append(tok)
+
+
+def test_running_out_of_pages_preempts_and_still_matches(folders):
+    """A pool too small for all requests at once: decoding preempts and recomputes, and greedy
+    output still equals the plain implementation's."""
+    from llm_b200 import LLM
+    cfg, page = CONFIGS["A"]
+    d = folders("A", "float32")
+    w = load_plain_weights(d)
+    prompts = [random_tokens(n, cfg["vocab_size"], 40 + n) for n in (30, 29, 31, 12)]
+    llm = LLM(d, dtype="float32", max_num_seqs=4, max_num_batched_tokens=32, kv_block_size=page, num_kv_blocks=8,
+              eos_token_id=-1, use_cuda_graphs=False)
+    got = llm.generate(prompts, max_new_tokens=28)
+    assert llm.last_num_preemptions > 0
+    for p, g in zip(prompts, got):
+        assert g == pl.greedy_generate(cfg, w, p, 28)
+    llm.engine.cache.check()
+    assert llm.engine.cache.num_free_pages(0) == 8
+
+
+def test_cuda_graphs_change_nothing_and_eos_stops(folders):
+    from llm_b200 import LLM
+    cfg, page = CONFIGS["D"]
+    d = folders("D", "bfloat16")
+    prompts = [random_tokens(n, cfg["vocab_size"], 70 + n) for n in (9, 50, 3)]
+    a = LLM(d, dtype="bfloat16", max_num_seqs=4, max_num_batched_tokens=64, num_kv_blocks=40, eos_token_id=-1,
+            use_cuda_graphs=True).generate(prompts, max_new_tokens=20)
+    llm = LLM(d, dtype="bfloat16", max_num_seqs=4, max_num_batched_tokens=64, num_kv_blocks=40, eos_token_id=-1,
+              use_cuda_graphs=False)
+    b = llm.generate(prompts, max_new_tokens=20)
+    assert a == b
+    # stop at a token: the first request's fifth token as eos
+    eos = b[0][4]
+    first = b[0].index(eos)
+    llm2 = LLM(d, dtype="bfloat16", max_num_seqs=4, max_num_batched_tokens=64, num_kv_blocks=40, eos_token_id=eos,
+               use_cuda_graphs=False)
+    c = llm2.generate(prompts[:1], max_new_tokens=20)
+    assert c[0] == b[0][:first + 1]
+
+
+def test_command_line(folders, tmp_path):
+    d = folders("A", "float32")
+    w = load_plain_weights(d)
+    cfg, _ = CONFIGS["A"]
+    prompts = [[5, 17, 3, 200], [1, 2, 3, 4, 5, 6, 7, 8, 9]]
+    text = "\n".join(" ".join(str(t) for t in p) for p in prompts) + "\n"
+    proc = subprocess.run([sys.executable, "-m", "llm_b200", "--model", d, "--dtype", "float32", "--max-new-tokens", "6",
+                           "--eos-token-id", "-1", "--num-kv-blocks", "16", "--max-num-seqs", "2",
+                           "--max-num-batched-tokens", "16"], input=text, capture_output=True, text=True, cwd=ROOT,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = dict(l.split(": ") for l in proc.stdout.strip().split("\n"))
+    for i, p in enumerate(prompts):
+        assert [int(x) for x in lines[str(i)].split()] == pl.greedy_generate(cfg, w, p, 6)
