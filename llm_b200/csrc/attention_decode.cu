@@ -78,8 +78,8 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
   __shared__ long long row_s[SUB];
   __shared__ int last_s;
 
+  pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
-  pdl_launch_dependents();
   const int split = blockIdx.x, g = blockIdx.y, e = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = n_heads / n_kv;

@@ -59,8 +59,8 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
                                const int* __restrict__ positions, int n_tokens, int n_heads, int n_kv,
                                int head_dim, int page_size, int window, float scale) {
   __shared__ float q_s[WARPS][MAX_HEAD_DIM];
+  pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
-  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * WARPS + warp;
   if (item >= (long long)n_tokens * n_heads) return;

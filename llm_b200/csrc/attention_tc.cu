@@ -118,8 +118,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     prefetch_tensormap(&map_v);
   }
   if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
-  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     // which request and which of its tokens this tile covers
     int tile = blockIdx.x, entry = -1, t0 = 0, nt = 0, p0 = 0;

@@ -38,8 +38,8 @@ gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ W, TC* __restric
                  long long lda, long long ldw, long long ldc) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
+  pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
-  pdl_launch_dependents();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int lrow = tid >> 2, lk = (tid & 3) * 4;

@@ -88,7 +88,11 @@ __device__ __forceinline__ void store_one(TOut* p, float v) { *p = from_f32<TOut
 // error codes written to *err_flag: which wait gave up
 enum : int { ERR_PRODUCER = 1, ERR_MMA = 2, ERR_EPILOGUE = 3 };
 
-template <int BNQ, bool SWAP, typename TOut>
+// CLUSTER (swapped mode only): the CTAs that split K for one tile form a thread-block cluster
+// along blockIdx.z.  Instead of writing float32 partial results to global memory for a later
+// kernel to sum, each CTA hands its accumulator to the first CTA of the cluster through
+// distributed shared memory; that CTA adds them in the order of the splits and stores the result.
+template <int BNQ, bool SWAP, typename TOut, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                TOut* __restrict__ C, long long ldc, long long split_stride, int M, int N, int K,
@@ -114,6 +118,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   const int kb_end = min(total_kb, kb_begin + kblocks_per_split);
   const int nkb = max(0, kb_end - kb_begin);
   C += (long long)blockIdx.z * split_stride;
+  float acc[CLUSTER ? BNQ : 1];          // the accumulator row of an epilogue thread, kept across the cluster barriers
+  static_assert(!CLUSTER || (SWAP && BNQ <= 64), "cluster reduction is for the swapped mode with up to 64 rows");
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -202,8 +208,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     fence_after_sync();
     constexpr int CHUNK = BNQ >= 32 ? 32 : 16;
     const int p_limit = SWAP ? N : M, q_limit = SWAP ? M : N;
+    if (CLUSTER) {
+#pragma unroll
+      for (int c = 0; c < BNQ; c += CHUNK) {
+        if (nkb > 0 && ok) {
+          const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c;
+          if (CHUNK == 32) {
+            uint32_t r[32];
+            tmem_ld_x32(taddr, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < CHUNK; ++j) acc[(CLUSTER ? c : 0) + (CLUSTER ? j : 0)] = __uint_as_float(r[j]);
+          } else {
+            uint32_t r[16];
+            tmem_ld_x16(taddr, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < CHUNK; ++j) acc[(CLUSTER ? c : 0) + (CLUSTER ? j : 0)] = __uint_as_float(r[j]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < CHUNK; ++j) acc[(CLUSTER ? c : 0) + (CLUSTER ? j : 0)] = 0.f;
+        }
+      }
+    }
 #pragma unroll 1
-    for (int c = 0; c < BNQ; c += CHUNK) {
+    for (int c = 0; c < (CLUSTER ? 0 : BNQ); c += CHUNK) {
       float v[CHUNK];
       if (nkb > 0 && ok) {
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c;
@@ -260,6 +290,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     }
   }
 
+  if (CLUSTER) {
+    // Every MMA of every CTA of the cluster is done once all epilogue threads have passed their
+    // accumulator wait, so after the first barrier the stage ring is free to receive the sums.
+    const uint32_t rank = cluster_ctarank();
+    const int m_valid = min(BNQ, M - q0);
+    const int quad = warp & 3;
+    const int n_local = quad * 32 + lane;
+    cluster_sync();
+    if (warp >= 2 && rank != 0) {
+      const uint32_t slot = map_to_cta(smem_u32(smem), 0) + (uint32_t)(((rank - 1) * BNQ) * BP + n_local) * 4u;
+#pragma unroll
+      for (int m = 0; m < BNQ; ++m)
+        if (m < m_valid) st_cluster_f32(slot + (uint32_t)(m * BP) * 4u, acc[CLUSTER ? m : 0]);
+    }
+    cluster_sync();
+    if (warp >= 2 && rank == 0) {
+      const float* slots = reinterpret_cast<const float*>(smem);
+      const int n = p0 + n_local;
+#pragma unroll
+      for (int m = 0; m < BNQ; ++m) {
+        if (m < m_valid && n < N) {
+          float v = acc[CLUSTER ? m : 0];
+          for (int r = 0; r + 1 < (int)gridDim.z; ++r) v += slots[((size_t)r * BNQ + m) * BP + n_local];
+          store_one(C + (long long)(q0 + m) * ldc + n, v);
+        }
+      }
+    }
+  }
+
   fence_before_sync();
   __syncthreads();
   if (warp == 1) {
@@ -308,10 +367,10 @@ int ensure_err_flag() {
   return 0;
 }
 
-template <int BNQ, bool SWAP, typename TOut>
+template <int BNQ, bool SWAP, typename TOut, bool CLUSTER>
 int launch_cfg(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long ldc, long long split_stride, int M,
                int N, int K, int splits, int kb_per_split, cudaStream_t stream) {
-  auto kern = gemm_tc_kernel<BNQ, SWAP, TOut>;
+  auto kern = gemm_tc_kernel<BNQ, SWAP, TOut, CLUSTER>;
   constexpr int smem = smem_bytes_for(BNQ);
   static bool configured = false;
   if (!configured) {
@@ -321,27 +380,51 @@ int launch_cfg(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long 
   }
   const int p_rows = SWAP ? N : M, q_rows = SWAP ? M : N;
   dim3 grid((p_rows + BP - 1) / BP, (q_rows + BNQ - 1) / BNQ, splits);
-  launch_kernel(kern, grid, dim3(THREADS), (size_t)smem, stream, mp, mq, (TOut*)C, ldc, split_stride, M, N, K, kb_per_split, g_err_flag);
+  if (CLUSTER) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = llmk_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, kern, mp, mq, (TOut*)C, ldc, split_stride, M, N, K, kb_per_split, g_err_flag);
+  } else {
+    launch_kernel(kern, grid, dim3(THREADS), (size_t)smem, stream, mp, mq, (TOut*)C, ldc, split_stride, M, N, K, kb_per_split, g_err_flag);
+  }
   LLMK_LAUNCH_CHECK("gemm_tc");
 }
 
 template <typename TOut>
-int launch_out(bool swap, int bnq, const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long ldc,
+int launch_out(bool swap, int bnq, bool cluster, const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long ldc,
                long long split_stride, int M, int N, int K, int splits, int kbps, cudaStream_t s) {
-  if (swap) {
+  if (swap && cluster) {
     switch (bnq) {
-      case 16: return launch_cfg<16, true, TOut>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
-      case 32: return launch_cfg<32, true, TOut>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
-      case 64: return launch_cfg<64, true, TOut>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
-      case 128: return launch_cfg<128, true, TOut>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+      case 16: return launch_cfg<16, true, TOut, true>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+      case 32: return launch_cfg<32, true, TOut, true>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+      case 64: return launch_cfg<64, true, TOut, true>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+    }
+  } else if (swap) {
+    switch (bnq) {
+      case 16: return launch_cfg<16, true, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+      case 32: return launch_cfg<32, true, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+      case 64: return launch_cfg<64, true, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+      case 128: return launch_cfg<128, true, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
     }
   } else {
     switch (bnq) {
-      case 128: return launch_cfg<128, false, TOut>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
-      case 256: return launch_cfg<256, false, TOut>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+      case 128: return launch_cfg<128, false, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+      case 256: return launch_cfg<256, false, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
     }
   }
-  return llmk_fail(-1, "gemm_tc: no kernel for swap=%d tile=%d", (int)swap, bnq);
+  return llmk_fail(-1, "gemm_tc: no kernel for swap=%d tile=%d cluster=%d", (int)swap, bnq, (int)cluster);
 }
 
 }  // namespace
@@ -356,17 +439,25 @@ LLMK_API int llmk_gemm_tc_supported(const void* A, const void* W, int M, int N, 
 }
 
 // A [M,K] and W [N,K] bf16.  splits == 1: C (bf16 if out_dtype == 1, else float32) [M, ldc].
-// splits > 1: C must be float32 and is written as [splits][M][ldc] partial sums
+// splits > 1 without cluster: C must be float32 and is written as [splits][M][ldc] partial sums
 // (split_stride = M * ldc elements) over kblocks_per_split blocks of 64 along K each.
+// splits > 1 with cluster != 0 (swapped mode, tile up to 64, at most 8 splits): the splits of a
+// tile form a thread-block cluster, sum their results on chip and write C as for splits == 1.
 // swap != 0 puts the weights on the 128-row side of the MMA; tile is the other side's width.
 LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
                           long long ldc, int out_dtype, int swap, int tile, int splits, int kblocks_per_split,
-                          cudaStream_t stream) {
+                          int cluster, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   LLMK_REQUIRE(llmk_gemm_tc_supported(A, W, M, N, K, lda, ldw), "gemm_tc: K=%d and the row pitches must be multiples of 8 and the bases 16-byte aligned", K);
   LLMK_REQUIRE(splits >= 1 && kblocks_per_split >= 1 && (long long)splits * kblocks_per_split * BK >= K,
                "gemm_tc: %d splits of %d k-blocks do not cover K=%d", splits, kblocks_per_split, K);
-  LLMK_REQUIRE(splits == 1 || out_dtype == LLMK_F32, "gemm_tc: split-K needs a float32 output");
+  if (splits == 1) cluster = 0;
+  LLMK_REQUIRE(splits == 1 || cluster || out_dtype == LLMK_F32, "gemm_tc: split-K without a cluster needs a float32 output");
+  if (cluster) {
+    LLMK_REQUIRE(swap && tile <= 64 && splits <= 8, "gemm_tc: cluster reduction needs the swapped mode, a tile up to 64 and at most 8 splits");
+    LLMK_REQUIRE((long long)(splits - 1) * tile * BP * 4 <= (long long)stages_for(tile) * (P_STAGE_BYTES + q_stage_bytes(tile)),
+                 "gemm_tc: %d splits of a %d-row tile do not fit the stage ring for the on-chip sum", splits, tile);
+  }
   LLMK_REQUIRE(splits <= 65535, "gemm_tc: too many splits");
   int rc = ensure_err_flag();
   if (rc) return rc;
@@ -376,9 +467,9 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
   const int p_rows = swap ? N : M, q_rows = swap ? M : N;
   if ((rc = get_map(&mp, P, p_rows, K, ldp, BP))) return rc;
   if ((rc = get_map(&mq, Q, q_rows, K, ldq, tile))) return rc;
-  const long long split_stride = splits > 1 ? (long long)M * ldc : 0;
-  if (out_dtype == LLMK_F32) return launch_out<float>(swap != 0, tile, mp, mq, C, ldc, split_stride, M, N, K, splits, kblocks_per_split, stream);
-  if (out_dtype == LLMK_BF16) return launch_out<__nv_bfloat16>(swap != 0, tile, mp, mq, C, ldc, split_stride, M, N, K, splits, kblocks_per_split, stream);
+  const long long split_stride = (splits > 1 && !cluster) ? (long long)M * ldc : 0;
+  if (out_dtype == LLMK_F32) return launch_out<float>(swap != 0, tile, cluster != 0, mp, mq, C, ldc, split_stride, M, N, K, splits, kblocks_per_split, stream);
+  if (out_dtype == LLMK_BF16) return launch_out<__nv_bfloat16>(swap != 0, tile, cluster != 0, mp, mq, C, ldc, split_stride, M, N, K, splits, kblocks_per_split, stream);
   return llmk_fail(-1, "gemm_tc: unsupported output kind %d", out_dtype);
 }
 
@@ -395,8 +486,8 @@ LLMK_API int llmk_gemm_tc_take_error() {
 // out[m, n] = sum over s of partials[s][m][n], in the order s = 0, 1, ...
 template <typename TOut>
 __global__ void reduce_partials_kernel(TOut* __restrict__ out, const float* __restrict__ partials, size_t mn, int splits) {
+  pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
-  pdl_launch_dependents();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < mn; i += (size_t)gridDim.x * blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < splits; ++s) acc += partials[(size_t)s * mn + i];

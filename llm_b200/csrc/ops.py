@@ -316,15 +316,25 @@ def _ceil_div(a: int, b: int) -> int:
     return -(-a // b)
 
 
+_RING_BYTES = {16: 6 * (16384 + 2048), 32: 6 * (16384 + 4096), 64: 6 * (16384 + 8192)}
+
+
+def cluster_fits(tile: int, splits: int) -> bool:
+    """Whether the splits of a tile can sum their results on chip: swapped tiles up to 64 rows,
+    at most 8 CTAs in a cluster, and the partial rows must fit the first CTA's stage ring."""
+    return tile in _RING_BYTES and 2 <= splits <= 8 and (splits - 1) * tile * 128 * 4 <= _RING_BYTES[tile]
+
+
 def plan_gemm(M: int, N: int, K: int, fused_reduce: bool = False):
-    """(swap, tile, splits, k-blocks per split) for the tensor-core product.
+    """(swap, tile, splits, k-blocks per split, cluster) for the tensor-core product.
 
     Up to 128 rows the weights take the 128-row side of the MMA and the rows become its N
     (16 to 128); above that the rows take the 128-row side and the tile is 128 or 256 weight
     rows wide.  K (in blocks of 64) is split over CTAs when there are too few tiles to keep
-    all SMs streaming.  The estimate, in microseconds: per CTA a fixed cost plus, per k-block,
-    the larger of its tensor-core time and its share of HBM time; times the number of waves;
-    plus what summing the partial results costs (less when the consumer sums them itself)."""
+    all SMs streaming; where the shape allows it the splits of a tile form a cluster and sum
+    their results in shared memory, else they write float32 partial results for a later sum.
+    The estimate, in microseconds: per CTA a fixed cost plus, per k-block, the larger of its
+    tensor-core time and its share of HBM time; times the number of waves; plus the sum."""
     kb = _ceil_div(K, 64)
     if M <= 128:
         options = [(True, 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128, _ceil_div(N, 128))]
@@ -339,15 +349,21 @@ def plan_gemm(M: int, N: int, K: int, fused_reduce: bool = False):
             per = _ceil_div(kb, s)
             if _ceil_div(kb, per) != s:
                 continue
-            if s > 1 and s * M * N * 4 > _PARTIAL_BYTES:
+            # On-chip sums through a cluster measured slower at decode sizes than partial results plus
+            # a reduction kernel: a cluster needs all its CTAs scheduled at once, which takes away
+            # the early start of the next product's weight loads.  Kept as an option of gemm_fast.
+            cluster = False
+            if s > 1 and not cluster and s * M * N * 4 > _PARTIAL_BYTES:
                 break
             waves = _ceil_div(tiles * s, _SMS)
             cost = waves * (per * t_kb + 2.5)
-            if s > 1:
+            if cluster:
+                cost += 0.8
+            elif s > 1:
                 traffic = (2 * s + 1) * M * N * 4 / 4e6               # partials written and read back, us
                 cost += traffic + (0.5 if fused_reduce else 3.0)
             if best is None or cost < best[0] - 1e-9:
-                best = (cost, swap, tile, s, per)
+                best = (cost, swap, tile, s, per, cluster)
     return best[1:]
 
 
@@ -375,18 +391,20 @@ def gemm_fast(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, pl
     _rows_contig(a, "a"); _rows_contig(w, "w"); _rows_contig(out, "out")
     n, k = w.shape
     assert a.shape[1] == k and out.shape[1] == n
-    swap, tile, splits, per = plan or plan_gemm(rows, n, k, fused_reduce=allow_partial)
+    plan = plan or plan_gemm(rows, n, k, fused_reduce=allow_partial)
+    swap, tile, splits, per = plan[:4]
+    cluster = bool(plan[4]) if len(plan) > 4 else False
     lib = load()
-    if splits == 1:
+    if splits == 1 or cluster:
         _check(lib.llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
                                 c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
-                                c_int(_kind(out.dtype)), c_int(int(swap)), c_int(tile), c_int(1), c_int(per),
-                                _stream()))
+                                c_int(_kind(out.dtype)), c_int(int(swap)), c_int(tile), c_int(splits), c_int(per),
+                                c_int(int(cluster)), _stream()))
         return out
     part = _partials(a.device)
     _check(lib.llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(part), c_int(rows), c_int(n), c_int(k),
                             c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(n), c_int(_F32),
-                            c_int(int(swap)), c_int(tile), c_int(splits), c_int(per), _stream()))
+                            c_int(int(swap)), c_int(tile), c_int(splits), c_int(per), c_int(0), _stream()))
     if allow_partial:
         return PartialSum(part, splits, rows, n, out.dtype)
     assert out.is_contiguous()

@@ -18,8 +18,8 @@ __global__ void rope_kv_write_kernel(MaybePartial<T> src, long long src_stride, 
                                      const int* __restrict__ slot_map, T* __restrict__ k_pages,
                                      T* __restrict__ v_pages, int n_heads, int n_kv, int head_dim,
                                      int page_size) {
+  pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
-  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int slot = slot_map[t];

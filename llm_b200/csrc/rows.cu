@@ -34,8 +34,8 @@ template <typename T>
 __global__ void embedding_kernel(float* __restrict__ resid, const T* __restrict__ table,
                                  const int* __restrict__ ids, int hidden, int vocab,
                                  int* __restrict__ status) {
+  pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
-  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int id = ids[t];
   if (id < 0 || id >= vocab) {
@@ -66,8 +66,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, MaybePartial<T> de
                                    const float* __restrict__ gamma, T* __restrict__ out, int hidden,
                                    float eps) {
   __shared__ float scratch[32];
+  pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
-  pdl_launch_dependents();
   const size_t base = (size_t)blockIdx.x * hidden;
   const bool has_delta = delta.present();
   float ss = 0.f;
@@ -149,8 +149,8 @@ LLMK_API int llmk_add_rmsnorm(float* resid, const void* delta, const float* part
 template <typename T>
 __global__ void gather_rows_kernel(float* __restrict__ out, const float* __restrict__ resid,
                                    MaybePartial<T> delta, const int* __restrict__ rows, int hidden) {
+  pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
-  pdl_launch_dependents();
   const size_t src = (size_t)rows[blockIdx.x] * hidden, dst = (size_t)blockIdx.x * hidden;
   const bool has_delta = delta.present();
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
@@ -178,8 +178,8 @@ LLMK_API int llmk_gather_rows(float* out, const float* resid, const void* delta,
 // act = g / (1 + exp(-g)) * u in float32 (kernel/activation/SwiGLU.h:31-33).
 template <typename T, bool VEC>
 __global__ void silu_mul_kernel(T* __restrict__ out, MaybePartial<T> in, int inter, size_t total) {
+  pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
-  pdl_launch_dependents();
   if (VEC) {
     const unsigned per_row = inter / 8;
     const size_t n_vec = total / 8;

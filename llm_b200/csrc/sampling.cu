@@ -17,8 +17,8 @@ sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, long
   __shared__ float vals[THREADS];
   __shared__ int idxs[THREADS];
   __shared__ float sums[THREADS];
+  pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
-  pdl_launch_dependents();
   const int r = blockIdx.x, tid = threadIdx.x;
   const float* row = logits + (size_t)r * row_stride;
 

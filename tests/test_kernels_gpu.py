@@ -127,9 +127,11 @@ def test_gemm_tensor_core(ops, M, N, K, out_dtype):
     assert float(out[M:].float().min()) == 3.0
 
 
-@pytest.mark.parametrize("swap,tile,splits", [(True, 16, 1), (True, 16, 4), (True, 32, 2), (True, 64, 3), (True, 128, 1),
-                                              (False, 128, 1), (False, 256, 1), (False, 256, 2), (False, 128, 5)])
-def test_gemm_tensor_core_every_configuration(ops, swap, tile, splits):
+@pytest.mark.parametrize("swap,tile,splits,cluster", [
+    (True, 16, 1, False), (True, 16, 4, False), (True, 32, 2, False), (True, 64, 3, False), (True, 128, 1, False),
+    (False, 128, 1, False), (False, 256, 1, False), (False, 256, 2, False), (False, 128, 5, False),
+    (True, 16, 6, True), (True, 16, 2, True), (True, 32, 3, True), (True, 64, 3, True)])
+def test_gemm_tensor_core_every_configuration(ops, swap, tile, splits, cluster):
     torch.manual_seed(6)
     M = {16: 9, 32: 30, 64: 64, 128: 77}[tile] if swap else 200
     N, K = 392, 5 * 64 + 24
@@ -138,10 +140,14 @@ def test_gemm_tensor_core_every_configuration(ops, swap, tile, splits):
     out = torch.zeros(M, N, device=DEV)
     kb = -(-K // 64)
     per = -(-kb // splits)
-    ops.gemm_fast(a, w, out, M, plan=(swap, tile, -(-kb // per), per))
+    ops.gemm_fast(a, w, out, M, plan=(swap, tile, -(-kb // per), per, cluster))
     torch.cuda.synchronize()
     assert ops.gemm_tc_take_error() == 0
     assert rel_err(out, a.double() @ w.double().T) < 1e-5
+    if cluster:
+        out16 = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
+        ops.gemm_fast(a, w, out16, M, plan=(swap, tile, -(-kb // per), per, cluster))
+        assert rel_err(out16, a.double() @ w.double().T) < 1e-2
 
 
 def test_gemm_tensor_core_refuses_unaligned_rows(ops):
