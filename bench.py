@@ -121,6 +121,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)
     ap.add_argument("--no-points", action="store_true", help="skip prefill and the batch 1 / 64 points")
+    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"],
+                    help="decode / prefill: only that measurement, for small profiling runs (not the benchmark line)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -142,6 +144,8 @@ def main() -> int:
 
     peaks = load_peaks()
     cfg = dict(MODEL, num_hidden_layers=args.layers)
+    if args.mode != "all":
+        args.no_points = True
     max_batch = max(64, args.batch) if not args.no_points else args.batch
     t_load = time.time()
     llm = LLM(None, dtype="bfloat16", max_num_seqs=max_batch, max_num_batched_tokens=PREFILL_TOKENS,
@@ -189,6 +193,26 @@ def main() -> int:
            "n_gpus": 1, "steps": args.steps, "warmup": warmup, "higher_is_better": True, "scaling": "weak",
            "vs_baseline": None, "dtype": "bf16", "data": "synthetic: seeded random weights and token ids",
            "impl": "ours"}
+
+    if args.mode == "prefill":
+        reps = []
+        for k in range(max(3, args.steps)):
+            rid = f"p{k}"
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            eng.step([StepEntry(rid, prompt(PREFILL_TOKENS), [PREFILL_TOKENS - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            reps.append(a.elapsed_time(b))
+            eng.release(rid)
+        print(json.dumps({"mode": "prefill", "layers": args.layers, "tokens": PREFILL_TOKENS, "ms": reps}))
+        return 0
+    if args.mode == "decode":
+        ms, launches, _ = timed_decode(args.batch, args.steps, warmup)
+        print(json.dumps({"mode": "decode", "layers": args.layers, "batch": args.batch, "ms_per_step": ms,
+                          "launches_per_step": launches}))
+        return 0
 
     # ---- headline: decode at the default batch, device-timed ----
     sampler = ClockSampler()
