@@ -121,8 +121,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
   if (threadIdx.x == 0) {
-    // which request and which of its tokens this tile covers
-    int tile = blockIdx.x, entry = -1, t0 = 0, nt = 0, p0 = 0;
+    // which request and which of its tokens this tile covers; the tiles are handed out from the
+    // back, so that the late tokens of long prompts (the most key blocks) start first
+    int tile = (int)gridDim.x - 1 - (int)blockIdx.x, entry = -1, t0 = 0, nt = 0, p0 = 0;
     for (int e = 0; e < n_entries; ++e) {
       const int n_e = cu_tokens[e + 1] - cu_tokens[e];
       const int tiles_e = (n_e + tq - 1) / tq;

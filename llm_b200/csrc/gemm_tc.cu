@@ -96,11 +96,14 @@ template <int BNQ, bool SWAP, typename TOut, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                TOut* __restrict__ C, long long ldc, long long split_stride, int M, int N, int K,
-               int kblocks_per_split, int* __restrict__ err_flag) {
+               int kblocks_per_split, int tile_q, int* __restrict__ err_flag) {
+  // BNQ sizes the stages and the tensor memory; tile_q <= BNQ (a multiple of 32, or 16 = BNQ) is
+  // the width actually computed, chosen on the host so that the grid fills whole waves.
   constexpr int STAGES = stages_for(BNQ);
   constexpr int Q_STAGE_BYTES = q_stage_bytes(BNQ);
   constexpr uint32_t TMEM_COLS = tmem_cols_for(BNQ);
-  constexpr uint32_t IDESC = idesc_bf16_f32(BP, BNQ);
+  const uint32_t IDESC = idesc_bf16_f32(BP, tile_q);
+  const uint32_t stage_tx = (uint32_t)(P_STAGE_BYTES + tile_q * BK * 2);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -112,7 +115,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int p0 = blockIdx.x * BP, q0 = blockIdx.y * BNQ;
+  const int p0 = blockIdx.x * BP, q0 = blockIdx.y * tile_q;
   const int total_kb = (K + BK - 1) / BK;
   const int kb_begin = blockIdx.z * kblocks_per_split;
   const int kb_end = min(total_kb, kb_begin + kblocks_per_split);
@@ -152,7 +155,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
       const int w0 = SWAP ? p0 : q0, a0 = SWAP ? q0 : p0;
       const int pre = min(nkb, STAGES);
       for (int i = 0; i < pre; ++i) {
-        mbar_arrive_expect_tx(&full_bar[i], P_STAGE_BYTES + Q_STAGE_BYTES);
+        mbar_arrive_expect_tx(&full_bar[i], stage_tx);
         tma_load_2d(smem_w + i * W_STAGE, map_w, (kb_begin + i) * BK, w0, &full_bar[i]);
       }
       pdl_wait();
@@ -165,7 +168,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         const uint32_t phase = (i / STAGES) & 1;
         ok = mbar_wait(&empty_bar[s], phase ^ 1);
         if (!ok) break;
-        mbar_arrive_expect_tx(&full_bar[s], P_STAGE_BYTES + Q_STAGE_BYTES);
+        mbar_arrive_expect_tx(&full_bar[s], stage_tx);
         const int k = (kb_begin + i) * BK;
         tma_load_2d(smem_w + s * W_STAGE, map_w, k, w0, &full_bar[s]);
         tma_load_2d(smem_a + s * A_STAGE, map_a, k, a0, &full_bar[s]);
@@ -233,7 +236,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
       }
     }
 #pragma unroll 1
-    for (int c = 0; c < (CLUSTER ? 0 : BNQ); c += CHUNK) {
+    for (int c = 0; c < (CLUSTER ? 0 : tile_q); c += CHUNK) {
       float v[CHUNK];
       if (nkb > 0 && ok) {
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c;
@@ -369,7 +372,7 @@ int ensure_err_flag() {
 
 template <int BNQ, bool SWAP, typename TOut, bool CLUSTER>
 int launch_cfg(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long ldc, long long split_stride, int M,
-               int N, int K, int splits, int kb_per_split, cudaStream_t stream) {
+               int N, int K, int splits, int kb_per_split, int tile_q, cudaStream_t stream) {
   auto kern = gemm_tc_kernel<BNQ, SWAP, TOut, CLUSTER>;
   constexpr int smem = smem_bytes_for(BNQ);
   static bool configured = false;
@@ -379,7 +382,7 @@ int launch_cfg(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long 
     configured = true;
   }
   const int p_rows = SWAP ? N : M, q_rows = SWAP ? M : N;
-  dim3 grid((p_rows + BP - 1) / BP, (q_rows + BNQ - 1) / BNQ, splits);
+  dim3 grid((p_rows + BP - 1) / BP, (q_rows + tile_q - 1) / tile_q, splits);
   if (CLUSTER) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -395,9 +398,9 @@ int launch_cfg(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long 
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = llmk_pdl_enabled() ? 2 : 1;
-    cudaLaunchKernelEx(&cfg, kern, mp, mq, (TOut*)C, ldc, split_stride, M, N, K, kb_per_split, g_err_flag);
+    cudaLaunchKernelEx(&cfg, kern, mp, mq, (TOut*)C, ldc, split_stride, M, N, K, kb_per_split, tile_q, g_err_flag);
   } else {
-    launch_kernel(kern, grid, dim3(THREADS), (size_t)smem, stream, mp, mq, (TOut*)C, ldc, split_stride, M, N, K, kb_per_split, g_err_flag);
+    launch_kernel(kern, grid, dim3(THREADS), (size_t)smem, stream, mp, mq, (TOut*)C, ldc, split_stride, M, N, K, kb_per_split, tile_q, g_err_flag);
   }
   LLMK_LAUNCH_CHECK("gemm_tc");
 }
@@ -407,22 +410,20 @@ int launch_out(bool swap, int bnq, bool cluster, const CUtensorMap& mp, const CU
                long long split_stride, int M, int N, int K, int splits, int kbps, cudaStream_t s) {
   if (swap && cluster) {
     switch (bnq) {
-      case 16: return launch_cfg<16, true, TOut, true>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
-      case 32: return launch_cfg<32, true, TOut, true>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
-      case 64: return launch_cfg<64, true, TOut, true>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+      case 16: return launch_cfg<16, true, TOut, true>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, bnq, s);
+      case 32: return launch_cfg<32, true, TOut, true>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, bnq, s);
+      case 64: return launch_cfg<64, true, TOut, true>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, bnq, s);
     }
   } else if (swap) {
     switch (bnq) {
-      case 16: return launch_cfg<16, true, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
-      case 32: return launch_cfg<32, true, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
-      case 64: return launch_cfg<64, true, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
-      case 128: return launch_cfg<128, true, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
+      case 16: return launch_cfg<16, true, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, bnq, s);
+      case 32: return launch_cfg<32, true, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, bnq, s);
+      case 64: return launch_cfg<64, true, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, bnq, s);
+      case 128: return launch_cfg<128, true, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, bnq, s);
     }
-  } else {
-    switch (bnq) {
-      case 128: return launch_cfg<128, false, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
-      case 256: return launch_cfg<256, false, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, s);
-    }
+  } else if (bnq % 32 == 0 && bnq >= 32 && bnq <= 256) {
+    if (bnq <= 128) return launch_cfg<128, false, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, bnq, s);
+    return launch_cfg<256, false, TOut, false>(mp, mq, C, ldc, split_stride, M, N, K, splits, kbps, bnq, s);
   }
   return llmk_fail(-1, "gemm_tc: no kernel for swap=%d tile=%d cluster=%d", (int)swap, bnq, (int)cluster);
 }
@@ -443,7 +444,8 @@ LLMK_API int llmk_gemm_tc_supported(const void* A, const void* W, int M, int N, 
 // (split_stride = M * ldc elements) over kblocks_per_split blocks of 64 along K each.
 // splits > 1 with cluster != 0 (swapped mode, tile up to 64, at most 8 splits): the splits of a
 // tile form a thread-block cluster, sum their results on chip and write C as for splits == 1.
-// swap != 0 puts the weights on the 128-row side of the MMA; tile is the other side's width.
+// swap != 0 puts the weights on the 128-row side of the MMA; tile is the other side's width
+// (16, 32, 64 or 128 when swapped; a multiple of 32 up to 256 otherwise).
 LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
                           long long ldc, int out_dtype, int swap, int tile, int splits, int kblocks_per_split,
                           int cluster, cudaStream_t stream) {

@@ -339,10 +339,12 @@ def plan_gemm(M: int, N: int, K: int, fused_reduce: bool = False):
     if M <= 128:
         options = [(True, 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128, _ceil_div(N, 128))]
     else:
-        options = [(False, t, _ceil_div(M, 128) * _ceil_div(N, t)) for t in (256, 128)]
+        options = [(False, t, _ceil_div(M, 128) * _ceil_div(N, t)) for t in (256, 224, 192, 160, 128)]
     best = None
     for swap, tile, tiles in options:
-        t_mma = 128 * tile * 64 * 2 / 15.2e6                       # us per k-block at one SM's tensor peak
+        # us per k-block at one SM's tensor peak; a tile of 128 or less reads as many bytes from
+        # shared memory per MMA as the tensor core consumes and runs at about two thirds of that
+        t_mma = 128 * tile * 64 * 2 / 15.2e6 * (1.5 if (not swap and tile <= 128) else 1.0)
         t_mem = (128 + tile) * 128 / 45e3 if swap else 0.0          # us per k-block at one SM's HBM share
         t_kb = max(t_mma, t_mem)
         for s in range(1, min(kb, 32) + 1):

@@ -130,6 +130,7 @@ def test_gemm_tensor_core(ops, M, N, K, out_dtype):
 @pytest.mark.parametrize("swap,tile,splits,cluster", [
     (True, 16, 1, False), (True, 16, 4, False), (True, 32, 2, False), (True, 64, 3, False), (True, 128, 1, False),
     (False, 128, 1, False), (False, 256, 1, False), (False, 256, 2, False), (False, 128, 5, False),
+    (False, 160, 1, False), (False, 224, 2, False), (False, 96, 1, False), (False, 32, 1, False),
     (True, 16, 6, True), (True, 16, 2, True), (True, 32, 3, True), (True, 64, 3, True)])
 def test_gemm_tensor_core_every_configuration(ops, swap, tile, splits, cluster):
     torch.manual_seed(6)
