@@ -232,47 +232,52 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         fence_after_sync();
         // every row sees every key of the block when the block lies inside all windows and below all diagonals
         const bool full = (key0 + BKV - 1 <= p0) && (window <= 0 || key0 >= p_last - window + 1);
-        // pass 1: the row's maximum over the block (scores stay in tensor memory)
-        float m_blk = -INFINITY;
+        // pass 1: the row's maximum over the block (scores stay in tensor memory).  The scale is
+        // positive, so the maximum is taken over the raw scores and scaled once.  Four running
+        // maxima (and four running sums below) keep the chains of dependent instructions short.
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < BKV; c += 32) {
-          uint32_t raw[32];
-          tmem_ld_x32(lane_addr + c, raw);
+        for (int c = 0; c < BKV; c += 64) {
+          uint32_t raw[64];
+          tmem_ld_x64(lane_addr + c, raw);
           tmem_ld_wait();
+          if (full) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = __uint_as_float(raw[j]) * scale_log2e;
-            if (!full) {
+            for (int j = 0; j < 64; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[j]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
               const int key = key0 + c + j;
-              if (key > pos || key < lo) x = -INFINITY;
+              if (key <= pos && key >= lo) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[j]));
             }
-            m_blk = fmaxf(m_blk, x);
           }
         }
-        const float m_new = fmaxf(m, m_blk);
+        const float m_raw = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        const float m_new = fmaxf(m, m_raw * scale_log2e);
         const float m_use = m_new == -INFINITY ? 0.f : m_new;          // a row that sees nothing yet
         const float alpha = fast_exp2(m - m_use);                       // 0 while m is -inf
-        float l_blk = 0.f;
-        // pass 2: P as bfloat16 into the swizzled K-major tile: 16-byte chunk c of row r sits at c ^ (r % 8)
+        const float neg_m = -m_use;
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+        // pass 2: P = exp2(score * scale - m) as bfloat16 into the swizzled K-major tile: 16-byte
+        // chunk c of row r sits at c ^ (r % 8)
 #pragma unroll
-        for (int c = 0; c < BKV; c += 32) {
-          uint32_t raw[32];
-          tmem_ld_x32(lane_addr + c, raw);
+        for (int c = 0; c < BKV; c += 64) {
+          uint32_t raw[64];
+          tmem_ld_x64(lane_addr + c, raw);
           tmem_ld_wait();
 #pragma unroll
-          for (int q8 = 0; q8 < 4; ++q8) {
+          for (int q8 = 0; q8 < 8; ++q8) {
             uint32_t packed[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              float xa = __uint_as_float(raw[q8 * 8 + 2 * j]) * scale_log2e;
-              float xb = __uint_as_float(raw[q8 * 8 + 2 * j + 1]) * scale_log2e;
+              float pa = fast_exp2(fmaf(__uint_as_float(raw[q8 * 8 + 2 * j]), scale_log2e, neg_m));
+              float pb = fast_exp2(fmaf(__uint_as_float(raw[q8 * 8 + 2 * j + 1]), scale_log2e, neg_m));
               if (!full) {
                 const int key = key0 + c + q8 * 8 + 2 * j;
-                if (key > pos || key < lo) xa = -INFINITY;
-                if (key + 1 > pos || key + 1 < lo) xb = -INFINITY;
+                if (key > pos || key < lo) pa = 0.f;
+                if (key + 1 > pos || key + 1 < lo) pb = 0.f;
               }
-              const float pa = fast_exp2(xa - m_use), pb = fast_exp2(xb - m_use);
-              l_blk += pa + pb;
+              ls[j] += pa + pb;
               const __nv_bfloat162 h2 = __floats2bfloat162_rn(pa, pb);
               packed[j] = *reinterpret_cast<const uint32_t*>(&h2);
             }
@@ -282,6 +287,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
           }
         }
+        const float l_blk = (ls[0] + ls[1]) + (ls[2] + ls[3]);
         l = l * alpha + l_blk;
         m = m_new;
         fence_proxy_async();                  // the MMA reads P through the async proxy
@@ -291,12 +297,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (ok) ok = mbar_wait(pv_full, i & 1);
         fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < HS; c += 32) {
-          uint32_t raw[32];
-          tmem_ld_x32(lane_addr + BKV + c, raw);
+        for (int c = 0; c < HS; c += 64) {
+          uint32_t raw[64];
+          tmem_ld_x64(lane_addr + BKV + c, raw);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o[c + j] = fmaf(o[c + j], alpha, __uint_as_float(raw[j]));
+          for (int j = 0; j < 64; ++j) o[c + j] = fmaf(o[c + j], alpha, __uint_as_float(raw[j]));
         }
         fence_before_sync();
       }
