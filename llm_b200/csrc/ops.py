@@ -56,7 +56,19 @@ def _ptr(t, name="tensor"):
     return c_void_p(t.data_ptr())
 
 
+_STREAM = None
+
+
+def set_stream(handle) -> None:
+    """Fix the CUDA stream that the kernels launch on (a raw handle), or None to go back to
+    asking torch for its current stream at every launch, which costs several microseconds."""
+    global _STREAM
+    _STREAM = handle
+
+
 def _stream():
+    if _STREAM is not None:
+        return c_void_p(_STREAM)
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 

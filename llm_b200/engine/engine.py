@@ -153,6 +153,8 @@ class Engine:
         widths = [self.cache.table_width(g) for g in range(self.cache.num_groups)]
         self.layout = lay = _MetaLayout(self.max_tokens, self.max_entries, self.max_rows, widths)
         self._host_ring = [torch.zeros(lay.total, dtype=torch.int32).pin_memory() for _ in range(4)]
+        # host copy of every request slot's block table, per group, kept up to date as pages are taken
+        self._table_mirror = [np.zeros((self.max_entries, w), dtype=np.int32) for w in widths]
         self._host_events = [None] * len(self._host_ring)
         self._ring_at = 0
         self.meta = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
@@ -263,36 +265,51 @@ class Engine:
         host_t = self._next_host_buffer()
         host = host_t.numpy()
         B = len(entries)
-        entry_tokens = np.zeros(B, dtype=np.int32)
-        entry_start = np.zeros(B, dtype=np.int32)
-        entry_slots = np.zeros(B, dtype=np.int32)
-        t0 = r0 = 0
-        host[lay.cu_tokens] = 0
+        ns = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=B)
+        starts = np.empty(B, dtype=np.int64)
+        slots = np.empty(B, dtype=np.int64)
+        G = cache.num_groups
         for b, e in enumerate(entries):
-            if not cache.is_live(e.request_id):
-                cache.admit(e.request_id)
-            n = len(e.tokens)
-            start = cache.extend(e.request_id, n)
-            toks = np.asarray(e.tokens, dtype=np.int32)
-            pos = np.arange(start, start + n, dtype=np.int32)
-            host[lay.token_ids + t0: lay.token_ids + t0 + n] = toks
-            host[lay.positions + t0: lay.positions + t0 + n] = pos
-            host[lay.token_entry + t0: lay.token_entry + t0 + n] = b
-            host[lay.cu_tokens + b + 1] = t0 + n
-            host[lay.kv_lens + b] = start + n
-            host[lay.state_slots + b] = cache.slot(e.request_id)
-            for g in range(cache.num_groups):
-                ps = self.page_size
-                table = np.asarray(cache.table(g, e.request_id), dtype=np.int32)
-                w = cache.table_width(g)
-                row = lay.block_table[g] + b * w
-                host[row: row + len(table)] = table
-                host[lay.slot_map[g] + t0: lay.slot_map[g] + t0 + n] = table[pos // ps] * ps + pos % ps
-            for w_ in e.want:
-                host[lay.logit_rows + r0] = t0 + w_
-                r0 += 1
-            entry_tokens[b], entry_start[b], entry_slots[b] = n, start, cache.slot(e.request_id)
-            t0 += n
+            rid = e.request_id
+            if not cache.is_live(rid):
+                cache.admit(rid)
+            start = cache.extend(rid, int(ns[b]))
+            slot = cache.slot(rid)
+            starts[b], slots[b] = start, slot
+            for g in range(G):                      # pages taken by this step go into the host mirror of the tables
+                table = cache.table(g, rid)
+                first_new = start // self.page_size
+                if len(table) > first_new:
+                    self._table_mirror[g][slot, first_new:len(table)] = table[first_new:]
+        cu = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(ns, out=cu[1:])
+        T = int(cu[B])
+        if T == B:                                  # one token each: no repeats needed
+            entry_of = np.arange(B, dtype=np.int64)
+            pos = starts
+            host[lay.token_ids: lay.token_ids + T] = [e.tokens[0] for e in entries]
+        else:
+            entry_of = np.repeat(np.arange(B, dtype=np.int64), ns)
+            pos = starts[entry_of] + (np.arange(T, dtype=np.int64) - cu[entry_of])
+            host[lay.token_ids: lay.token_ids + T] = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        host[lay.positions: lay.positions + T] = pos
+        host[lay.token_entry: lay.token_entry + T] = entry_of
+        host[lay.cu_tokens: lay.cu_tokens + B + 1] = cu
+        host[lay.kv_lens: lay.kv_lens + B] = starts + ns
+        host[lay.state_slots: lay.state_slots + B] = slots
+        ps = self.page_size
+        for g in range(G):
+            w = cache.table_width(g)
+            mirror = self._table_mirror[g]
+            host[lay.block_table[g]: lay.block_table[g] + B * w].reshape(B, w)[:] = mirror[slots]
+            host[lay.slot_map[g]: lay.slot_map[g] + T] = mirror[slots[entry_of], pos // ps] * ps + pos % ps
+        if n_rows:
+            r0 = 0
+            for b, e in enumerate(entries):
+                for w_ in e.want:
+                    host[lay.logit_rows + r0] = cu[b] + w_
+                    r0 += 1
+        entry_tokens, entry_start, entry_slots = ns.astype(np.int32), starts.astype(np.int32), slots.astype(np.int32)
         fresh = cache.take_fresh_slots()
         if fresh:
             self.state_storage.zero_slots(fresh)
@@ -315,6 +332,13 @@ class Engine:
         return self._host_ring[self._ring_at]
 
     def _forward(self, ctx: StepContext) -> None:
+        ops.set_stream(torch.cuda.current_stream().cuda_stream)     # looked up once per step, not per kernel
+        try:
+            self._forward_on_stream(ctx)
+        finally:
+            ops.set_stream(None)
+
+    def _forward_on_stream(self, ctx: StepContext) -> None:
         stream = ResidualStream(self.resid, ctx.n_tokens)
         self.model.forward(ctx, stream, self._views)
         R = ctx.n_logit_rows

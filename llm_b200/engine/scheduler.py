@@ -140,19 +140,25 @@ class Scheduler:
                        for g in range(G))
 
         # Decoding requests first; preempt from the back while they do not all fit.
+        per_request = {}
         while self.decode_ready:
             needs = [0] * G
-            for rid in list(self.decode_ready)[:cfg.max_num_seqs]:
-                for g, k in enumerate(cache.pages_needed(rid, 1)):
-                    needs[g] += max(k, 0)
+            first = list(self.decode_ready)[:cfg.max_num_seqs]
+            for rid in first:
+                k = per_request.get(rid)
+                if k is None:
+                    k = per_request[rid] = cache.pages_needed(rid, 1)
+                for g in range(G):
+                    needs[g] += max(k[g], 0)
             if fits(needs):
                 break
             self._preempt_last_decode()
         for rid in list(self.decode_ready)[:cfg.max_num_seqs]:
             r = self.requests[rid]
             self.decode_ready.popleft()
-            for g, k in enumerate(cache.pages_needed(rid, 1)):
-                promised[g] += k
+            k = per_request[rid]
+            for g in range(G):
+                promised[g] += k[g]
             batch.entries.append(ScheduledEntry(rid, r.cached_len, [r.token_ids[-1]], True))
         budget = cfg.max_num_batched_tokens - batch.num_tokens
 
