@@ -211,6 +211,12 @@ def paged_attention_generic(out: torch.Tensor, q: torch.Tensor, k_pages: torch.T
         c_float(scale), c_int(_kind(q.dtype)), _stream()))
 
 
+def feed_tokens(token_ids: torch.Tensor, sampled: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, n: int) -> None:
+    """token_ids[dst[i]] = sampled[src[i]] for i < n, all int32 on the device."""
+    assert token_ids.dtype == sampled.dtype == dst.dtype == src.dtype == torch.int32
+    _check(load().llmk_feed_tokens(_ptr(token_ids), _ptr(sampled), _ptr(dst), _ptr(src), c_int(n), _stream()))
+
+
 def sample_rows(out: torch.Tensor, logits: torch.Tensor, rows: int, temperature=None, uniform=None) -> None:
     """out[r] = argmax of logits[r] (ties to the lowest id) where temperature[r] <= 0 or no
     temperatures are given, else the inverse-CDF draw of softmax(logits[r] / temperature[r])

@@ -90,3 +90,21 @@ LLMK_API int llmk_sample_rows(int* out, const float* logits, long long row_strid
   launch_kernel(sample_rows_kernel, dim3(rows), dim3(THREADS), 0, stream, out, logits, row_stride, vocab, temperature, uniform);
   LLMK_LAUNCH_CHECK("sample_rows");
 }
+
+
+// token_ids[dst[i]] = sampled[src[i]]: the tokens that the previous step sampled become the
+// inputs of this step without a round trip through the host.
+__global__ void feed_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ sampled,
+                                   const int* __restrict__ dst, const int* __restrict__ src, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) token_ids[dst[i]] = sampled[src[i]];
+}
+
+LLMK_API int llmk_feed_tokens(int* token_ids, const int* sampled, const int* dst, const int* src, int n,
+                              cudaStream_t stream) {
+  if (n == 0) return 0;
+  launch_kernel(feed_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, token_ids, sampled, dst, src, n);
+  LLMK_LAUNCH_CHECK("feed_tokens");
+}

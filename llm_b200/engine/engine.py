@@ -39,6 +39,7 @@ class StepEntry:
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=list)   # indices into tokens
+    feed: Optional[int] = None      # take the (single) token from this row of step()'s feed_source, on the device
 
 
 class _MetaLayout:
@@ -60,6 +61,8 @@ class _MetaLayout:
         self.positions = take(max_tokens)
         self.token_entry = take(max_tokens)
         self.logit_rows = take(max_rows)
+        self.feed_dst = take(max_entries)
+        self.feed_src = take(max_entries)
         self.slot_map = [take(max_tokens) for _ in table_widths]
         self.block_table = [take(max_entries * w) for w in table_widths]
         self.total = off
@@ -210,14 +213,16 @@ class Engine:
         return self.cache.is_live(request_id)
 
     # ---- the step -----------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], feed_source: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run one batch; returns float32 logits [wanted rows, vocab] on the device, in
         the order of the entries and of their `want`.  The tensor is a view of a buffer
-        that the next step overwrites."""
-        ctx = self._prepare(entries)
+        that the next step overwrites.  Entries with `feed` take their token from
+        feed_source (int32 on the device, e.g. what the sampler made of the previous step),
+        so that a step can be launched before the host has seen the previous step's tokens."""
+        ctx = self._prepare(entries, feed_source)
         return self._run(ctx)
 
-    def _prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+    def _prepare(self, entries: Sequence[StepEntry], feed_source: Optional[torch.Tensor] = None) -> StepContext:
         if not entries:
             raise StepError("a step needs at least one entry")
         if len(entries) > self.max_entries:
@@ -234,7 +239,10 @@ class Engine:
             for w in e.want:
                 if not (0 <= w < n):
                     raise StepError(f"request {e.request_id!r}: wanted place {w} is outside its {n} tokens")
-            if min(e.tokens) < 0 or max(e.tokens) >= self.vocab:
+            if e.feed is not None:
+                if n != 1 or feed_source is None or not (0 <= e.feed < feed_source.numel()):
+                    raise StepError(f"request {e.request_id!r}: a fed entry brings one token from a row of feed_source")
+            elif min(e.tokens) < 0 or max(e.tokens) >= self.vocab:
                 raise StepError(f"request {e.request_id!r}: token id outside [0, {self.vocab})")
             n_tokens += n
             n_rows += len(e.want)
@@ -287,11 +295,12 @@ class Engine:
         if T == B:                                  # one token each: no repeats needed
             entry_of = np.arange(B, dtype=np.int64)
             pos = starts
-            host[lay.token_ids: lay.token_ids + T] = [e.tokens[0] for e in entries]
+            host[lay.token_ids: lay.token_ids + T] = [e.tokens[0] if e.feed is None else 0 for e in entries]
         else:
             entry_of = np.repeat(np.arange(B, dtype=np.int64), ns)
             pos = starts[entry_of] + (np.arange(T, dtype=np.int64) - cu[entry_of])
-            host[lay.token_ids: lay.token_ids + T] = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+            host[lay.token_ids: lay.token_ids + T] = np.concatenate(
+                [np.asarray(e.tokens if e.feed is None else [0], dtype=np.int32) for e in entries])
         host[lay.positions: lay.positions + T] = pos
         host[lay.token_entry: lay.token_entry + T] = entry_of
         host[lay.cu_tokens: lay.cu_tokens + B + 1] = cu
@@ -309,6 +318,13 @@ class Engine:
                 for w_ in e.want:
                     host[lay.logit_rows + r0] = cu[b] + w_
                     r0 += 1
+        n_feed = 0
+        if feed_source is not None:
+            for b, e in enumerate(entries):
+                if e.feed is not None:
+                    host[lay.feed_dst + n_feed] = cu[b]
+                    host[lay.feed_src + n_feed] = e.feed
+                    n_feed += 1
         entry_tokens, entry_start, entry_slots = ns.astype(np.int32), starts.astype(np.int32), slots.astype(np.int32)
         fresh = cache.take_fresh_slots()
         if fresh:
@@ -317,6 +333,9 @@ class Engine:
         ev = torch.cuda.Event()
         ev.record()
         self._host_events[self._ring_at] = ev
+        if n_feed:
+            ops.feed_tokens(self._ctx.token_ids, feed_source, self.meta[lay.feed_dst: lay.feed_dst + n_feed],
+                            self.meta[lay.feed_src: lay.feed_src + n_feed], n_feed)
 
         ctx = self._ctx
         ctx.n_tokens, ctx.n_entries, ctx.n_logit_rows = n_tokens, B, n_rows

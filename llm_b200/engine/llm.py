@@ -17,7 +17,7 @@ import torch
 from ..config.engine_options import EngineOptions
 from ..sampling.sampler import Sampler, uniform_for
 from .engine import Engine, StepEntry
-from .scheduler import Request, ScheduledBatch, Scheduler, SchedulerConfig
+from .scheduler import PENDING_TOKEN, Request, ScheduledBatch, Scheduler, SchedulerConfig
 
 
 class LLM:
@@ -26,7 +26,7 @@ class LLM:
                  eos_token_id: Optional[int] = None, kv_block_size: int = 16,
                  num_kv_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.9,
                  use_cuda_graphs: bool = True, device: str = "cuda:0", random_config: Optional[dict] = None,
-                 random_seed: int = 0):
+                 random_seed: int = 0, lookahead: bool = True):
         """model: a folder with config.json and model.safetensors, or None together with
         random_config (a config.json's contents) for seeded random weights."""
         options = EngineOptions(dtype=dtype, kv_block_size=kv_block_size, max_num_seqs=max_num_seqs,
@@ -39,22 +39,36 @@ class LLM:
         self.eos_token_id = eos_token_id
         self.scheduler_config = SchedulerConfig(max_num_seqs, max_num_batched_tokens, eos_token_id)
         self.sampler = Sampler(max_num_seqs, self.engine.device)
+        self.lookahead = lookahead     # launch decode steps before the previous step's tokens are read
 
     # ---- one scheduled batch through the model: tokens in, next tokens out ----
-    def inference(self, scheduler: Scheduler, batch: ScheduledBatch) -> Dict[int, int]:
+    def launch(self, scheduler: Scheduler, batch: ScheduledBatch, previous=None):
+        """Start a step and the sampling of its tokens without waiting for either.  Tokens that
+        are still pending in the scheduler (sampled by `previous`, a launch() result that the
+        host has not read yet) are taken from the previous step's sampler output on the device.
+        Returns (rows, handle): the entries that sample and the handle of their tokens."""
         entries, rows = [], []
+        feed_rows = {e.request_id: i for i, e in enumerate(previous[0])} if previous is not None else {}
         for e in batch.entries:
-            entries.append(StepEntry(e.request_id, e.tokens, [len(e.tokens) - 1] if e.samples else []))
+            want = [len(e.tokens) - 1] if e.samples else []
+            if len(e.tokens) == 1 and e.tokens[0] == PENDING_TOKEN:
+                entries.append(StepEntry(e.request_id, [0], want, feed=feed_rows[e.request_id]))
+            else:
+                entries.append(StepEntry(e.request_id, e.tokens, want))
             if e.samples:
                 rows.append(e)
-        logits = self.engine.step(entries)
+        logits = self.engine.step(entries, feed_source=previous[1].device if feed_rows else None)
         temps, unis = [], []
         for e in rows:
             r = scheduler.requests[e.request_id]
             temps.append(r.temperature)
             unis.append(uniform_for(r.seed, r.id, e.start + len(e.tokens)) if r.temperature > 0 else 0.0)
-        tokens = self.sampler.sample(logits, temps, unis)
-        return {e.request_id: t for e, t in zip(rows, tokens)}
+        return rows, self.sampler.sample_async(logits, temps, unis)
+
+    def inference(self, scheduler: Scheduler, batch: ScheduledBatch) -> Dict[int, int]:
+        """One step, waited for: the next token of every entry that samples."""
+        rows, handle = self.launch(scheduler, batch)
+        return {e.request_id: t for e, t in zip(rows, handle.result())}
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 256, temperature: float = 0.0,
                  seed: int = 0, ignore_eos: bool = False) -> List[List[int]]:
@@ -73,26 +87,48 @@ class LLM:
         return [results[rid] for rid in ids]
 
     def _run_to_idle(self, scheduler: Scheduler, on_finished: Callable[[Request], None]) -> None:
-        """Steps until no request is left.  Host-side times of the steps that only decode
-        (schedule, copy in, run, sample, copy out, update) are kept in last_stats, as the
-        reference's driver keeps sched/wait/update times per step (runtime/Driver.h:16,74-83)."""
-        stats = {"steps": 0, "decode_steps": 0, "decode_tokens": 0, "decode_seconds": 0.0,
+        """Steps until no request is left.
+
+        While requests only decode, a step is launched before the tokens of the step before it
+        have reached the host: its input tokens are fed on the device from the sampler's output,
+        and the host reads the earlier tokens (to store them and to look for the end of a request)
+        while the GPU is already busy.  A request that turns out to have ended runs one step too
+        far; that step's token is dropped.  Whenever the next batch could depend on the tokens
+        (a request at its last token, prompts waiting, pages short) the step is waited for first.
+        Host-side times of the steps that only decode are kept in last_stats, as the reference's
+        driver keeps sched/wait/update times per step (runtime/Driver.h:16,74-83)."""
+        stats = {"steps": 0, "decode_steps": 0, "decode_tokens": 0, "decode_seconds": 0.0, "lookahead_steps": 0,
                  "h2d_bytes_per_step": self.engine.layout.total * 4, "d2h_bytes_per_step": 0}
+        previous = None              # (batch, rows, handle) of a launched step whose tokens are not read yet
+        t_mark = time.perf_counter()
         while scheduler.num_requests():
-            t0 = time.perf_counter()
             batch = scheduler.schedule()
             if batch.empty():
                 raise RuntimeError("the scheduler has requests but nothing can run: the cache pool is too "
                                    "small for the request at the head of the queue")
-            tokens = self.inference(scheduler, batch)       # ends with the device-to-host copy of the tokens
-            for r in scheduler.update(batch, tokens):
-                on_finished(r)
+            rows, handle = self.launch(scheduler, batch, (previous[1], previous[2]) if previous else None)
+            if previous is not None:         # the GPU is busy with `batch`: now read the step before it
+                p_batch, p_rows, p_handle = previous
+                scheduler.resolve(p_batch, {e.request_id: t for e, t in zip(p_rows, p_handle.result())})
+                previous = None
+            decode_only = all(len(e.tokens) == 1 for e in batch.entries)
+            if self.lookahead and decode_only and scheduler.can_look_ahead(batch):
+                scheduler.update_pending(batch)
+                previous = (batch, rows, handle)
+                stats["lookahead_steps"] += 1
+            else:
+                tokens = {e.request_id: t for e, t in zip(rows, handle.result())}
+                for r in scheduler.update(batch, tokens):
+                    on_finished(r)
             stats["steps"] += 1
-            if all(len(e.tokens) == 1 for e in batch.entries):
+            now = time.perf_counter()
+            if decode_only:
                 stats["decode_steps"] += 1
                 stats["decode_tokens"] += len(batch.entries)
-                stats["decode_seconds"] += time.perf_counter() - t0
-                stats["d2h_bytes_per_step"] = max(stats["d2h_bytes_per_step"], 4 * len(tokens))
+                stats["decode_seconds"] += now - t_mark
+                stats["d2h_bytes_per_step"] = max(stats["d2h_bytes_per_step"], 4 * len(rows))
+            t_mark = now
+        assert previous is None
         self.last_stats = stats
         self.engine.check_status()
 

@@ -29,6 +29,7 @@ from typing import Deque, Dict, List, Optional
 from ..cache.manager import CacheManager
 
 PREFILL, DECODE = "prefill", "decode"
+PENDING_TOKEN = -1      # stands in a request's tokens for a token that is sampled but not read back yet
 
 
 @dataclass
@@ -50,6 +51,7 @@ class Request:
     phase: str = PREFILL
     cached_len: int = 0          # tokens whose keys and values are in the cache
     num_preemptions: int = 0
+    ended: bool = False          # its end was found after the next step had already been launched
 
     @property
     def generated(self) -> List[int]:
@@ -236,17 +238,68 @@ class Scheduler:
             r.cached_len = e.start + len(e.tokens)
             if not e.samples:
                 continue
+            if r.ended:                      # ran one step too far: that step's token is dropped
+                self._retire(r, done)
+                continue
             tok = int(new_tokens[e.request_id])
             r.token_ids.append(tok)
-            if self._finished(r, tok):
-                if self.cache.is_live(r.id):
-                    self.cache.release(r.id)
-                del self.requests[r.id]
-                done.append(r)
+            if tok != PENDING_TOKEN and self._finished(r, tok):
+                self._retire(r, done)
             else:
                 r.phase = DECODE
                 self.decode_ready.append(r.id)
         return done
+
+    def _retire(self, r: Request, done: List[Request]) -> None:
+        if self.cache.is_live(r.id):
+            self.cache.release(r.id)
+        del self.requests[r.id]
+        done.append(r)
+
+    # ---- one step of lookahead: the next step is launched before this step's tokens are read ----
+    def can_look_ahead(self, batch: ScheduledBatch) -> bool:
+        """Whether the step after `batch` can be scheduled before the tokens of `batch` are
+        known: only decoding requests, nobody waiting to be admitted, nobody at its last token,
+        and pages for one more token of each without preempting anyone."""
+        if self.prefill_ready or not batch.entries:
+            return False
+        need = [0] * self.cache.num_groups
+        for e in batch.entries:
+            r = self.requests.get(e.request_id)
+            if r is None or not e.samples or r.ended:
+                return False
+            if len(r.token_ids) - r.prompt_len + 2 > r.max_new_tokens:     # this step's token would be its last
+                return False
+            if self.cache.length(r.id) + 1 > self.cache.max_seq_len:
+                return False
+            for g, k in enumerate(self.cache.pages_needed(r.id, 1)):
+                need[g] += max(k, 0)
+        return all(need[g] <= self.cache.num_free_pages(g) for g in range(self.cache.num_groups))
+
+    def update_pending(self, batch: ScheduledBatch) -> None:
+        """update() for a step whose tokens are not known yet: every request gets a placeholder
+        and goes on decoding.  Only after can_look_ahead(batch)."""
+        done = self.update(batch, {e.request_id: PENDING_TOKEN for e in batch.entries})
+        assert not done
+
+    def resolve(self, batch: ScheduledBatch, new_tokens: Dict[int, int]) -> None:
+        """The tokens of a step that was accounted with update_pending() have arrived.  A request
+        that ends with its token is marked: it is already part of the step in flight and retires
+        when that step is accounted."""
+        eos = self.cfg.eos_token_id
+        for e in batch.entries:
+            r = self.requests.get(e.request_id)
+            if r is None:
+                continue
+            tok = int(new_tokens[e.request_id])
+            at = len(r.token_ids) - 1
+            while at >= r.prompt_len and r.token_ids[at] != PENDING_TOKEN:
+                at -= 1
+            assert at >= r.prompt_len, "no pending token to resolve"
+            r.token_ids[at] = tok
+            if eos is not None and eos >= 0 and tok == eos and not r.ignore_eos:
+                del r.token_ids[at + 1:]
+                r.ended = True
 
     def _finished(self, r: Request, tok: int) -> bool:
         eos = self.cfg.eos_token_id

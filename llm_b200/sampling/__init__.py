@@ -1,3 +1,3 @@
-from .sampler import Sampler, SamplingParams, uniform_for
+from .sampler import SampleHandle, Sampler, SamplingParams, uniform_for
 
-__all__ = ["Sampler", "SamplingParams", "uniform_for"]
+__all__ = ["SampleHandle", "Sampler", "SamplingParams", "uniform_for"]

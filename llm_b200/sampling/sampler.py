@@ -43,29 +43,56 @@ class SamplingParams:
     ignore_eos: bool = False
 
 
+class SampleHandle:
+    """Tokens that are being sampled: `device` holds them on the GPU (for feeding the next
+    step), result() waits for the copy to the host and returns them as ints."""
+
+    def __init__(self, device: torch.Tensor, host: torch.Tensor, rows: int, event):
+        self.device, self._host, self.rows, self._event = device, host, rows, event
+
+    def result(self) -> List[int]:
+        if self.rows == 0:
+            return []
+        self._event.synchronize()
+        return self._host[:self.rows].tolist()
+
+
 class Sampler:
+    """Two sets of buffers, used in turn, so that the tokens of one step can still be read (by
+    the host, and by the next step on the device) while the following step is sampled."""
+
     def __init__(self, max_rows: int, device: torch.device):
         self.device = device
         self.max_rows = max_rows
-        self._host = torch.zeros((2, max_rows), dtype=torch.float32).pin_memory()
-        self._dev = torch.zeros((2, max_rows), dtype=torch.float32, device=device)
-        self._out = torch.zeros(max_rows, dtype=torch.int32, device=device)
-        self._out_host = torch.zeros(max_rows, dtype=torch.int32).pin_memory()
+        self._host = [torch.zeros((2, max_rows), dtype=torch.float32).pin_memory() for _ in range(2)]
+        self._dev = [torch.zeros((2, max_rows), dtype=torch.float32, device=device) for _ in range(2)]
+        self._out = [torch.zeros(max_rows, dtype=torch.int32, device=device) for _ in range(2)]
+        self._out_host = [torch.zeros(max_rows, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._turn = 0
 
-    def sample(self, logits: torch.Tensor, temperatures: Sequence[float], uniforms: Sequence[float]) -> List[int]:
-        """One token per row of logits [R, V] (float32, device); returns host ints."""
+    def sample_async(self, logits: torch.Tensor, temperatures: Sequence[float], uniforms: Sequence[float]) -> SampleHandle:
+        """One token per row of logits [R, V] (float32, device), without waiting for them."""
         rows = logits.shape[0]
-        if rows == 0:
-            return []
         if rows > self.max_rows:
             raise ValueError(f"{rows} rows exceed the sampler's limit {self.max_rows}")
+        k = self._turn
+        self._turn ^= 1
+        out = self._out[k]
+        if rows == 0:
+            return SampleHandle(out, self._out_host[k], 0, None)
         if any(t > 0.0 for t in temperatures):
-            self._host[0, :rows] = torch.tensor(list(temperatures), dtype=torch.float32)
-            self._host[1, :rows] = torch.tensor(list(uniforms), dtype=torch.float32)
-            self._dev.copy_(self._host, non_blocking=True)
-            ops.sample_rows(self._out, logits, rows, self._dev[0], self._dev[1])
+            h = self._host[k]
+            h[0, :rows] = torch.tensor(list(temperatures), dtype=torch.float32)
+            h[1, :rows] = torch.tensor(list(uniforms), dtype=torch.float32)
+            self._dev[k].copy_(h, non_blocking=True)
+            ops.sample_rows(out, logits, rows, self._dev[k][0], self._dev[k][1])
         else:
-            ops.sample_rows(self._out, logits, rows)
-        self._out_host.copy_(self._out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self._out_host[:rows].tolist()
+            ops.sample_rows(out, logits, rows)
+        self._out_host[k].copy_(out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return SampleHandle(out, self._out_host[k], rows, event)
+
+    def sample(self, logits: torch.Tensor, temperatures: Sequence[float], uniforms: Sequence[float]) -> List[int]:
+        """One token per row of logits [R, V]; returns host ints."""
+        return self.sample_async(logits, temperatures, uniforms).result()

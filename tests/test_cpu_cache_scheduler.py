@@ -234,3 +234,38 @@ def test_random_load_finishes_and_frees_everything(seed):
         assert r.generated[-1] == 3 or len(r.generated) == want[rid]
     assert all(c.num_free_pages(g) == c.group_spec(g).num_pages for g in range(c.num_groups))
     assert c.num_free_slots() == 4
+
+
+def test_lookahead_placeholders_resolve_and_late_end():
+    """A step accounted before its tokens are known: placeholders, then the real tokens; a request
+    whose token was the end retires when the step it ran too far is accounted."""
+    from llm_b200.engine.scheduler import PENDING_TOKEN
+    c = full_pool(pages=16)
+    s = Scheduler(c, SchedulerConfig(4, 64, eos_token_id=3))
+    a = s.add_request([5] * 10, 6)
+    b_ = s.add_request([6] * 4, 6)
+    run_step(s, c, s.schedule(), token=9)                     # prompts; both sampled 9
+    b1 = s.schedule()
+    assert s.can_look_ahead(b1)
+    for e in b1.entries:
+        c.extend(e.request_id, 1)
+    s.update_pending(b1)
+    assert s.requests[a].token_ids[-1] == PENDING_TOKEN
+    b2 = s.schedule()                                         # scheduled with the tokens still unknown
+    assert [e.tokens for e in b2.entries] == [[PENDING_TOKEN], [PENDING_TOKEN]]
+    for e in b2.entries:
+        c.extend(e.request_id, 1)
+    s.resolve(b1, {a: 7, b_: 3})                              # b's token was the end
+    assert s.requests[a].token_ids[-1] == 7 and s.requests[b_].ended
+    assert not s.can_look_ahead(b2)
+    done = s.update(b2, {a: 8, b_: 8})
+    assert [r.id for r in done] == [b_] and done[0].generated == [9, 3]
+    assert s.requests[a].generated == [9, 7, 8] and not c.is_live(b_)
+    c.check()
+    # a request one token before its limit is not looked ahead
+    b3 = s.schedule()
+    run_step(s, c, b3, token=8)
+    b4 = s.schedule()
+    run_step(s, c, b4, token=8)
+    b5 = s.schedule()                                         # generated 5 of 6: this step's token is the last
+    assert not s.can_look_ahead(b5)

@@ -124,3 +124,24 @@ def test_command_line(folders, tmp_path):
     lines = dict(l.split(": ") for l in proc.stdout.strip().split("\n"))
     for i, p in enumerate(prompts):
         assert [int(x) for x in lines[str(i)].split()] == pl.greedy_generate(cfg, w, p, 6)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_lookahead_changes_nothing(folders, dtype):
+    """Launching a decode step before the previous step's tokens are read gives the same tokens,
+    also when a request ends on a token and when sampling with a temperature."""
+    from llm_b200 import LLM
+    cfg, page = CONFIGS["D"]
+    d = folders("D", dtype)
+    prompts = [random_tokens(n, cfg["vocab_size"], 170 + n) for n in (9, 50, 3, 130)]
+    mk = lambda la, eos: LLM(d, dtype=dtype, max_num_seqs=4, max_num_batched_tokens=64, num_kv_blocks=60,
+                             eos_token_id=eos, lookahead=la)
+    base = mk(False, -1).generate(prompts, max_new_tokens=24)
+    llm = mk(True, -1)
+    assert llm.generate(prompts, max_new_tokens=24) == base
+    assert llm.last_stats["lookahead_steps"] >= 20
+    eos = base[1][6]
+    assert mk(True, eos).generate(prompts, max_new_tokens=24) == mk(False, eos).generate(prompts, max_new_tokens=24)
+    assert mk(True, -1).generate(prompts, max_new_tokens=12, temperature=0.7, seed=2) == \
+        mk(False, -1).generate(prompts, max_new_tokens=12, temperature=0.7, seed=2)
+    llm.engine.cache.check()
