@@ -304,23 +304,26 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
   if (!last_s) return;
   __threadfence();
   const int n_active = min(splits, (n_keys + chunk - 1) / chunk);      // ranges that hold keys
-  float* w_s = &q_s[0][0];                                             // [GT][n_active] merge weights
+  float* w_s = &q_s[0][0];                                             // [GT][splits] maxima, then merge weights
+  float* l_in = reinterpret_cast<float*>(vo_s);                        // [GT][splits] sums of the ranges
   for (int h0 = 0; h0 < group; h0 += GT) {
     const int nh = min(GT, group - h0);
     const size_t base0 = ((size_t)e * n_heads + g * group + h0) * splits;
     __syncthreads();
-    for (int i = tid; i < nh * n_active; i += THREADS) {                // maxima of (head, range)
+    for (int i = tid; i < nh * n_active; i += THREADS) {                // maximum and sum of every (head, range): one round trip
       const int h = i / n_active, sp = i % n_active;
-      w_s[h * splits + sp] = __ldcg(&partial_ml[(base0 + (size_t)h * splits + sp) * 2]);
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(partial_ml + (base0 + (size_t)h * splits + sp) * 2));
+      w_s[h * splits + sp] = ml.x;
+      l_in[h * splits + sp] = ml.y;
     }
     __syncthreads();
-    if (tid < nh) {                                                     // weights exp(m_s - m) / l
+    if (tid < nh) {                                                     // weights exp(m_s - m) / l, from shared memory only
       float m = -INFINITY;
       for (int sp = 0; sp < n_active; ++sp) m = fmaxf(m, w_s[tid * splits + sp]);
       float l = 0.f;
       for (int sp = 0; sp < n_active; ++sp) {
         const float wgt = expf(w_s[tid * splits + sp] - m);
-        l += wgt * __ldcg(&partial_ml[(base0 + (size_t)tid * splits + sp) * 2 + 1]);
+        l += wgt * l_in[tid * splits + sp];
         w_s[tid * splits + sp] = wgt;
       }
       const float inv = 1.f / l;
@@ -332,13 +335,12 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
       const float* o = partial_o + (base0 + (size_t)h * splits) * head_dim + d;
       float accum = 0.f;
       int sp = 0;
-      for (; sp + 4 <= n_active; sp += 4) {                             // four loads in flight, fixed order of sums
-        const float o0 = __ldcg(o + (size_t)sp * head_dim), o1 = __ldcg(o + (size_t)(sp + 1) * head_dim);
-        const float o2 = __ldcg(o + (size_t)(sp + 2) * head_dim), o3 = __ldcg(o + (size_t)(sp + 3) * head_dim);
-        accum = fmaf(w_s[h * splits + sp], o0, accum);
-        accum = fmaf(w_s[h * splits + sp + 1], o1, accum);
-        accum = fmaf(w_s[h * splits + sp + 2], o2, accum);
-        accum = fmaf(w_s[h * splits + sp + 3], o3, accum);
+      for (; sp + 8 <= n_active; sp += 8) {                             // eight loads in flight, fixed order of sums
+        float ov[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) ov[u] = __ldcg(o + (size_t)(sp + u) * head_dim);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) accum = fmaf(w_s[h * splits + sp + u], ov[u], accum);
       }
       for (; sp < n_active; ++sp) accum = fmaf(w_s[h * splits + sp], __ldcg(o + (size_t)sp * head_dim), accum);
       out[(size_t)e * out_stride + (size_t)(g * group + h0 + h) * head_dim + d] = from_f32<T>(accum);

@@ -155,7 +155,17 @@ struct MaybePartial {
     if (parts) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] = 0.f;
-      for (int s = 0; s < splits; ++s) {
+      int s = 0;
+      for (; s + 4 <= splits; s += 4) {              // the loads of four splits in flight, sums in split order
+        float t[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) Vec8<float>::load(parts + (size_t)(s + u) * split_stride + idx, t[u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] += t[u][i];
+      }
+      for (; s < splits; ++s) {
         float t[8];
         Vec8<float>::load(parts + (size_t)s * split_stride + idx, t);
 #pragma unroll

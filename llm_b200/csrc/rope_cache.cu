@@ -32,7 +32,8 @@ __global__ void rope_kv_write_kernel(MaybePartial<T> src, long long src_stride, 
   if (VEC) {
     // eight pairs per thread: half is a multiple of 8 because head_dim is a multiple of 16
     const int per_head = half / 8;
-    for (int idx = threadIdx.x; idx < (n_heads + n_kv) * per_head; idx += blockDim.x) {
+    const int tid = blockIdx.y * blockDim.x + threadIdx.x, stride = gridDim.y * blockDim.x;
+    for (int idx = tid; idx < (n_heads + n_kv) * per_head; idx += stride) {
       const int head = idx / per_head, i = (idx % per_head) * 8;
       const size_t h = row + (size_t)head * head_dim;
       float a[8], b[8], c[8], s[8], ya[8], yb[8];
@@ -53,7 +54,7 @@ __global__ void rope_kv_write_kernel(MaybePartial<T> src, long long src_stride, 
       Vec8<T>::store(dst + i + half, yb);
     }
     const size_t v = row + (size_t)(n_heads + n_kv) * head_dim;
-    for (int idx = threadIdx.x * 8; idx < n_kv * head_dim; idx += blockDim.x * 8) {
+    for (int idx = tid * 8; idx < n_kv * head_dim; idx += stride * 8) {
       const int g = idx / head_dim, d = idx % head_dim;
       float x[8];
       src.at8(v + idx, x);
@@ -108,7 +109,10 @@ LLMK_API int llmk_rope_kv_write(const void* qkv, const float* partials, int spli
                      (uintptr_t)q_out % 16 == 0 && (uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0 &&
                      (uintptr_t)cos_table % 16 == 0 && (uintptr_t)sin_table % 16 == 0;
     auto kern = vec ? rope_kv_write_kernel<T, true> : rope_kv_write_kernel<T, false>;
-    launch_kernel(kern, dim3(n_tokens), dim3(128), 0, stream, src, src_stride, (T*)q_out,
+    // few tokens: spread a token's heads over several CTAs (the vector path strides over blockIdx.y)
+    const int items = (n_heads + n_kv) * (head_dim / 16);
+    const int ys = (vec && n_tokens < 64) ? (items + 63) / 64 : 1;
+    launch_kernel(kern, dim3(n_tokens, ys), dim3(vec && ys > 1 ? 64 : 128), 0, stream, src, src_stride, (T*)q_out,
                   q_out_stride, cos_table, sin_table, head_dim / 2, positions, slot_map, (T*)k_pages, (T*)v_pages,
                   n_heads, n_kv, head_dim, page_size);
     LLMK_LAUNCH_CHECK("rope_kv_write");

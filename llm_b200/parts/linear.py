@@ -14,9 +14,9 @@ from ..csrc import ops
 
 
 # Whether the built-in parts hand split-K partial results to the next kernel instead of summing
-# them with a kernel of their own.  Measured on B200 at batch 8 the consumers (a few CTAs, one
-# per row) sum them more slowly than the wide reduction kernel does, so it is off.
-FUSE_PARTIALS = False
+# them with a kernel of their own.  Measured on B200 at batch 8: 54.7 us per layer with the
+# consumers summing (four splits' loads in flight at a time) against 56.8 us with reduction kernels.
+FUSE_PARTIALS = True
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int, allow_partial: bool = False):
