@@ -14,6 +14,7 @@
 // one row used and no split (kernel/attention/attention_NH_32_NKV_4_HS_64.h:374-386).
 // Softmax and all sums are float32; visible keys are max(0, pos-window+1) .. pos.
 #include "common.cuh"
+#include "attention_decode_mma.cuh"
 
 namespace {
 
@@ -374,6 +375,15 @@ LLMK_API int llmk_paged_attention_decode(void* out, long long out_stride, const 
   LLMK_REQUIRE((long long)n_entries * n_kv <= COUNTER_WORDS, "attention_decode: %d entries x %d kv heads exceed %d counters",
                n_entries, n_kv, COUNTER_WORDS);
   LLMK_REQUIRE(page_size > 0 && window >= 0, "attention_decode: bad page_size %d or window %d", page_size, window);
+  if (dtype == LLMK_BF16 && (head_dim == 64 || head_dim == 128) && q_stride % 2 == 0 && (uintptr_t)q % 4 == 0) {
+    // bfloat16 with a head size of 64 or 128: the query heads of a group as rows of warp-level MMAs
+    dim3 grid(splits, n_kv, n_entries);
+    auto kern = head_dim == 64 ? decode_mma::decode_attention_mma_kernel<64> : decode_mma::decode_attention_mma_kernel<128>;
+    launch_kernel(kern, grid, dim3(decode_mma::THREADS), 0, stream, (__nv_bfloat16*)out, out_stride, scratch,
+                  (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
+                  block_table, table_width, kv_lens, n_heads, n_kv, page_size, window, scale * 1.4426950408889634f, splits);
+    LLMK_LAUNCH_CHECK("attention_decode_mma");
+  }
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     dim3 grid(splits, n_kv, n_entries);

@@ -1,0 +1,300 @@
+// Decode attention on the warp-level tensor cores (bfloat16, head size 64 or 128).
+//
+// The same split of the keys into ranges, one CTA per (range, kv head, request), and the same
+// merge by the last CTA as the CUDA-core kernel in attention_decode.cu; what differs is the
+// inside of a range.  The query heads of the kv group are the rows of an m16n8k16 MMA (up to 16
+// per pass): one instruction scores 8 keys for all of them, so the arithmetic per key no longer
+// grows with the group size.  Each of the four warps works alone on tiles of 32 keys, without
+// block-wide barriers: K fragments come straight from the pages (a lane's two values of a key
+// are 4 contiguous bytes), V is staged per warp through shared memory with cp.async and read
+// back transposed with ldmatrix; scores, maxima, sums and the output are float32, P is rounded
+// to bfloat16 for the second MMA as in the prompt kernel.  A single decoded token has no use for
+// the 128-row tcgen05 MMA; this is the tensor path that fits 8 to 16 rows.
+#pragma once
+
+#include "common.cuh"
+
+namespace decode_mma {
+
+constexpr int THREADS = 128;
+constexpr int ROWS = 16;         // query heads per pass
+constexpr int TILE = 32;         // keys per warp tile
+constexpr int COUNTER_WORDS = 4096;
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_addr));
+}
+__device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;                      // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Scratch layout as in attention_decode.cu: counters, then ml [entries, heads, splits, 2] (the
+// maximum here in the base-2 domain of the pre-scaled scores), then o [entries, heads, splits, HS].
+template <int HS>
+__global__ void __launch_bounds__(THREADS)
+decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_stride, float* __restrict__ scratch,
+                            const __nv_bfloat16* __restrict__ q, long long q_stride,
+                            const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
+                            const int* __restrict__ block_table, int table_width, const int* __restrict__ kv_lens,
+                            int n_heads, int n_kv, int page_size, int window, float scale_log2e, int splits) {
+  constexpr int KS = HS / 16;                  // k-steps of Q K^T
+  constexpr int DT = HS / 8;                   // 8-wide tiles of the output row
+  constexpr int CH = HS / 8;                   // 16-byte chunks of a row
+  constexpr int V_BYTES = TILE * HS * 2;       // one warp's staged values
+  __shared__ __align__(128) uint8_t vbuf[4 * V_BYTES > 4 * ROWS * HS * 4 ? 4 * V_BYTES : 4 * ROWS * HS * 4];
+  __shared__ float wm_s[4][ROWS], wl_s[4][ROWS];
+  __shared__ float w_s[ROWS][64], l_in[ROWS][64];        // merge: per (head, range)
+  __shared__ int last_s;
+
+  pdl_launch_dependents();
+  pdl_wait();
+  const int split = blockIdx.x, g = blockIdx.y, e = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int group = n_heads / n_kv;
+  const int pos = kv_lens[e] - 1;
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int n_keys = pos - lo + 1;
+  int chunk = (n_keys + splits - 1) / splits;
+  chunk = (chunk + TILE - 1) / TILE * TILE;
+  const int k_begin = lo + split * chunk;
+  const int k_end = min(pos + 1, k_begin + chunk);
+  const int* table = block_table + (size_t)e * table_width;
+  const int qrow = lane >> 2, qcol = (lane & 3) * 2;
+
+  int* counters = reinterpret_cast<int*>(scratch);
+  float* partial_ml = scratch + COUNTER_WORDS;
+  float* partial_o = partial_ml + (size_t)gridDim.z * n_heads * splits * 2;
+  uint8_t* v_s = vbuf + warp * V_BYTES;
+  const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(v_s);
+
+  for (int h0 = 0; h0 < group && k_begin < k_end; h0 += ROWS) {        // a range without keys only reports in
+    const int nh = min(ROWS, group - h0);
+    const int head0 = g * group + h0;
+    // Q fragments: rows = heads, straight from global memory (4 bytes = 2 bf16 per load)
+    uint32_t qf[KS][4];
+    {
+      const __nv_bfloat16* q0 = q + (size_t)e * q_stride + (size_t)(head0 + qrow) * HS;
+      const __nv_bfloat16* q1 = q0 + 8 * HS;
+      const bool r0 = qrow < nh, r1 = qrow + 8 < nh;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        qf[ks][0] = r0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + qcol) : 0u;
+        qf[ks][1] = r1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + qcol) : 0u;
+        qf[ks][2] = r0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + qcol) : 0u;
+        qf[ks][3] = r1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + qcol) : 0u;
+      }
+    }
+    float o[DT][4];
+#pragma unroll
+    for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;        // rows qrow and qrow + 8 (l: this lane's share)
+
+    for (int t = k_begin + warp * TILE; t < k_end; t += 4 * TILE) {
+      // ---- stage the tile's values: 32 rows of CH chunks, swizzled by the row ----
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const int idx = i * 32 + lane;
+        const int kl = idx / CH, c = idx % CH;
+        const int kp = t + kl;
+        const bool valid = kp < k_end;
+        const int kq = valid ? kp : k_begin;
+        const size_t row = (((size_t)table[kq / page_size] * n_kv + g) * page_size + kq % page_size) * HS;
+        const int cs = (c & ~7) | ((c ^ kl) & 7);
+        cp_async_16(v_addr + kl * (HS * 2) + cs * 16, v_pages + row + c * 8, valid);
+      }
+      // ---- keys: fragments straight from the pages ----
+      uint32_t kf[4][KS][2];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const int kp = t + nt * 8 + qrow;
+        const int kq = kp < k_end ? kp : k_begin;
+        const __nv_bfloat16* kr = k_pages + (((size_t)table[kq / page_size] * n_kv + g) * page_size + kq % page_size) * HS;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          kf[nt][ks][0] = *reinterpret_cast<const uint32_t*>(kr + ks * 16 + qcol);
+          kf[nt][ks][1] = *reinterpret_cast<const uint32_t*>(kr + ks * 16 + 8 + qcol);
+        }
+      }
+      // ---- S = Q K^T ----
+      float s[4][4];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) mma_16816(s[nt], qf[ks], kf[nt][ks][0], kf[nt][ks][1]);
+      }
+      // ---- scale, mask the keys past the range, running maximum and sum ----
+      float t0 = -INFINITY, t1 = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const int kp = t + nt * 8 + qcol;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const bool valid = kp + j < k_end;
+          s[nt][j] = valid ? s[nt][j] * scale_log2e : -INFINITY;
+          s[nt][2 + j] = valid ? s[nt][2 + j] * scale_log2e : -INFINITY;
+          t0 = fmaxf(t0, s[nt][j]);
+          t1 = fmaxf(t1, s[nt][2 + j]);
+        }
+      }
+      t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1));
+      t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
+      t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1));
+      t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
+      const float n0 = fmaxf(m0, t0), n1 = fmaxf(m1, t1);          // finite: the tile holds at least one key
+      const float a0 = ex2(m0 - n0), a1 = ex2(m1 - n1);
+      m0 = n0; m1 = n1;
+      l0 *= a0; l1 *= a1;
+#pragma unroll
+      for (int d = 0; d < DT; ++d) { o[d][0] *= a0; o[d][1] *= a0; o[d][2] *= a1; o[d][3] *= a1; }
+      uint32_t pf[2][4];                                          // P as the A operand of two k-steps of 16 keys
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const float p0 = ex2(s[nt][0] - n0), p1 = ex2(s[nt][1] - n0);
+        const float p2 = ex2(s[nt][2] - n1), p3 = ex2(s[nt][3] - n1);
+        l0 += p0 + p1;
+        l1 += p2 + p3;
+        pf[nt >> 1][(nt & 1) * 2] = pack2(p0, p1);
+        pf[nt >> 1][(nt & 1) * 2 + 1] = pack2(p2, p3);
+      }
+      // ---- O += P V ----
+      cp_async_wait_all();
+      __syncwarp();
+      const int mid = lane >> 3, r8 = lane & 7;
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+        const int kl = kk * 16 + (mid & 1) * 8 + r8;               // the key whose row this lane points at
+#pragma unroll
+        for (int dp = 0; dp < DT / 2; ++dp) {
+          const int c = dp * 2 + (mid >> 1);
+          const int cs = (c & ~7) | ((c ^ kl) & 7);
+          uint32_t vb[4];
+          ldmatrix_x4_trans(vb, v_addr + kl * (HS * 2) + cs * 16);
+          mma_16816(o[dp * 2], pf[kk], vb[0], vb[1]);
+          mma_16816(o[dp * 2 + 1], pf[kk], vb[2], vb[3]);
+        }
+      }
+      __syncwarp();                                               // the values are consumed before the next tile lands
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    // ---- the four warps' results, merged in their order ----
+    __syncthreads();                                              // every warp is done with its staged values
+    float* wo = reinterpret_cast<float*>(vbuf) + (size_t)warp * ROWS * HS;
+    if ((lane & 3) == 0) {
+      wm_s[warp][qrow] = m0; wm_s[warp][qrow + 8] = m1;
+      wl_s[warp][qrow] = l0; wl_s[warp][qrow + 8] = l1;
+    }
+#pragma unroll
+    for (int d = 0; d < DT; ++d) {
+      *reinterpret_cast<float2*>(wo + qrow * HS + d * 8 + qcol) = make_float2(o[d][0], o[d][1]);
+      *reinterpret_cast<float2*>(wo + (qrow + 8) * HS + d * 8 + qcol) = make_float2(o[d][2], o[d][3]);
+    }
+    __syncthreads();
+    for (int i = tid; i < nh * HS; i += THREADS) {
+      const int h = i / HS, d = i % HS;
+      float m = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) m = fmaxf(m, wm_s[w][h]);
+      float l = 0.f, acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = wm_s[w][h];
+        if (mw > -INFINITY) {
+          const float f = ex2(mw - m);
+          l += f * wl_s[w][h];
+          acc += f * reinterpret_cast<const float*>(vbuf)[((size_t)w * ROWS + h) * HS + d];
+        }
+      }
+      if (splits == 1) {
+        out[(size_t)e * out_stride + (size_t)(head0 + h) * HS + d] = __float2bfloat16_rn(acc / l);
+      } else {
+        partial_o[(((size_t)e * n_heads + head0 + h) * splits + split) * HS + d] = acc;
+        if (d == 0) {
+          float* ml = partial_ml + (((size_t)e * n_heads + head0 + h) * splits + split) * 2;
+          ml[0] = m;
+          ml[1] = l;
+        }
+      }
+    }
+    __syncthreads();                                              // vbuf is reused by the next pass
+  }
+  if (splits == 1) return;
+
+  // ---- the last range to arrive merges all of them ----
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int arrived = atomicAdd(&counters[e * n_kv + g], 1);
+    last_s = arrived == splits - 1;
+  }
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence();
+  const int n_active = min(splits, (n_keys + chunk - 1) / chunk);
+  for (int h0 = 0; h0 < group; h0 += ROWS) {
+    const int nh = min(ROWS, group - h0);
+    const size_t base0 = ((size_t)e * n_heads + g * group + h0) * splits;
+    __syncthreads();
+    for (int i = tid; i < nh * n_active; i += THREADS) {
+      const int h = i / n_active, sp = i % n_active;
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(partial_ml + (base0 + (size_t)h * splits + sp) * 2));
+      w_s[h][sp] = ml.x;
+      l_in[h][sp] = ml.y;
+    }
+    __syncthreads();
+    if (tid < nh) {
+      float m = -INFINITY;
+      for (int sp = 0; sp < n_active; ++sp) m = fmaxf(m, w_s[tid][sp]);
+      float l = 0.f;
+      for (int sp = 0; sp < n_active; ++sp) {
+        const float f = ex2(w_s[tid][sp] - m);
+        l += f * l_in[tid][sp];
+        w_s[tid][sp] = f;
+      }
+      const float inv = 1.f / l;
+      for (int sp = 0; sp < n_active; ++sp) w_s[tid][sp] *= inv;
+    }
+    __syncthreads();
+    for (int i = tid; i < nh * HS; i += THREADS) {
+      const int h = i / HS, d = i % HS;
+      const float* po = partial_o + (base0 + (size_t)h * splits) * HS + d;
+      float acc = 0.f;
+      int sp = 0;
+      for (; sp + 8 <= n_active; sp += 8) {
+        float ov[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) ov[u] = __ldcg(po + (size_t)(sp + u) * HS);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc = fmaf(w_s[h][sp + u], ov[u], acc);
+      }
+      for (; sp < n_active; ++sp) acc = fmaf(w_s[h][sp], __ldcg(po + (size_t)sp * HS), acc);
+      out[(size_t)e * out_stride + (size_t)(g * group + h0 + h) * HS + d] = __float2bfloat16_rn(acc);
+    }
+  }
+  if (tid == 0) counters[e * n_kv + g] = 0;
+}
+
+}  // namespace decode_mma

@@ -243,10 +243,10 @@ def _attn_partials(device, n_floats: int) -> torch.Tensor:
 
 
 def decode_splits(n_entries: int, n_kv: int, max_keys: int) -> int:
-    """How many ranges the keys of one request are cut into: many short ranges while the batch
-    is small (the kernel is bound by latency then), no range shorter than one round of 32 keys
-    at the longest context, all CTAs resident at once (about five per SM), at most 64."""
-    return max(1, min(64, _ceil_div(max_keys, 32), (_SMS * 5) // max(1, n_entries * n_kv)))
+    """How many ranges the keys of one request are cut into: ranges of about 128 keys (one tile
+    of 32 per warp of a CTA) while the batch is small and the kernel bound by latency, fewer
+    and longer ones once (requests x kv heads) alone fill the GPU; at most 64."""
+    return max(1, min(64, _ceil_div(max_keys, 128), (_SMS * 4) // max(1, n_entries * n_kv)))
 
 
 def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
