@@ -378,10 +378,37 @@ LLMK_API int llmk_paged_attention_decode(void* out, long long out_stride, const 
   if (dtype == LLMK_BF16 && (head_dim == 64 || head_dim == 128) && q_stride % 2 == 0 && (uintptr_t)q % 4 == 0) {
     // bfloat16 with a head size of 64 or 128: the query heads of a group as rows of warp-level MMAs
     dim3 grid(splits, n_kv, n_entries);
-    auto kern = head_dim == 64 ? decode_mma::decode_attention_mma_kernel<64> : decode_mma::decode_attention_mma_kernel<128>;
-    launch_kernel(kern, grid, dim3(decode_mma::THREADS), 0, stream, (__nv_bfloat16*)out, out_stride, scratch,
-                  (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
-                  block_table, table_width, kv_lens, n_heads, n_kv, page_size, window, scale * 1.4426950408889634f, splits);
+    const float scale_log2e = scale * 1.4426950408889634f;
+    const int group_rows = n_heads / n_kv < decode_mma::ROWS ? n_heads / n_kv : decode_mma::ROWS;
+    // 2 to 8 ranges whose shares fit the first CTA's buffers, and a grid of at most two waves:
+    // merge inside a cluster, no scratch.  (Measured at 64 requests, 512 CTAs: 30 us with
+    // clusters against 23 us with the counter-based merge; at 8 requests 9.3 us against 13.5 us.)
+    const bool cluster = splits >= 2 && splits <= 8 && (long long)splits * n_kv * n_entries <= 2 * 148 &&
+                         (splits - 1) * group_rows * head_dim * 4 <= 4 * decode_mma::TILE * head_dim * 2;
+    if (cluster) {
+      auto kern = head_dim == 64 ? decode_mma::decode_attention_mma_kernel<64, true> : decode_mma::decode_attention_mma_kernel<128, true>;
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = grid;
+      cfg.blockDim = dim3(decode_mma::THREADS);
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[2];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = splits;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[1].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = llmk_pdl_enabled() ? 2 : 1;
+      cudaLaunchKernelEx(&cfg, kern, (__nv_bfloat16*)out, out_stride, scratch, (const __nv_bfloat16*)q, q_stride,
+                         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, table_width, kv_lens,
+                         n_heads, n_kv, page_size, window, scale_log2e, splits);
+    } else {
+      auto kern = head_dim == 64 ? decode_mma::decode_attention_mma_kernel<64, false> : decode_mma::decode_attention_mma_kernel<128, false>;
+      launch_kernel(kern, grid, dim3(decode_mma::THREADS), 0, stream, (__nv_bfloat16*)out, out_stride, scratch,
+                    (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
+                    block_table, table_width, kv_lens, n_heads, n_kv, page_size, window, scale_log2e, splits);
+    }
     LLMK_LAUNCH_CHECK("attention_decode_mma");
   }
   return dispatch_dtype(dtype, [&](auto* tag) {

@@ -13,6 +13,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace decode_mma {
 
@@ -49,7 +50,12 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 
 // Scratch layout as in attention_decode.cu: counters, then ml [entries, heads, splits, 2] (the
 // maximum here in the base-2 domain of the pre-scaled scores), then o [entries, heads, splits, HS].
-template <int HS>
+//
+// CLUSTER: the CTAs of the ranges of one (request, kv head) form a thread-block cluster (2 to 8
+// along blockIdx.x).  They hand their results to the first CTA through distributed shared memory
+// and that CTA merges them: no scratch in global memory, no fence, no counter, and two cluster
+// barriers instead of three round trips to L2.
+template <int HS, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS)
 decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_stride, float* __restrict__ scratch,
                             const __nv_bfloat16* __restrict__ q, long long q_stride,
@@ -86,7 +92,8 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
   uint8_t* v_s = vbuf + warp * V_BYTES;
   const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(v_s);
 
-  for (int h0 = 0; h0 < group && k_begin < k_end; h0 += ROWS) {        // a range without keys only reports in
+  // a range without keys only reports in; in a cluster it still has to meet the others at the barriers
+  for (int h0 = 0; h0 < group && (CLUSTER || k_begin < k_end); h0 += ROWS) {
     const int nh = min(ROWS, group - h0);
     const int head0 = g * group + h0;
     // Q fragments: rows = heads, straight from global memory (4 bytes = 2 bf16 per load)
@@ -213,7 +220,12 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
       *reinterpret_cast<float2*>(wo + (qrow + 8) * HS + d * 8 + qcol) = make_float2(o[d][2], o[d][3]);
     }
     __syncthreads();
-    for (int i = tid; i < nh * HS; i += THREADS) {
+    constexpr int PER = ROWS * HS / THREADS;                      // output elements per thread
+    float racc[CLUSTER ? PER : 1], rm[CLUSTER ? PER : 1], rl[CLUSTER ? PER : 1];
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int i = tid + k * THREADS;
+      if (i >= nh * HS) break;
       const int h = i / HS, d = i % HS;
       float m = -INFINITY;
 #pragma unroll
@@ -228,7 +240,9 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
           acc += f * reinterpret_cast<const float*>(vbuf)[((size_t)w * ROWS + h) * HS + d];
         }
       }
-      if (splits == 1) {
+      if (CLUSTER) {
+        racc[CLUSTER ? k : 0] = acc; rm[CLUSTER ? k : 0] = m; rl[CLUSTER ? k : 0] = l;
+      } else if (splits == 1) {
         out[(size_t)e * out_stride + (size_t)(head0 + h) * HS + d] = __float2bfloat16_rn(acc / l);
       } else {
         partial_o[(((size_t)e * n_heads + head0 + h) * splits + split) * HS + d] = acc;
@@ -239,9 +253,50 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
         }
       }
     }
+    if (CLUSTER) {
+      // every CTA of the cluster has its share in registers; after the first barrier the first
+      // CTA's buffers are free to receive the others' shares
+      const uint32_t rank = tc::cluster_ctarank();
+      const uint32_t slots = tc::map_to_cta((uint32_t)__cvta_generic_to_shared(vbuf), 0);
+      const uint32_t m_remote = tc::map_to_cta((uint32_t)__cvta_generic_to_shared(&w_s[0][0]), 0);
+      const uint32_t l_remote = tc::map_to_cta((uint32_t)__cvta_generic_to_shared(&l_in[0][0]), 0);
+      tc::cluster_sync();
+#pragma unroll
+      for (int k = 0; k < PER; ++k) {
+        const int i = tid + k * THREADS;
+        if (i >= nh * HS) break;
+        const int h = i / HS, d = i % HS;
+        if (rank != 0 && rm[k] > -INFINITY) tc::st_cluster_f32(slots + (uint32_t)(((rank - 1) * nh + h) * HS + d) * 4u, racc[k]);
+        if (d == 0) {
+          tc::st_cluster_f32(m_remote + (uint32_t)(h * 64 + rank) * 4u, rm[k]);
+          tc::st_cluster_f32(l_remote + (uint32_t)(h * 64 + rank) * 4u, rl[k]);
+        }
+      }
+      tc::cluster_sync();
+      if (rank == 0) {
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+          const int i = tid + k * THREADS;
+          if (i >= nh * HS) break;
+          const int h = i / HS, d = i % HS;
+          float m = -INFINITY;
+          for (int r = 0; r < splits; ++r) m = fmaxf(m, w_s[h][r]);
+          float l = 0.f, acc = 0.f;
+          for (int r = 0; r < splits; ++r) {                      // in the order of the ranges
+            const float mr = w_s[h][r];
+            if (mr > -INFINITY) {
+              const float f = ex2(mr - m);
+              l += f * l_in[h][r];
+              acc += f * (r == 0 ? racc[k] : reinterpret_cast<const float*>(vbuf)[((size_t)(r - 1) * nh + h) * HS + d]);
+            }
+          }
+          out[(size_t)e * out_stride + (size_t)(head0 + h) * HS + d] = __float2bfloat16_rn(acc / l);
+        }
+      }
+    }
     __syncthreads();                                              // vbuf is reused by the next pass
   }
-  if (splits == 1) return;
+  if (splits == 1 || CLUSTER) return;
 
   // ---- the last range to arrive merges all of them ----
   __threadfence();
