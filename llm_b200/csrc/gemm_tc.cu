@@ -330,6 +330,178 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   }
 }
 
+// ---- persistent variant for many rows ---------------------------------------------------
+// One CTA per SM walks over the output tiles (blockIdx.x, + gridDim.x, ...).  The accumulator is
+// double-buffered in tensor memory (2 x 256 columns), so the epilogue of one tile (tensor memory
+// -> registers -> global) runs while the MMA thread already works on the next tile; the stage
+// ring keeps running across tiles.  Tiles are numbered with the row tile fastest, so CTAs that
+// run at the same time share the same few weight tiles in L2.  Normal mode only (P = rows of A).
+enum : int { ERR_P_PRODUCER = 4, ERR_P_MMA = 5, ERR_P_EPILOGUE = 6 };
+
+template <typename TOut>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                          TOut* __restrict__ C, long long ldc, int M, int N, int K, int tile_q,
+                          int* __restrict__ err_flag) {
+  constexpr int BNQ = 256;
+  constexpr int STAGES = stages_for(BNQ);
+  constexpr int Q_STAGE_BYTES = q_stage_bytes(BNQ);
+  constexpr uint32_t TMEM_COLS = 512;
+  const uint32_t IDESC = idesc_bf16_f32(BP, tile_q);
+  const uint32_t stage_tx = (uint32_t)(P_STAGE_BYTES + tile_q * BK * 2);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem_p = smem;
+  uint8_t* smem_q = smem + STAGES * P_STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * (P_STAGE_BYTES + Q_STAGE_BYTES));
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;       // [2] MMA -> epilogue
+  uint64_t* acc_empty = acc_full + 2;            // [2] epilogue -> MMA (four warps arrive)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (M + BP - 1) / BP, n_tiles = (N + tile_q - 1) / tile_q;
+  const int total_tiles = m_tiles * n_tiles;
+  const int nkb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);
+    }
+    fence_mbar_init();
+    prefetch_tensormap(&map_p);
+    prefetch_tensormap(&map_q);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  pdl_launch_dependents();
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- producer ----
+      pdl_wait();
+      bool ok = true;
+      int it = 0;                                             // k-blocks issued so far, over all tiles
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int p0 = (tile % m_tiles) * BP, q0 = (tile / m_tiles) * tile_q;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&full_bar[s], stage_tx);
+          tma_load_2d(smem_q + s * Q_STAGE_BYTES, &map_q, kb * BK, q0, &full_bar[s]);
+          tma_load_2d(smem_p + s * P_STAGE_BYTES, &map_p, kb * BK, p0, &full_bar[s]);
+        }
+      }
+      if (!ok) {
+        atomicExch(err_flag, ERR_P_PRODUCER);
+        for (int i = max(0, it - STAGES); i < it; ++i) mbar_wait(&full_bar[i % STAGES], (i / STAGES) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer ----
+      bool ok = true;
+      int it = 0, n = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++n) {
+        const int buf = n & 1;
+        ok = mbar_wait(&acc_empty[buf], ((n >> 1) & 1) ^ 1);   // the epilogue has drained this accumulator
+        if (!ok) break;
+        fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BNQ);
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(&full_bar[s], (it / STAGES) & 1);
+          if (!ok) break;
+          fence_after_sync();
+          const uint64_t desc_p = smem_desc_sw128(smem_u32(smem_p + s * P_STAGE_BYTES));
+          const uint64_t desc_q = smem_desc_sw128(smem_u32(smem_q + s * Q_STAGE_BYTES));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) mma_bf16(d_tmem, desc_p + 2 * k, desc_q + 2 * k, IDESC, (kb | k) != 0);
+          mma_commit(&empty_bar[s]);
+        }
+        mma_commit(&acc_full[buf]);
+      }
+      if (!ok) {
+        atomicExch(err_flag, ERR_P_MMA);
+        mma_commit(&acc_full[0]);
+        mma_commit(&acc_full[1]);
+      }
+    }
+  } else {
+    // ---- epilogue ----
+    const int quad = warp & 3;
+    bool ok = true;
+    int n = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++n) {
+      const int buf = n & 1;
+      const int p0 = (tile % m_tiles) * BP, q0 = (tile / m_tiles) * tile_q;
+      const int p = p0 + quad * 32 + lane;
+      if (ok) ok = mbar_wait(&acc_full[buf], (n >> 1) & 1);
+      fence_after_sync();
+#pragma unroll 1
+      for (int c = 0; c < tile_q; c += 32) {
+        float v[32];
+        if (ok) {
+          uint32_t r[32];
+          tmem_ld_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BNQ + c), r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+        if (p >= M) continue;
+        const int q = q0 + c;
+        TOut* row = C + (long long)p * ldc + q;
+        const bool vec_ok = (q + 32 <= N) && ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
+        if (vec_ok) {
+          if (sizeof(TOut) == 2) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 u;
+              __nv_bfloat162 b0 = __floats2bfloat162_rn(v[j], v[j + 1]), b1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+              __nv_bfloat162 b2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), b3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+              u.x = *reinterpret_cast<uint32_t*>(&b0); u.y = *reinterpret_cast<uint32_t*>(&b1);
+              u.z = *reinterpret_cast<uint32_t*>(&b2); u.w = *reinterpret_cast<uint32_t*>(&b3);
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(row) + j) = u;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4*>(reinterpret_cast<float*>(row) + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (q + j < N) store_one(row + j, v[j]);
+        }
+      }
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);             // this warp has read its lanes of the accumulator
+    }
+    if (!ok && lane == 0) atomicExch(err_flag, ERR_P_EPILOGUE);
+  }
+
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 // ---- host side ----------------------------------------------------------------
 struct MapKey {
   const void* base; uint64_t rows, cols, ld; uint32_t box;
@@ -406,6 +578,23 @@ int launch_cfg(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long 
 }
 
 template <typename TOut>
+int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long ldc, int M, int N, int K,
+                      int tile_q, cudaStream_t stream) {
+  auto kern = gemm_tc_persistent_kernel<TOut>;
+  constexpr int smem = smem_bytes_for(256);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return llmk_fail((int)e, "gemm_tc: cannot set %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int tiles = ((M + BP - 1) / BP) * ((N + tile_q - 1) / tile_q);
+  launch_kernel(kern, dim3(tiles < 148 ? tiles : 148), dim3(THREADS), (size_t)smem, stream, mp, mq, (TOut*)C, ldc, M, N, K,
+                tile_q, g_err_flag);
+  LLMK_LAUNCH_CHECK("gemm_tc_persistent");
+}
+
+template <typename TOut>
 int launch_out(bool swap, int bnq, bool cluster, const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long ldc,
                long long split_stride, int M, int N, int K, int splits, int kbps, cudaStream_t s) {
   if (swap && cluster) {
@@ -444,6 +633,8 @@ LLMK_API int llmk_gemm_tc_supported(const void* A, const void* W, int M, int N, 
 // (split_stride = M * ldc elements) over kblocks_per_split blocks of 64 along K each.
 // splits > 1 with cluster != 0 (swapped mode, tile up to 64, at most 8 splits): the splits of a
 // tile form a thread-block cluster, sum their results on chip and write C as for splits == 1.
+// cluster == 2 selects the persistent kernel (normal mode, one split): one CTA per SM walks over
+// the tiles with two accumulators in tensor memory.
 // swap != 0 puts the weights on the 128-row side of the MMA; tile is the other side's width
 // (16, 32, 64 or 128 when swapped; a multiple of 32 up to 256 otherwise).
 LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
@@ -453,9 +644,9 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
   LLMK_REQUIRE(llmk_gemm_tc_supported(A, W, M, N, K, lda, ldw), "gemm_tc: K=%d and the row pitches must be multiples of 8 and the bases 16-byte aligned", K);
   LLMK_REQUIRE(splits >= 1 && kblocks_per_split >= 1 && (long long)splits * kblocks_per_split * BK >= K,
                "gemm_tc: %d splits of %d k-blocks do not cover K=%d", splits, kblocks_per_split, K);
-  if (splits == 1) cluster = 0;
+  if (splits == 1 && cluster == 1) cluster = 0;
   LLMK_REQUIRE(splits == 1 || cluster || out_dtype == LLMK_F32, "gemm_tc: split-K without a cluster needs a float32 output");
-  if (cluster) {
+  if (cluster == 1) {
     LLMK_REQUIRE(swap && tile <= 64 && splits <= 8, "gemm_tc: cluster reduction needs the swapped mode, a tile up to 64 and at most 8 splits");
     LLMK_REQUIRE((long long)(splits - 1) * tile * BP * 4 <= (long long)stages_for(tile) * (P_STAGE_BYTES + q_stage_bytes(tile)),
                  "gemm_tc: %d splits of a %d-row tile do not fit the stage ring for the on-chip sum", splits, tile);
@@ -469,6 +660,13 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
   const int p_rows = swap ? N : M, q_rows = swap ? M : N;
   if ((rc = get_map(&mp, P, p_rows, K, ldp, BP))) return rc;
   if ((rc = get_map(&mq, Q, q_rows, K, ldq, tile))) return rc;
+  if (cluster == 2) {       // persistent kernel: normal mode, no split
+    LLMK_REQUIRE(!swap && splits == 1 && tile % 32 == 0 && tile >= 32 && tile <= 256,
+                 "gemm_tc: the persistent kernel takes the normal mode, one split and a tile of 32..256 in steps of 32");
+    if (out_dtype == LLMK_F32) return launch_persistent<float>(mp, mq, C, ldc, M, N, K, tile, stream);
+    if (out_dtype == LLMK_BF16) return launch_persistent<__nv_bfloat16>(mp, mq, C, ldc, M, N, K, tile, stream);
+    return llmk_fail(-1, "gemm_tc: unsupported output kind %d", out_dtype);
+  }
   const long long split_stride = (splits > 1 && !cluster) ? (long long)M * ldc : 0;
   if (out_dtype == LLMK_F32) return launch_out<float>(swap != 0, tile, cluster != 0, mp, mq, C, ldc, split_stride, M, N, K, splits, kblocks_per_split, stream);
   if (out_dtype == LLMK_BF16) return launch_out<__nv_bfloat16>(swap != 0, tile, cluster != 0, mp, mq, C, ldc, split_stride, M, N, K, splits, kblocks_per_split, stream);

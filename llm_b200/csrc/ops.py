@@ -343,8 +343,12 @@ def cluster_fits(tile: int, splits: int) -> bool:
     return tile in _RING_BYTES and 2 <= splits <= 8 and (splits - 1) * tile * 128 * 4 <= _RING_BYTES[tile]
 
 
+PERSISTENT_GEMM = True
+
+
 def plan_gemm(M: int, N: int, K: int, fused_reduce: bool = False):
-    """(swap, tile, splits, k-blocks per split, cluster) for the tensor-core product.
+    """(swap, tile, splits, k-blocks per split, mode) for the tensor-core product; mode 0 = one
+    CTA per tile, 1 = the splits of a tile sum on chip in a cluster, 2 = persistent CTAs.
 
     Up to 128 rows the weights take the 128-row side of the MMA and the rows become its N
     (16 to 128); above that the rows take the 128-row side and the tile is 128 or 256 weight
@@ -372,12 +376,17 @@ def plan_gemm(M: int, N: int, K: int, fused_reduce: bool = False):
             # On-chip sums through a cluster measured slower at decode sizes than partial results plus
             # a reduction kernel: a cluster needs all its CTAs scheduled at once, which takes away
             # the early start of the next product's weight loads.  Kept as an option of gemm_fast.
-            cluster = False
+            cluster = 0
             if s > 1 and not cluster and s * M * N * 4 > _PARTIAL_BYTES:
                 break
             waves = _ceil_div(tiles * s, _SMS)
             cost = waves * (per * t_kb + 2.5)
-            if cluster:
+            if PERSISTENT_GEMM and not swap and s == 1 and tiles > _SMS:
+                # more than one wave of tiles: one CTA per SM walks over them and drains one
+                # accumulator while the next tile's products run, so the fixed cost is paid once
+                cluster = 2
+                cost = waves * per * t_kb + 2.5
+            if cluster == 1:
                 cost += 0.8
             elif s > 1:
                 traffic = (2 * s + 1) * M * N * 4 / 4e6               # partials written and read back, us
@@ -413,7 +422,7 @@ def gemm_fast(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, pl
     assert a.shape[1] == k and out.shape[1] == n
     plan = plan or plan_gemm(rows, n, k, fused_reduce=allow_partial)
     swap, tile, splits, per = plan[:4]
-    cluster = bool(plan[4]) if len(plan) > 4 else False
+    cluster = int(plan[4]) if len(plan) > 4 else 0
     lib = load()
     if splits == 1 or cluster:
         _check(lib.llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
