@@ -48,6 +48,25 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+// Two adjacent values (idx even): of a tensor, or the sums in split order of split-K partial
+// results, with the loads of up to eight splits in flight (a split past the last adds zero).
+__device__ __forceinline__ float2 sum2(const MaybePartial<__nv_bfloat16>& s, size_t idx) {
+  if (s.parts) {
+    float2 acc = make_float2(0.f, 0.f);
+    for (int sp = 0; sp < s.splits; sp += 8) {
+      float2 t[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        t[u] = sp + u < s.splits ? *reinterpret_cast<const float2*>(s.parts + (size_t)(sp + u) * s.split_stride + idx)
+                                 : make_float2(0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) { acc.x += t[u].x; acc.y += t[u].y; }
+    }
+    return acc;
+  }
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(s.direct + idx));
+}
+
 // Scratch layout as in attention_decode.cu: counters, then ml [entries, heads, splits, 2] (the
 // maximum here in the base-2 domain of the pre-scaled scores), then o [entries, heads, splits, HS].
 //
@@ -55,13 +74,29 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 // along blockIdx.x).  They hand their results to the first CTA through distributed shared memory
 // and that CTA merges them: no scratch in global memory, no fence, no counter, and two cluster
 // barriers instead of three round trips to L2.
-template <int HS, bool CLUSTER>
+//
+// FUSED: the kernel takes the row of the QKV product itself (a tensor or unsummed split-K
+// partial results) instead of rotated queries.  Every CTA sums and rotates its group's queries
+// into shared memory; the CTA whose range holds the newest position also sums and rotates that
+// token's key, stores key and value in the pages (unless the layer reads another layer's
+// pages) and keeps a copy in shared memory for its own use.  This replaces the separate
+// rotate-and-store kernel of a decode step.
+struct FusedQkv {
+  MaybePartial<__nv_bfloat16> src;     // [entries, src_stride]: q heads, then k heads, then v heads
+  long long src_stride;
+  const float* cos_table;              // [max_position, HS/2], or null: nothing is rotated
+  const float* sin_table;
+  int write_kv;
+};
+
+template <int HS, bool CLUSTER, bool FUSED>
 __global__ void __launch_bounds__(THREADS)
 decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_stride, float* __restrict__ scratch,
                             const __nv_bfloat16* __restrict__ q, long long q_stride,
-                            const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
+                            __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
                             const int* __restrict__ block_table, int table_width, const int* __restrict__ kv_lens,
-                            int n_heads, int n_kv, int page_size, int window, float scale_log2e, int splits) {
+                            int n_heads, int n_kv, int page_size, int window, float scale_log2e, int splits,
+                            FusedQkv fused) {
   constexpr int KS = HS / 16;                  // k-steps of Q K^T
   constexpr int DT = HS / 8;                   // 8-wide tiles of the output row
   constexpr int CH = HS / 8;                   // 16-byte chunks of a row
@@ -70,9 +105,10 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
   __shared__ float wm_s[4][ROWS], wl_s[4][ROWS];
   __shared__ float w_s[ROWS][64], l_in[ROWS][64];        // merge: per (head, range)
   __shared__ int last_s;
+  __shared__ __align__(16) __nv_bfloat16 q_s[FUSED ? ROWS * HS : 8];
+  __shared__ __align__(16) __nv_bfloat16 kv_new_s[FUSED ? 2 * HS : 8];    // the newest key, then the newest value
 
   pdl_launch_dependents();
-  pdl_wait();
   const int split = blockIdx.x, g = blockIdx.y, e = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = n_heads / n_kv;
@@ -85,12 +121,85 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
   const int k_end = min(pos + 1, k_begin + chunk);
   const int* table = block_table + (size_t)e * table_width;
   const int qrow = lane >> 2, qcol = (lane & 3) * 2;
+  uint8_t* v_s = vbuf + warp * V_BYTES;
+  const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(v_s);
+  const int t_first = k_begin + warp * TILE;                // this warp's first tile
+
+  // stage a tile's values: 32 rows of CH chunks, swizzled by the row
+  auto stage_values = [&](int t) {
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const int idx = i * 32 + lane;
+      const int kl = idx / CH, c = idx % CH;
+      const int kp = t + kl;
+      const bool valid = kp < k_end;
+      const int kq = valid ? kp : k_begin;
+      const size_t row = (((size_t)table[kq / page_size] * n_kv + g) * page_size + kq % page_size) * HS;
+      const int cs = (c & ~7) | ((c ^ kl) & 7);
+      cp_async_16(v_addr + kl * (HS * 2) + cs * 16, v_pages + row + c * 8, valid);
+    }
+  };
+  // a tile's keys: fragments straight from the pages
+  uint32_t kf[4][KS][2];
+  auto load_keys = [&](int t) {
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int kp = t + nt * 8 + qrow;
+      const int kq = kp < k_end ? kp : k_begin;
+      const __nv_bfloat16* kr = k_pages + (((size_t)table[kq / page_size] * n_kv + g) * page_size + kq % page_size) * HS;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        kf[nt][ks][0] = *reinterpret_cast<const uint32_t*>(kr + ks * 16 + qcol);
+        kf[nt][ks][1] = *reinterpret_cast<const uint32_t*>(kr + ks * 16 + 8 + qcol);
+      }
+    }
+  };
+
+  // Lengths and block tables were copied before the step's first kernel, and every key but the
+  // newest was stored by an earlier step.  So each warp fetches the keys and values of its first
+  // tile, and the CTA requests the rest of its range into L2, while the kernels before this one
+  // still run; only the queries and the newest key and value (stored by a kernel of this step,
+  // or by this one) have to wait.  The newest row of a tile fetched early is replaced below.
+  bool early = t_first < k_end;
+  if (early) {
+    stage_values(t_first);
+    load_keys(t_first);
+  }
+  {
+    constexpr int LINES = HS * 2 / 128;                    // 128-byte lines per row
+    const int n_rows = max(0, k_end - k_begin - 4 * TILE);
+    for (int i = tid; i < n_rows * LINES * 2; i += THREADS) {
+      const int which = i & 1, line = (i >> 1) % LINES, kp = k_begin + 4 * TILE + (i >> 1) / LINES;
+      const size_t row = (((size_t)table[kp / page_size] * n_kv + g) * page_size + kp % page_size) * HS;
+      const __nv_bfloat16* src = (which ? v_pages : k_pages) + row + line * 64;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
+    }
+  }
+  pdl_wait();
+
+  // the newest key and value are read, once they are valid, from the pages, or from this CTA's
+  // shared copy when it computes them itself
+  const size_t new_row = (((size_t)table[pos / page_size] * n_kv + g) * page_size + pos % page_size) * HS;
+  const bool owner = FUSED && fused.write_kv && k_begin <= pos && pos < k_end;
+  // FUSED, owner: the last threads sum the newest token's key (two pairs each) and value (two
+  // elements each); their loads are issued here and used after the queries' loads below
+  const int kv_item = THREADS - 1 - tid;
+  const bool does_k = owner && kv_item < HS / 4, does_v = owner && !does_k && kv_item < HS / 4 + HS / 2;
+  float2 nk_a = make_float2(0.f, 0.f), nk_b = nk_a, nv = nk_a;
+  if (FUSED) {
+    const size_t src_row = (size_t)e * fused.src_stride;
+    if (does_k) {
+      const size_t h = src_row + (size_t)(n_heads + g) * HS + kv_item * 2;
+      nk_a = sum2(fused.src, h);
+      nk_b = sum2(fused.src, h + HS / 2);
+    } else if (does_v) {
+      nv = sum2(fused.src, src_row + (size_t)(n_heads + n_kv + g) * HS + (kv_item - HS / 4) * 2);
+    }
+  }
 
   int* counters = reinterpret_cast<int*>(scratch);
   float* partial_ml = scratch + COUNTER_WORDS;
   float* partial_o = partial_ml + (size_t)gridDim.z * n_heads * splits * 2;
-  uint8_t* v_s = vbuf + warp * V_BYTES;
-  const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(v_s);
 
   // a range without keys only reports in; in a cluster it still has to meet the others at the barriers
   for (int h0 = 0; h0 < group && (CLUSTER || k_begin < k_end); h0 += ROWS) {
@@ -98,8 +207,59 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
     const int head0 = g * group + h0;
     // Q fragments: rows = heads, straight from global memory (4 bytes = 2 bf16 per load)
     uint32_t qf[KS][4];
+    const __nv_bfloat16* q0;
+    if (FUSED) {
+      // the pass's queries: summed, rotated, rounded to bfloat16 into shared memory; two pairs
+      // (i, i+1 and their partners half a head further) per item, all loads issued before any use
+      constexpr int ITEMS = ROWS * (HS / 4) / THREADS;
+      float2 qa[ITEMS], qb[ITEMS], qc[ITEMS], qs[ITEMS];
+#pragma unroll
+      for (int it = 0; it < ITEMS; ++it) {
+        const int idx = tid + it * THREADS;
+        if (idx < nh * (HS / 4)) {
+          const int h = idx / (HS / 4), i = (idx % (HS / 4)) * 2;
+          const size_t src = (size_t)e * fused.src_stride + (size_t)(head0 + h) * HS + i;
+          qa[it] = sum2(fused.src, src);
+          qb[it] = sum2(fused.src, src + HS / 2);
+          qc[it] = fused.cos_table ? *reinterpret_cast<const float2*>(fused.cos_table + (size_t)pos * (HS / 2) + i) : make_float2(1.f, 1.f);
+          qs[it] = fused.cos_table ? *reinterpret_cast<const float2*>(fused.sin_table + (size_t)pos * (HS / 2) + i) : make_float2(0.f, 0.f);
+        }
+      }
+      if (h0 == 0 && (does_k || does_v)) {
+        if (does_k) {
+          const int i = kv_item * 2;
+          const float2 c = fused.cos_table ? *reinterpret_cast<const float2*>(fused.cos_table + (size_t)pos * (HS / 2) + i) : make_float2(1.f, 1.f);
+          const float2 sn = fused.cos_table ? *reinterpret_cast<const float2*>(fused.sin_table + (size_t)pos * (HS / 2) + i) : make_float2(0.f, 0.f);
+          const __nv_bfloat162 ya = __floats2bfloat162_rn(nk_a.x * c.x - nk_b.x * sn.x, nk_a.y * c.y - nk_b.y * sn.y);
+          const __nv_bfloat162 yb = __floats2bfloat162_rn(nk_a.x * sn.x + nk_b.x * c.x, nk_a.y * sn.y + nk_b.y * c.y);
+          *reinterpret_cast<__nv_bfloat162*>(k_pages + new_row + i) = ya;
+          *reinterpret_cast<__nv_bfloat162*>(k_pages + new_row + i + HS / 2) = yb;
+          *reinterpret_cast<__nv_bfloat162*>(kv_new_s + i) = ya;
+          *reinterpret_cast<__nv_bfloat162*>(kv_new_s + i + HS / 2) = yb;
+        } else {
+          const int d = (kv_item - HS / 4) * 2;
+          const __nv_bfloat162 x = __floats2bfloat162_rn(nv.x, nv.y);
+          *reinterpret_cast<__nv_bfloat162*>(v_pages + new_row + d) = x;
+          *reinterpret_cast<__nv_bfloat162*>(kv_new_s + HS + d) = x;
+        }
+      }
+#pragma unroll
+      for (int it = 0; it < ITEMS; ++it) {
+        const int idx = tid + it * THREADS;
+        if (idx < nh * (HS / 4)) {
+          const int h = idx / (HS / 4), i = (idx % (HS / 4)) * 2;
+          const float2 a = qa[it], b = qb[it], c = qc[it], sn = qs[it];
+          *reinterpret_cast<__nv_bfloat162*>(q_s + h * HS + i) = __floats2bfloat162_rn(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y);
+          *reinterpret_cast<__nv_bfloat162*>(q_s + h * HS + i + HS / 2) = __floats2bfloat162_rn(a.x * sn.x + b.x * c.x, a.y * sn.y + b.y * c.y);
+        }
+      }
+      __syncthreads();                  // queries, and the owner's newest key and value, in shared memory
+      q0 = q_s + qrow * HS;
+    } else {
+      q0 = q + (size_t)e * q_stride + (size_t)(head0 + qrow) * HS;
+    }
     {
-      const __nv_bfloat16* q0 = q + (size_t)e * q_stride + (size_t)(head0 + qrow) * HS;
+      // Q fragments: rows = heads (4 bytes = 2 bf16 per load)
       const __nv_bfloat16* q1 = q0 + 8 * HS;
       const bool r0 = qrow < nh, r1 = qrow + 8 < nh;
 #pragma unroll
@@ -115,31 +275,41 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
     for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;        // rows qrow and qrow + 8 (l: this lane's share)
 
-    for (int t = k_begin + warp * TILE; t < k_end; t += 4 * TILE) {
-      // ---- stage the tile's values: 32 rows of CH chunks, swizzled by the row ----
-#pragma unroll
-      for (int i = 0; i < CH; ++i) {
-        const int idx = i * 32 + lane;
-        const int kl = idx / CH, c = idx % CH;
-        const int kp = t + kl;
-        const bool valid = kp < k_end;
-        const int kq = valid ? kp : k_begin;
-        const size_t row = (((size_t)table[kq / page_size] * n_kv + g) * page_size + kq % page_size) * HS;
-        const int cs = (c & ~7) | ((c ^ kl) & 7);
-        cp_async_16(v_addr + kl * (HS * 2) + cs * 16, v_pages + row + c * 8, valid);
+    for (int t = t_first; t < k_end; t += 4 * TILE) {
+      if (!(early && t == t_first)) {                             // else: fetched before the wait
+        stage_values(t);
+        load_keys(t);
       }
-      // ---- keys: fragments straight from the pages ----
-      uint32_t kf[4][KS][2];
+      if (pos < t + TILE) {                                       // pos >= t: the range ends at pos
+        // The newest row: not valid when a tile was fetched early, and a copy of its line from
+        // before may sit in this SM's L1.  It is read again from the CTA's own copy, or from L2.
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        const int kp = t + nt * 8 + qrow;
-        const int kq = kp < k_end ? kp : k_begin;
-        const __nv_bfloat16* kr = k_pages + (((size_t)table[kq / page_size] * n_kv + g) * page_size + kq % page_size) * HS;
+        for (int nt = 0; nt < 4; ++nt) {
+          if (t + nt * 8 + qrow == pos) {
 #pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-          kf[nt][ks][0] = *reinterpret_cast<const uint32_t*>(kr + ks * 16 + qcol);
-          kf[nt][ks][1] = *reinterpret_cast<const uint32_t*>(kr + ks * 16 + 8 + qcol);
+            for (int ks = 0; ks < KS; ++ks) {
+              if (owner) {
+                kf[nt][ks][0] = *reinterpret_cast<const uint32_t*>(kv_new_s + ks * 16 + qcol);
+                kf[nt][ks][1] = *reinterpret_cast<const uint32_t*>(kv_new_s + ks * 16 + 8 + qcol);
+              } else {
+                kf[nt][ks][0] = __ldcg(reinterpret_cast<const uint32_t*>(k_pages + new_row + ks * 16 + qcol));
+                kf[nt][ks][1] = __ldcg(reinterpret_cast<const uint32_t*>(k_pages + new_row + ks * 16 + 8 + qcol));
+              }
+            }
+          }
         }
+        uint4 v_row = make_uint4(0u, 0u, 0u, 0u);
+        if (lane < CH)
+          v_row = owner ? *reinterpret_cast<const uint4*>(kv_new_s + HS + lane * 8)
+                        : __ldcg(reinterpret_cast<const uint4*>(v_pages + new_row + lane * 8));
+        cp_async_wait_all();
+        __syncwarp();
+        if (lane < CH) {
+          const int kl = pos - t;
+          const int cs = (lane & ~7) | ((lane ^ kl) & 7);
+          *reinterpret_cast<uint4*>(v_s + kl * (HS * 2) + cs * 16) = v_row;
+        }
+        __syncwarp();
       }
       // ---- S = Q K^T ----
       float s[4][4];
@@ -202,6 +372,7 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
       }
       __syncwarp();                                               // the values are consumed before the next tile lands
     }
+    early = false;                                                // a later pass fetches its tiles again
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);

@@ -271,6 +271,46 @@ def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Te
         c_void_p(buf.data_ptr()), c_int(_kind(q.dtype)), _stream()))
 
 
+def decode_attention_fused_supported(qkv, cos, sin, head_dim: int) -> bool:
+    """Whether one kernel can rotate, store and attend for a decode step: bfloat16, head size 64
+    or 128, rows that start on 16-byte boundaries."""
+    if qkv.dtype != torch.bfloat16:
+        return False
+    d, parts, _, stride = _split_args(qkv)
+    src_stride = qkv.cols if isinstance(qkv, PartialSum) else qkv.stride(0)
+    return bool(load().llmk_decode_attention_fused_supported(d, parts, stride, c_longlong(src_stride), _ptr(cos),
+                                                             _ptr(sin), c_int(head_dim), c_int(_BF16)))
+
+
+def decode_attention_fused(out: torch.Tensor, qkv, cos, sin, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                           block_table: torch.Tensor, kv_lens: torch.Tensor, n_entries: int, n_heads: int,
+                           n_kv: int, head_dim: int, window: int, scale: float, write_kv: bool = True,
+                           splits=None) -> None:
+    """One new token per entry: row e of qkv (a tensor or a PartialSum) holds its q, k and v
+    heads (q alone if not write_kv).  q and k are rotated at position kv_lens[e] - 1, k and v are
+    stored there in the entry's pages, and the token attends to its request's kv_lens[e] keys."""
+    _rows_contig(out, "out")
+    assert block_table.dim() == 2 and block_table.is_contiguous() and block_table.dtype == torch.int32
+    assert kv_lens.dtype == torch.int32 and k_pages.is_contiguous() and v_pages.is_contiguous()
+    assert qkv.dtype == k_pages.dtype == out.dtype == torch.bfloat16
+    page = k_pages.shape[2]
+    if splits is None:
+        splits = decode_splits(n_entries, n_kv, block_table.shape[1] * page)
+    lib = load()
+    lib.llmk_paged_attention_decode_scratch.restype = c_longlong
+    need = lib.llmk_paged_attention_decode_scratch(c_int(n_entries), c_int(n_heads), c_int(head_dim), c_int(splits))
+    buf = _attn_partials(out.device, int(need))
+    d, parts, qkv_splits, stride = _split_args(qkv)
+    src_stride = qkv.cols if isinstance(qkv, PartialSum) else qkv.stride(0)
+    if isinstance(qkv, PartialSum):
+        assert qkv.rows == n_entries
+    _check(lib.llmk_decode_attention_fused(
+        _ptr(out), c_longlong(out.stride(0)), d, parts, qkv_splits, stride, c_longlong(src_stride), _ptr(cos),
+        _ptr(sin), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), c_int(block_table.shape[1]), _ptr(kv_lens),
+        c_int(n_entries), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(page), c_int(window or 0),
+        c_float(scale), c_int(splits), c_int(int(write_kv)), c_void_p(buf.data_ptr()), _stream()))
+
+
 def attention_tc_supported(dtype, n_heads: int, n_kv: int, head_dim: int, page_size: int) -> bool:
     """Whether the tcgen05 attention takes these sizes (bfloat16, head size 64 or 128, pages
     of 16 to 128 tokens, at most 128 query heads per kv head)."""
@@ -321,6 +361,30 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
         return
     paged_attention_generic(out, qkv, k_pages, v_pages, group.block_table, ctx.token_entry, ctx.positions,
                             ctx.n_tokens, n_heads, n_kv, head_dim, window, scale)
+
+
+FUSE_DECODE_ATTENTION = True
+
+
+def rope_store_attend(out, qkv, cos, sin, k_pages, v_pages, group, ctx, n_heads: int, n_kv: int, head_dim: int,
+                      window: int, scale: float, write_kv: bool, q_rot) -> None:
+    """The three steps between the QKV product and the output projection: rotate q and k by the
+    tables, store k and v in the pages (if write_kv), attend.  qkv is a tensor or a PartialSum;
+    q_rot() gives a buffer for rotated queries when they cannot stay where they are.  A decode
+    step in bfloat16 with a head size of 64 or 128 runs as one kernel, everything else as the
+    rotate-and-store kernel followed by the attention kernel that fits the batch."""
+    if (FUSE_DECODE_ATTENTION and ctx.decode_only and ctx.n_tokens == ctx.n_entries
+            and decode_attention_fused_supported(qkv, cos, sin, head_dim)):
+        max_keys = min(ctx.kv_bucket or 1 << 30, group.block_table.shape[1] * k_pages.shape[2])
+        if window:
+            max_keys = min(max_keys, window)
+        decode_attention_fused(out, qkv, cos, sin, k_pages, v_pages, group.block_table, ctx.kv_lens, ctx.n_entries,
+                               n_heads, n_kv, head_dim, window, scale, write_kv=write_kv,
+                               splits=decode_splits(ctx.n_entries, n_kv, max_keys))
+        return
+    q = rope_kv_write(qkv, cos, sin, ctx.positions, group.slot_map, k_pages, v_pages, ctx.n_tokens, n_heads,
+                      n_kv if write_kv else 0, head_dim, q_out=q_rot() if isinstance(qkv, PartialSum) else None)
+    paged_attention(out, q, k_pages, v_pages, group, ctx, n_heads, n_kv, head_dim, window, scale)
 
 
 # ---- tensor-core product ------------------------------------------------------------

@@ -71,14 +71,12 @@ class PagedAttention(Part):
         cos = sin = None
         if self.position is not None:
             cos, sin = self.position.tables()
-        n_kv_written = 0 if self.shares_cache else self.num_kv_heads
         k_pages, v_pages = view.k_pages, view.v_pages
-        q_out = ws.get("q_rot", T, self.q_size, self.dtype) if isinstance(qkv, ops.PartialSum) else None
-        q = ops.rope_kv_write(qkv, cos, sin, ctx.positions, view.group.slot_map, k_pages, v_pages, T,
-                              self.num_heads, n_kv_written, self.head_dim, q_out=q_out)
         attn = ws.get("attn_out", T, self.q_size, self.dtype)
-        ops.paged_attention(attn, q, k_pages, v_pages, view.group, ctx, self.num_heads,
-                            k_pages.shape[1], self.head_dim, self.window or 0, self.scale)
+        ops.rope_store_attend(attn, qkv, cos, sin, k_pages, v_pages, view.group, ctx, self.num_heads,
+                              k_pages.shape[1], self.head_dim, self.window or 0, self.scale,
+                              write_kv=not self.shares_cache,
+                              q_rot=lambda: ws.get("q_rot", T, self.q_size, self.dtype))
         return linear(attn, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
 
 

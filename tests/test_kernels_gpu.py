@@ -357,6 +357,88 @@ def test_decode_attention_matches_the_general_kernel_and_plain(ops, dtype, NH, N
     assert rel_err(out, gen.double()) < (2e-6 if dtype == torch.float32 else 1e-2)
 
 
+@pytest.mark.parametrize("partial", [False, True])
+@pytest.mark.parametrize("NH,NKV,HS,page,window,splits,write_kv", [
+    (32, 4, 64, 16, 0, 5, True),       # ranges merged in a cluster
+    (8, 1, 64, 8, 0, 1, True),         # one range
+    (40, 2, 64, 32, 100, 12, True),    # 20 heads per group: two passes; merge through the scratch
+    (6, 3, 128, 16, 0, 3, True),
+    (4, 2, 128, 64, 70, 2, False)])    # reads pages that it does not write
+def test_decode_attention_fused_with_rotation_and_store(ops, partial, NH, NKV, HS, page, window, splits, write_kv):
+    """One kernel for a decode step's rotation, cache store and attention gives what the
+    rotate-and-store kernel followed by the decode attention gives, from a tensor and from
+    unsummed split-K partial results; requests whose newest token is first or last in a page."""
+    torch.manual_seed(13)
+    dtype = torch.bfloat16
+    lens = [1, page, page + 1, 257, 140, 2 * page]
+    B = len(lens)
+    W = -(-max(lens) // page) + 1
+    n_pages = sum(-(-n // page) for n in lens) + 3
+    perm = torch.randperm(n_pages).tolist()
+    kp = torch.randn(n_pages, NKV, page, HS, device=DEV).to(dtype)
+    vp = torch.randn(n_pages, NKV, page, HS, device=DEV).to(dtype)
+    bt = torch.zeros(B, W, dtype=torch.int32)
+    at = 0
+    for b, n in enumerate(lens):
+        k = -(-n // page)
+        bt[b, :k] = torch.tensor(perm[at:at + k], dtype=torch.int32)
+        at += k
+    slot = torch.tensor([int(bt[b, (n - 1) // page]) * page + (n - 1) % page for b, n in enumerate(lens)],
+                        dtype=torch.int32, device=DEV)
+    bt = bt.to(DEV)
+    kv_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    pos = kv_lens - 1
+    width = (NH + (2 * NKV if write_kv else 0)) * HS
+    qk_splits = 5
+    parts = torch.randn(qk_splits, B, width, device=DEV)
+    if partial:
+        src = ops.PartialSum(parts.reshape(-1), qk_splits, B, width, dtype)
+        plain_src = ops.PartialSum(parts.reshape(-1), qk_splits, B, width, dtype)
+    else:
+        src = parts.sum(0).to(dtype)
+        plain_src = src.clone()
+    cos = torch.cos(torch.rand(300, HS // 2, device=DEV) * 6)
+    sin = torch.sqrt(1 - cos * cos)
+    scale = 0.9 / math.sqrt(HS)
+    # the two-kernel path
+    kp1, vp1 = kp.clone(), vp.clone()
+    q1 = torch.zeros(B, NH * HS, device=DEV, dtype=dtype)
+    ops.rope_kv_write(plain_src, cos, sin, pos, slot, kp1, vp1, B, NH, NKV if write_kv else 0, HS, q_out=q1)
+    out1 = torch.zeros(B, NH * HS, device=DEV, dtype=dtype)
+    ops.paged_attention_decode(out1, q1, kp1, vp1, bt, kv_lens, B, NH, NKV, HS, window, scale, splits=splits)
+    # the fused kernel
+    kp2, vp2 = kp.clone(), vp.clone()
+    out2 = torch.zeros(B, NH * HS, device=DEV, dtype=dtype)
+    assert ops.decode_attention_fused_supported(src, cos, sin, HS)
+    ops.decode_attention_fused(out2, src, cos, sin, kp2, vp2, bt, kv_lens, B, NH, NKV, HS, window, scale,
+                               write_kv=write_kv, splits=splits)
+    torch.cuda.synchronize()
+    assert torch.equal(kp1, kp2) and torch.equal(vp1, vp2)          # the same values at the same places, nothing else touched
+    if write_kv:
+        assert not torch.equal(kp, kp2)
+    assert rel_err(out2, out1.double()) < 2e-3
+    # and against the plain formula on the stored pages
+    ref = torch.zeros(B, NH * HS, dtype=torch.float64)
+    G = NH // NKV
+    for b, n in enumerate(lens):
+        lo = max(0, n - window) if window else 0
+        keys = [(int(bt[b, j // page]), j % page) for j in range(lo, n)]
+        for h in range(NH):
+            K = torch.stack([kp1[pg, h // G, o].double().cpu() for pg, o in keys])
+            V = torch.stack([vp1[pg, h // G, o].double().cpu() for pg, o in keys])
+            sc = (K @ q1[b, h * HS:(h + 1) * HS].double().cpu()) * scale
+            ref[b, h * HS:(h + 1) * HS] = torch.softmax(sc, 0) @ V
+    assert rel_err(out2, ref) < 1e-2
+
+
+def test_decode_attention_fused_refuses_other_sizes(ops):
+    cos = torch.ones(8, 24, device=DEV)
+    assert not ops.decode_attention_fused_supported(torch.zeros(2, 48 * 3, device=DEV, dtype=torch.bfloat16), cos, cos, 48)
+    assert not ops.decode_attention_fused_supported(torch.zeros(2, 64 * 3, device=DEV), cos, cos, 64)
+    odd = torch.zeros(2, 64 * 3 + 4, device=DEV, dtype=torch.bfloat16)
+    assert not ops.decode_attention_fused_supported(odd, cos, cos, 64)
+
+
 def test_consumers_sum_split_k_partials_themselves(ops):
     """add_rmsnorm, silu_mul, gather_rows and rope_kv_write given the float32 partial results
     of a split-K product give what they give for the summed tensor."""
