@@ -367,17 +367,26 @@ int launch_decode_mma(void* out, long long out_stride, const void* q, long long 
   dim3 grid(splits, n_kv, n_entries);
   const float scale_log2e = scale * 1.4426950408889634f;
   const int group_rows = n_heads / n_kv < decode_mma::ROWS ? n_heads / n_kv : decode_mma::ROWS;
-  // 2 to 8 ranges whose shares fit the first CTA's buffers, and a grid of at most two waves:
-  // merge inside a cluster, no scratch.  (Measured at 64 requests, 512 CTAs: 30 us with
+  // 2 to 8 ranges whose shares fit the first CTA's receive buffer, and a grid of at most two
+  // waves: merge inside a cluster, no scratch.  (Measured at 64 requests, 512 CTAs: 30 us with
   // clusters against 23 us with the counter-based merge; at 8 requests 9.3 us against 13.5 us.)
+  constexpr int RECV_LIMIT = 64 * 1024;
+  const int recv_bytes = (splits - 1) * group_rows * head_dim * 4;
   const bool cluster = splits >= 2 && splits <= 8 && (long long)splits * n_kv * n_entries <= 2 * 148 &&
-                       (splits - 1) * group_rows * head_dim * 4 <= 4 * decode_mma::TILE * head_dim * 2;
+                       recv_bytes <= RECV_LIMIT;
   if (cluster) {
     auto kern = head_dim == 64 ? decode_mma::decode_attention_mma_kernel<64, true, FUSED>
                                : decode_mma::decode_attention_mma_kernel<128, true, FUSED>;
+    static bool configured[2] = {false, false};
+    if (!configured[head_dim == 128]) {
+      cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RECV_LIMIT);
+      if (err != cudaSuccess) return llmk_fail((int)err, "attention_decode: cannot set the receive buffer: %s", cudaGetErrorString(err));
+      configured[head_dim == 128] = true;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(decode_mma::THREADS);
+    cfg.dynamicSmemBytes = (size_t)recv_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;

@@ -72,8 +72,10 @@ __device__ __forceinline__ float2 sum2(const MaybePartial<__nv_bfloat16>& s, siz
 //
 // CLUSTER: the CTAs of the ranges of one (request, kv head) form a thread-block cluster (2 to 8
 // along blockIdx.x).  They hand their results to the first CTA through distributed shared memory
-// and that CTA merges them: no scratch in global memory, no fence, no counter, and two cluster
-// barriers instead of three round trips to L2.
+// (into its dynamic shared memory, (ranges - 1) x heads of a pass x HS floats) and that CTA
+// merges them: no scratch in global memory, no fence, no counter.  Every CTA arrives at a first
+// cluster barrier when it starts and waits for it only before it writes to the first CTA, which
+// must be running by then; a second barrier publishes the writes.
 //
 // FUSED: the kernel takes the row of the QKV product itself (a tensor or unsummed split-K
 // partial results) instead of rotated queries.  Every CTA sums and rotates its group's queries
@@ -108,7 +110,9 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
   __shared__ __align__(16) __nv_bfloat16 q_s[FUSED ? ROWS * HS : 8];
   __shared__ __align__(16) __nv_bfloat16 kv_new_s[FUSED ? 2 * HS : 8];    // the newest key, then the newest value
 
+  extern __shared__ __align__(16) float recv_s[];            // CLUSTER: what the other ranges send to the first CTA
   pdl_launch_dependents();
+  if (CLUSTER) tc::cluster_arrive();
   const int split = blockIdx.x, g = blockIdx.y, e = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = n_heads / n_kv;
@@ -425,13 +429,13 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
       }
     }
     if (CLUSTER) {
-      // every CTA of the cluster has its share in registers; after the first barrier the first
-      // CTA's buffers are free to receive the others' shares
+      // every CTA of the cluster has its share in registers; the first CTA runs once the barrier
+      // of the kernel's start has completed (a later pass: once it has merged the pass before)
       const uint32_t rank = tc::cluster_ctarank();
-      const uint32_t slots = tc::map_to_cta((uint32_t)__cvta_generic_to_shared(vbuf), 0);
+      const uint32_t slots = tc::map_to_cta((uint32_t)__cvta_generic_to_shared(recv_s), 0);
       const uint32_t m_remote = tc::map_to_cta((uint32_t)__cvta_generic_to_shared(&w_s[0][0]), 0);
       const uint32_t l_remote = tc::map_to_cta((uint32_t)__cvta_generic_to_shared(&l_in[0][0]), 0);
-      tc::cluster_sync();
+      if (h0 == 0) tc::cluster_wait(); else tc::cluster_sync();
 #pragma unroll
       for (int k = 0; k < PER; ++k) {
         const int i = tid + k * THREADS;
@@ -458,7 +462,7 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
             if (mr > -INFINITY) {
               const float f = ex2(mr - m);
               l += f * l_in[h][r];
-              acc += f * (r == 0 ? racc[k] : reinterpret_cast<const float*>(vbuf)[((size_t)(r - 1) * nh + h) * HS + d]);
+              acc += f * (r == 0 ? racc[k] : recv_s[((size_t)(r - 1) * nh + h) * HS + d]);
             }
           }
           out[(size_t)e * out_stride + (size_t)(head0 + h) * HS + d] = __float2bfloat16_rn(acc / l);

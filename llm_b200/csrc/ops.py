@@ -245,8 +245,10 @@ def _attn_partials(device, n_floats: int) -> torch.Tensor:
 def decode_splits(n_entries: int, n_kv: int, max_keys: int) -> int:
     """How many ranges the keys of one request are cut into: ranges of about 128 keys (one tile
     of 32 per warp of a CTA) while the batch is small and the kernel bound by latency, fewer
-    and longer ones once (requests x kv heads) alone fill the GPU; at most 64."""
-    return max(1, min(64, _ceil_div(max_keys, 128), (_SMS * 4) // max(1, n_entries * n_kv)))
+    and longer ones as (requests x kv heads) grows, so that about 256 CTAs run; at most 16.
+    Clusters of 7 or 8 CTAs measured slower than 6 longer ranges."""
+    s = max(1, min(16, _ceil_div(max_keys, 128), 256 // max(1, n_entries * n_kv)))
+    return 6 if s in (7, 8) else s
 
 
 def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,

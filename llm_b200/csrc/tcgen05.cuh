@@ -166,6 +166,9 @@ __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The two halves of cluster_sync, for work between arriving and waiting.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 // The address, in the cluster's shared window, of `local` (an address in this CTA's shared
 // memory) inside the CTA of the given rank.
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank) {
