@@ -374,19 +374,23 @@ int launch_decode_mma(void* out, long long out_stride, const void* q, long long 
   const int recv_bytes = (splits - 1) * group_rows * head_dim * 4;
   const bool cluster = splits >= 2 && splits <= 8 && (long long)splits * n_kv * n_entries <= 2 * 148 &&
                        recv_bytes <= RECV_LIMIT;
+  // per warp two stages (one in a cluster) of a tile of keys and a tile of values
+  const int stage_bytes = 4 * (cluster ? 1 : 2) * 2 * decode_mma::TILE * head_dim * 2;
+  using Kernel = decltype(&decode_mma::decode_attention_mma_kernel<64, false, FUSED>);
+  const Kernel kern = head_dim == 64
+      ? (cluster ? decode_mma::decode_attention_mma_kernel<64, true, FUSED> : decode_mma::decode_attention_mma_kernel<64, false, FUSED>)
+      : (cluster ? decode_mma::decode_attention_mma_kernel<128, true, FUSED> : decode_mma::decode_attention_mma_kernel<128, false, FUSED>);
+  static bool configured[2][2] = {{false, false}, {false, false}};
+  if (!configured[head_dim == 128][cluster]) {
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, stage_bytes + (cluster ? RECV_LIMIT : 0));
+    if (err != cudaSuccess) return llmk_fail((int)err, "attention_decode: cannot set the shared memory size: %s", cudaGetErrorString(err));
+    configured[head_dim == 128][cluster] = true;
+  }
   if (cluster) {
-    auto kern = head_dim == 64 ? decode_mma::decode_attention_mma_kernel<64, true, FUSED>
-                               : decode_mma::decode_attention_mma_kernel<128, true, FUSED>;
-    static bool configured[2] = {false, false};
-    if (!configured[head_dim == 128]) {
-      cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RECV_LIMIT);
-      if (err != cudaSuccess) return llmk_fail((int)err, "attention_decode: cannot set the receive buffer: %s", cudaGetErrorString(err));
-      configured[head_dim == 128] = true;
-    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(decode_mma::THREADS);
-    cfg.dynamicSmemBytes = (size_t)recv_bytes;
+    cfg.dynamicSmemBytes = (size_t)(stage_bytes + recv_bytes);
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -401,9 +405,7 @@ int launch_decode_mma(void* out, long long out_stride, const void* q, long long 
                        (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table, table_width, kv_lens, n_heads,
                        n_kv, page_size, window, scale_log2e, splits, fused);
   } else {
-    auto kern = head_dim == 64 ? decode_mma::decode_attention_mma_kernel<64, false, FUSED>
-                               : decode_mma::decode_attention_mma_kernel<128, false, FUSED>;
-    launch_kernel(kern, grid, dim3(decode_mma::THREADS), 0, stream, (__nv_bfloat16*)out, out_stride, scratch,
+    launch_kernel(kern, grid, dim3(decode_mma::THREADS), (size_t)stage_bytes, stream, (__nv_bfloat16*)out, out_stride, scratch,
                   (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table,
                   table_width, kv_lens, n_heads, n_kv, page_size, window, scale_log2e, splits, fused);
   }

@@ -5,10 +5,10 @@
 // inside of a range.  The query heads of the kv group are the rows of an m16n8k16 MMA (up to 16
 // per pass): one instruction scores 8 keys for all of them, so the arithmetic per key no longer
 // grows with the group size.  Each of the four warps works alone on tiles of 32 keys, without
-// block-wide barriers: K fragments come straight from the pages (a lane's two values of a key
-// are 4 contiguous bytes), V is staged per warp through shared memory with cp.async and read
-// back transposed with ldmatrix; scores, maxima, sums and the output are float32, P is rounded
-// to bfloat16 for the second MMA as in the prompt kernel.  A single decoded token has no use for
+// block-wide barriers: keys and values are staged per warp through two stages of shared memory
+// with cp.async (the next tile is in flight while one is computed) and read back with ldmatrix
+// (values transposed); scores, maxima, sums and the output are float32, P is rounded to
+// bfloat16 for the second MMA as in the prompt kernel.  A single decoded token has no use for
 // the 128-row tcgen05 MMA; this is the tensor path that fits 8 to 16 rows.
 #pragma once
 
@@ -37,7 +37,14 @@ __device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* src,
   const int bytes = valid ? 16 : 0;                      // 0: the 16 bytes are filled with zeros
   asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(src), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_addr));
+}
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -102,15 +109,23 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
   constexpr int KS = HS / 16;                  // k-steps of Q K^T
   constexpr int DT = HS / 8;                   // 8-wide tiles of the output row
   constexpr int CH = HS / 8;                   // 16-byte chunks of a row
-  constexpr int V_BYTES = TILE * HS * 2;       // one warp's staged values
-  __shared__ __align__(128) uint8_t vbuf[4 * V_BYTES > 4 * ROWS * HS * 4 ? 4 * V_BYTES : 4 * ROWS * HS * 4];
+  constexpr int V_BYTES = TILE * HS * 2;       // one tile of keys, or of values
+  // Stages of (keys, values) per warp.  Two let the next tile fly while one is computed, which
+  // pays for long ranges.  A cluster is only formed for short ranges on a small grid; there one
+  // stage keeps the CTA small enough to become resident beside the CTAs of the kernel before it,
+  // which is what lets its early requests overlap that kernel.
+  constexpr int NST = CLUSTER ? 1 : 2;
+  constexpr int WARP_BYTES = NST * 2 * V_BYTES;
+  constexpr int RANGES = CLUSTER ? 8 : 64;     // most ranges that a merge in shared memory takes
+  static_assert(4 * WARP_BYTES >= 4 * ROWS * HS * 4, "the warps' results are merged in the stage buffers");
+  extern __shared__ __align__(128) uint8_t vbuf[];            // 4 warps x WARP_BYTES, then (CLUSTER) the receive buffer
   __shared__ float wm_s[4][ROWS], wl_s[4][ROWS];
-  __shared__ float w_s[ROWS][64], l_in[ROWS][64];        // merge: per (head, range)
+  __shared__ float w_s[ROWS][RANGES], l_in[ROWS][RANGES];    // merge: per (head, range)
   __shared__ int last_s;
   __shared__ __align__(16) __nv_bfloat16 q_s[FUSED ? ROWS * HS : 8];
   __shared__ __align__(16) __nv_bfloat16 kv_new_s[FUSED ? 2 * HS : 8];    // the newest key, then the newest value
 
-  extern __shared__ __align__(16) float recv_s[];            // CLUSTER: what the other ranges send to the first CTA
+  float* recv_s = reinterpret_cast<float*>(vbuf + 4 * WARP_BYTES);   // CLUSTER: what the other ranges send to the first CTA
   pdl_launch_dependents();
   if (CLUSTER) tc::cluster_arrive();
   const int split = blockIdx.x, g = blockIdx.y, e = blockIdx.z;
@@ -125,12 +140,16 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
   const int k_end = min(pos + 1, k_begin + chunk);
   const int* table = block_table + (size_t)e * table_width;
   const int qrow = lane >> 2, qcol = (lane & 3) * 2;
-  uint8_t* v_s = vbuf + warp * V_BYTES;
-  const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(v_s);
+  uint8_t* w_buf = vbuf + warp * WARP_BYTES;                 // stage st: keys at st * 2 * V_BYTES, values V_BYTES further
+  const uint32_t w_addr = (uint32_t)__cvta_generic_to_shared(w_buf);
   const int t_first = k_begin + warp * TILE;                // this warp's first tile
+  const int n_tiles = t_first < k_end ? (k_end - t_first + 4 * TILE - 1) / (4 * TILE) : 0;
 
-  // stage a tile's values: 32 rows of CH chunks, swizzled by the row
-  auto stage_values = [&](int t) {
+  // request a tile's keys and values: 32 rows of CH chunks each, swizzled by the row; rows past
+  // the range are filled with zeros
+  auto stage_tile = [&](int j) {
+    const int t = t_first + j * 4 * TILE;
+    const uint32_t dst = w_addr + (j % NST) * 2 * V_BYTES;
 #pragma unroll
     for (int i = 0; i < CH; ++i) {
       const int idx = i * 32 + lane;
@@ -140,40 +159,24 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
       const int kq = valid ? kp : k_begin;
       const size_t row = (((size_t)table[kq / page_size] * n_kv + g) * page_size + kq % page_size) * HS;
       const int cs = (c & ~7) | ((c ^ kl) & 7);
-      cp_async_16(v_addr + kl * (HS * 2) + cs * 16, v_pages + row + c * 8, valid);
+      cp_async_16(dst + kl * (HS * 2) + cs * 16, k_pages + row + c * 8, valid);
+      cp_async_16(dst + V_BYTES + kl * (HS * 2) + cs * 16, v_pages + row + c * 8, valid);
     }
-  };
-  // a tile's keys: fragments straight from the pages
-  uint32_t kf[4][KS][2];
-  auto load_keys = [&](int t) {
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
-      const int kp = t + nt * 8 + qrow;
-      const int kq = kp < k_end ? kp : k_begin;
-      const __nv_bfloat16* kr = k_pages + (((size_t)table[kq / page_size] * n_kv + g) * page_size + kq % page_size) * HS;
-#pragma unroll
-      for (int ks = 0; ks < KS; ++ks) {
-        kf[nt][ks][0] = *reinterpret_cast<const uint32_t*>(kr + ks * 16 + qcol);
-        kf[nt][ks][1] = *reinterpret_cast<const uint32_t*>(kr + ks * 16 + 8 + qcol);
-      }
-    }
+    cp_async_commit();
   };
 
   // Lengths and block tables were copied before the step's first kernel, and every key but the
-  // newest was stored by an earlier step.  So each warp fetches the keys and values of its first
-  // tile, and the CTA requests the rest of its range into L2, while the kernels before this one
-  // still run; only the queries and the newest key and value (stored by a kernel of this step,
-  // or by this one) have to wait.  The newest row of a tile fetched early is replaced below.
-  bool early = t_first < k_end;
-  if (early) {
-    stage_values(t_first);
-    load_keys(t_first);
-  }
+  // newest was stored by an earlier step.  So each warp requests its first two tiles, and the
+  // CTA asks the rest of its range into L2, while the kernels before this one still run; only
+  // the queries and the newest key and value (stored by a kernel of this step, or by this one)
+  // have to wait.  The newest row of a tile is replaced after it has landed, see below.
+  if (n_tiles > 0) stage_tile(0);
+  if (NST > 1 && n_tiles > 1) stage_tile(1);
   {
     constexpr int LINES = HS * 2 / 128;                    // 128-byte lines per row
-    const int n_rows = max(0, k_end - k_begin - 4 * TILE);
+    const int n_rows = max(0, k_end - k_begin - NST * 4 * TILE);
     for (int i = tid; i < n_rows * LINES * 2; i += THREADS) {
-      const int which = i & 1, line = (i >> 1) % LINES, kp = k_begin + 4 * TILE + (i >> 1) / LINES;
+      const int which = i & 1, line = (i >> 1) % LINES, kp = k_begin + NST * 4 * TILE + (i >> 1) / LINES;
       const size_t row = (((size_t)table[kp / page_size] * n_kv + g) * page_size + kp % page_size) * HS;
       const __nv_bfloat16* src = (which ? v_pages : k_pages) + row + line * 64;
       asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
@@ -279,49 +282,43 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
     for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;        // rows qrow and qrow + 8 (l: this lane's share)
 
-    for (int t = t_first; t < k_end; t += 4 * TILE) {
-      if (!(early && t == t_first)) {                             // else: fetched before the wait
-        stage_values(t);
-        load_keys(t);
-      }
+    if (h0 > 0) {                                                 // a later pass requests its tiles again
+      if (n_tiles > 0) stage_tile(0);
+      if (NST > 1 && n_tiles > 1) stage_tile(1);
+    }
+    for (int j = 0; j < n_tiles; ++j) {
+      const int t = t_first + j * 4 * TILE;
+      const uint32_t k_addr = w_addr + (j % NST) * 2 * V_BYTES, v_addr = k_addr + V_BYTES;
+      if (NST > 1 && j + 1 < n_tiles) cp_async_wait_but_one(); else cp_async_wait_all();
+      __syncwarp();
       if (pos < t + TILE) {                                       // pos >= t: the range ends at pos
-        // The newest row: not valid when a tile was fetched early, and a copy of its line from
-        // before may sit in this SM's L1.  It is read again from the CTA's own copy, or from L2.
-#pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-          if (t + nt * 8 + qrow == pos) {
-#pragma unroll
-            for (int ks = 0; ks < KS; ++ks) {
-              if (owner) {
-                kf[nt][ks][0] = *reinterpret_cast<const uint32_t*>(kv_new_s + ks * 16 + qcol);
-                kf[nt][ks][1] = *reinterpret_cast<const uint32_t*>(kv_new_s + ks * 16 + 8 + qcol);
-              } else {
-                kf[nt][ks][0] = __ldcg(reinterpret_cast<const uint32_t*>(k_pages + new_row + ks * 16 + qcol));
-                kf[nt][ks][1] = __ldcg(reinterpret_cast<const uint32_t*>(k_pages + new_row + ks * 16 + 8 + qcol));
-              }
-            }
-          }
-        }
-        uint4 v_row = make_uint4(0u, 0u, 0u, 0u);
-        if (lane < CH)
-          v_row = owner ? *reinterpret_cast<const uint4*>(kv_new_s + HS + lane * 8)
-                        : __ldcg(reinterpret_cast<const uint4*>(v_pages + new_row + lane * 8));
-        cp_async_wait_all();
-        __syncwarp();
-        if (lane < CH) {
-          const int kl = pos - t;
-          const int cs = (lane & ~7) | ((lane ^ kl) & 7);
-          *reinterpret_cast<uint4*>(v_s + kl * (HS * 2) + cs * 16) = v_row;
+        // The newest row: not valid when the tile was requested early, and a copy of its line
+        // from before may sit in this SM's L1.  It is taken from the CTA's own copy, or from L2.
+        if (lane < 2 * CH) {
+          const int c = lane % CH, kl = pos - t;
+          const bool is_v = lane >= CH;
+          const uint4 row = owner ? *reinterpret_cast<const uint4*>(kv_new_s + (is_v ? HS : 0) + c * 8)
+                                  : __ldcg(reinterpret_cast<const uint4*>((is_v ? v_pages : k_pages) + new_row + c * 8));
+          const int cs = (c & ~7) | ((c ^ kl) & 7);
+          *reinterpret_cast<uint4*>(w_buf + (j % NST) * 2 * V_BYTES + (is_v ? V_BYTES : 0) + kl * (HS * 2) + cs * 16) = row;
         }
         __syncwarp();
       }
-      // ---- S = Q K^T ----
+      // ---- S = Q K^T: K fragments with ldmatrix, two k-steps per instruction ----
       float s[4][4];
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
         s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        const int kl = nt * 8 + (lane & 7);
 #pragma unroll
-        for (int ks = 0; ks < KS; ++ks) mma_16816(s[nt], qf[ks], kf[nt][ks][0], kf[nt][ks][1]);
+        for (int k2 = 0; k2 < KS / 2; ++k2) {
+          const int c = k2 * 4 + (lane >> 3);
+          const int cs = (c & ~7) | ((c ^ kl) & 7);
+          uint32_t kb[4];
+          ldmatrix_x4(kb, k_addr + kl * (HS * 2) + cs * 16);
+          mma_16816(s[nt], qf[2 * k2], kb[0], kb[1]);
+          mma_16816(s[nt], qf[2 * k2 + 1], kb[2], kb[3]);
+        }
       }
       // ---- scale, mask the keys past the range, running maximum and sum ----
       float t0 = -INFINITY, t1 = -INFINITY;
@@ -358,8 +355,6 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
         pf[nt >> 1][(nt & 1) * 2 + 1] = pack2(p2, p3);
       }
       // ---- O += P V ----
-      cp_async_wait_all();
-      __syncwarp();
       const int mid = lane >> 3, r8 = lane & 7;
 #pragma unroll
       for (int kk = 0; kk < 2; ++kk) {
@@ -374,9 +369,9 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
           mma_16816(o[dp * 2 + 1], pf[kk], vb[2], vb[3]);
         }
       }
-      __syncwarp();                                               // the values are consumed before the next tile lands
+      __syncwarp();                                               // the stage is consumed before it is requested again
+      if (j + NST < n_tiles) stage_tile(j + NST);
     }
-    early = false;                                                // a later pass fetches its tiles again
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
@@ -443,8 +438,8 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
         const int h = i / HS, d = i % HS;
         if (rank != 0 && rm[k] > -INFINITY) tc::st_cluster_f32(slots + (uint32_t)(((rank - 1) * nh + h) * HS + d) * 4u, racc[k]);
         if (d == 0) {
-          tc::st_cluster_f32(m_remote + (uint32_t)(h * 64 + rank) * 4u, rm[k]);
-          tc::st_cluster_f32(l_remote + (uint32_t)(h * 64 + rank) * 4u, rl[k]);
+          tc::st_cluster_f32(m_remote + (uint32_t)(h * RANGES + rank) * 4u, rm[k]);
+          tc::st_cluster_f32(l_remote + (uint32_t)(h * RANGES + rank) * 4u, rl[k]);
         }
       }
       tc::cluster_sync();
