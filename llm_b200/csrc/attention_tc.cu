@@ -102,7 +102,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   int* tile_info = reinterpret_cast<int*>(tmem_slot + 1);  // entry, first row in the batch, tokens, first position
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = blockIdx.y;
+  const int g = blockIdx.x % n_kv;                        // kv heads fastest: the heaviest tiles of every head start first
   const int group = n_heads / n_kv;
   const int tq = ROWS / group;                             // tokens per tile
 
@@ -123,7 +123,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   if (threadIdx.x == 0) {
     // which request and which of its tokens this tile covers; the tiles are handed out from the
     // back, so that the late tokens of long prompts (the most key blocks) start first
-    int tile = (int)gridDim.x - 1 - (int)blockIdx.x, entry = -1, t0 = 0, nt = 0, p0 = 0;
+    int tile = (int)(gridDim.x / n_kv) - 1 - (int)(blockIdx.x / n_kv), entry = -1, t0 = 0, nt = 0, p0 = 0;
     for (int e = 0; e < n_entries; ++e) {
       const int n_e = cu_tokens[e + 1] - cu_tokens[e];
       const int tiles_e = (n_e + tq - 1) / tq;
@@ -414,7 +414,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     if (e != cudaSuccess) return llmk_fail((int)e, "attention_tc: cannot set %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid(max_tiles, n_kv);
+  dim3 grid(max_tiles * n_kv);
   launch_kernel(kern, grid, dim3(THREADS), (size_t)smem, stream, mq, mk, mv, (__nv_bfloat16*)out, out_stride, block_table,
                 table_width, cu_tokens, kv_lens, n_entries, n_heads, n_kv, page_size, n_pages, window, scale_log2e, g_attn_err);
   LLMK_LAUNCH_CHECK("attention_tc");
