@@ -5,15 +5,21 @@
 // group: row r = (token r / G, head r % G), up to 128 rows, so every key and value that is
 // fetched serves the whole group.  Per block of 128 keys (blocks start at absolute positions
 // 0, 128, ...):
-//   producer thread   TMA copies the block's pages of K and V ([page, 64 dims] boxes with the
-//                     128-byte swizzle) into a two-stage ring
-//   MMA thread        S = Q K^T (tcgen05.mma, M = 128 rows, N = 128 keys) into tensor memory;
-//                     after the softmax warps have written P: O_blk = P V (M = 128, N = head size)
-//   softmax warps     thread r owns row r = lane r of tensor memory: reads its 128 scores with
-//                     tcgen05.ld, masks (causal, window), keeps the running maximum and sum in
-//                     float32 (exp2 of pre-scaled scores), writes P as bfloat16 into shared
-//                     memory in the swizzled K-major layout that the second MMA reads, then
-//                     adds O_blk to its float32 output row, rescaled when the maximum moved.
+//   producer thread   TMA copies the block's pages of K and of V ([page, 64 dims] boxes with the
+//                     128-byte swizzle) into two rings of two stages
+//   MMA thread        S = Q K^T (tcgen05.mma, M = 128 rows, N = 128 keys) into tensor memory, for
+//                     the next block as soon as the softmax warps hold the scores of this one in
+//                     registers; after they have written P: O += P V (M = 128, N = head size),
+//                     accumulated in tensor memory over all blocks
+//   softmax warps     thread r owns row r = lane r of tensor memory: takes its 128 scores with
+//                     tcgen05.ld, masks (causal, window), keeps a reference maximum and the sum
+//                     in float32 (exp2 of pre-scaled scores) and writes P as bfloat16 into shared
+//                     memory in the swizzled K-major layout that the second MMA reads.  The
+//                     reference maximum only moves when the true maximum has grown by more than
+//                     2^8 (P stays below 256, the sum stays exact in float32 terms); only then
+//                     is the row of O in tensor memory rescaled (tcgen05.ld, multiply,
+//                     tcgen05.st), which after the first blocks of a row is rare.  At the end
+//                     the row of O is divided by the sum.
 // Visible keys of a row at position p: max(0, p-window+1) .. p.  The reference's kernel is an
 // mma.sync flash attention fixed to 32/4/64 (kernel/attention/attention_NH_32_NKV_4_HS_64.h);
 // this one takes any head counts with group size up to 128.
@@ -60,6 +66,32 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Blackwell's three-input maximum and its two-wide float32 arithmetic halve the instruction
+// count of the softmax's inner loops.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 template <int HS>
 struct Smem {
   static constexpr int KB = HS / 64;                      // 64-dim blocks of a head
@@ -93,11 +125,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   uint8_t* p_s = v_s + KV_STAGES * S::KV_BYTES;            // [2][128 rows][128 bytes]
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + S::P_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;                            // [KV_STAGES]
-  uint64_t* kv_empty = kv_full + KV_STAGES;                // [KV_STAGES]
-  uint64_t* s_full = kv_empty + KV_STAGES;
-  uint64_t* p_ready = s_full + 1;
-  uint64_t* pv_full = p_ready + 1;
+  uint64_t* k_full = bars + 1;                             // [KV_STAGES]
+  uint64_t* k_empty = k_full + KV_STAGES;
+  uint64_t* v_full = k_empty + KV_STAGES;
+  uint64_t* v_empty = v_full + KV_STAGES;
+  uint64_t* s_full = v_empty + KV_STAGES;                  // MMA -> softmax: the scores of a block are in tensor memory
+  uint64_t* s_free = s_full + 1;                           // softmax -> MMA: they are in registers now
+  uint64_t* p_ready = s_free + 1;                          // softmax -> MMA: P is in shared memory (and O rescaled)
+  uint64_t* pv_full = p_ready + 1;                         // MMA -> softmax: O holds the blocks so far, P may be overwritten
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_full + 1);
   int* tile_info = reinterpret_cast<int*>(tmem_slot + 1);  // entry, first row in the batch, tokens, first position
 
@@ -108,8 +143,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+    }
     mbar_init(s_full, 1);
+    mbar_init(s_free, 128);
     mbar_init(p_ready, 128);
     mbar_init(pv_full, 1);
     fence_mbar_init();
@@ -152,44 +191,47 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int n_blocks = kb_last - kb_first + 1;
 
     if (warp == 0) {
+      // ---- producer: the whole warp.  A block of keys (or values) is pages_per_block * KB boxes;
+      // looking up a page and issuing its copy costs a thread a few hundred cycles, so the lanes
+      // issue one box each, after lane 0 has told the barrier how many bytes to expect ----
       if (lane == 0) {
-        // ---- producer ----
         mbar_arrive_expect_tx(q_full, (uint32_t)(KB * group * tq * 128));
         for (int b = 0; b < KB; ++b) tma_load_3d(q_s + b * ROWS * 128, &map_q, b * 64, g * group, t0, q_full);
-        const int* table = block_table + (size_t)entry * table_width;
-        const int pages_per_block = BKV / page_size;
-        bool ok = true;
-        for (int i = 0; i < n_blocks && ok; ++i) {
-          const int s = i % KV_STAGES;
-          ok = mbar_wait(&kv_empty[s], ((i / KV_STAGES) & 1) ^ 1);
+      }
+      const int* table = block_table + (size_t)entry * table_width;
+      const int pages_per_block = BKV / page_size;
+      const int n_boxes = pages_per_block * KB;
+      bool ok = true;
+      for (int i = 0; i < n_blocks && ok; ++i) {
+        const int s = i % KV_STAGES;
+        const uint32_t free_parity = ((i / KV_STAGES) & 1) ^ 1;
+        const int key0 = (kb_first + i) * BKV;
+        for (int which = 0; which < 2 && ok; ++which) {           // keys first: the next scores need them early
+          uint64_t* full = which ? &v_full[s] : &k_full[s];
+          if (lane == 0) {
+            ok = mbar_wait(which ? &v_empty[s] : &k_empty[s], free_parity);
+            if (ok) mbar_arrive_expect_tx(full, S::KV_BYTES);
+          }
+          ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;         // also orders the lanes' copies after the announcement
           if (!ok) break;
-          mbar_arrive_expect_tx(&kv_full[s], 2 * S::KV_BYTES);
-          const int key0 = (kb_first + i) * BKV;
-          for (int pg = 0; pg < pages_per_block; ++pg) {
+          for (int box = lane; box < n_boxes; box += 32) {
+            const int pg = box / KB, b = box % KB;
             int idx = key0 / page_size + pg;
             idx = idx < table_width ? idx : table_width - 1;
             int page = table[idx];
-            page = page < 0 ? 0 : (page >= n_pages ? n_pages - 1 : page);   // pages past the request hold masked keys
-            for (int b = 0; b < KB; ++b) {
-              const int off = b * BKV * 128 + pg * page_size * 128;
-              tma_load_3d(k_s + s * S::KV_BYTES + off, &map_k, b * 64, 0, page * n_kv + g, &kv_full[s]);
-              tma_load_3d(v_s + s * S::KV_BYTES + off, &map_v, b * 64, 0, page * n_kv + g, &kv_full[s]);
-            }
+            page = page < 0 ? 0 : (page >= n_pages ? n_pages - 1 : page);     // pages past the request hold masked keys
+            const int off = b * BKV * 128 + pg * page_size * 128;
+            tma_load_3d((which ? v_s : k_s) + s * S::KV_BYTES + off, which ? &map_v : &map_k, b * 64, 0,
+                        page * n_kv + g, full);
           }
         }
-        if (!ok) atomicExch(err_flag, ERR_KV);
       }
+      if (!ok && lane == 0) atomicExch(err_flag, ERR_KV);
     } else if (warp == 1) {
       if (lane == 0) {
         // ---- MMA issuer ----
-        bool ok = mbar_wait(q_full, 0);
-        if (!ok) atomicExch(err_flag, ERR_Q);
-        for (int i = 0; i < n_blocks && ok; ++i) {
+        auto scores = [&](int i) {                                // S = Q K^T of block i
           const int s = i % KV_STAGES;
-          ok = mbar_wait(&kv_full[s], (i / KV_STAGES) & 1);
-          if (!ok) { atomicExch(err_flag, ERR_KV); break; }
-          fence_after_sync();
-          // S = Q K^T
 #pragma unroll
           for (int k = 0; k < HS / 16; ++k) {
             const uint32_t off = (k / 4) * (ROWS * 128) + (k % 4) * 32;
@@ -198,22 +240,48 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             mma_bf16(tmem_base, da, db, IDESC_QK, k != 0);
           }
           mma_commit(s_full);
-          // O_blk = P V once the softmax warps have written P
+          mma_commit(&k_empty[s]);
+        };
+        bool ok = mbar_wait(q_full, 0);
+        if (!ok) atomicExch(err_flag, ERR_Q);
+        if (ok) {
+          ok = mbar_wait(&k_full[0], 0);
+          if (!ok) atomicExch(err_flag, ERR_KV);
+        }
+        if (ok) {
+          fence_after_sync();
+          scores(0);
+        }
+        for (int i = 0; i < n_blocks && ok; ++i) {
+          const int s = i % KV_STAGES;
+          if (i + 1 < n_blocks) {
+            // the scores of block i are in the softmax warps' registers: block i + 1 may overwrite them
+            ok = mbar_wait(s_free, i & 1);
+            if (!ok) { atomicExch(err_flag, ERR_S); break; }
+            ok = mbar_wait(&k_full[(i + 1) % KV_STAGES], ((i + 1) / KV_STAGES) & 1);
+            if (!ok) { atomicExch(err_flag, ERR_KV); break; }
+            fence_after_sync();
+            scores(i + 1);
+          }
+          // O += P V once the softmax warps have written P (and rescaled O where they had to)
           ok = mbar_wait(p_ready, i & 1);
           if (!ok) { atomicExch(err_flag, ERR_P); break; }
+          ok = mbar_wait(&v_full[s], (i / KV_STAGES) & 1);
+          if (!ok) { atomicExch(err_flag, ERR_KV); break; }
           fence_after_sync();
 #pragma unroll
           for (int k = 0; k < BKV / 16; ++k) {
             const uint64_t da = smem_desc_sw128(smem_u32(p_s + (k / 4) * (ROWS * 128) + (k % 4) * 32));
             const uint64_t db = smem_desc_sw128_mn(smem_u32(v_s + s * S::KV_BYTES + k * 16 * 128), BKV * 128);
-            mma_bf16(tmem_base + BKV, da, db, IDESC_PV, k != 0);
+            mma_bf16(tmem_base + BKV, da, db, IDESC_PV, (i | k) != 0);
           }
           mma_commit(pv_full);
-          mma_commit(&kv_empty[s]);
+          mma_commit(&v_empty[s]);
         }
       }
     } else {
       // ---- softmax and output: thread r owns row r ----
+      constexpr float TAU = 8.f;                                  // how far the true maximum may run ahead of the reference
       const int quad = warp & 3;
       const int r = quad * 32 + lane;
       const int tok = r / group, head = r % group;
@@ -221,105 +289,128 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int pos = p0 + tok;
       const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-      float o[HS];
-#pragma unroll
-      for (int d = 0; d < HS; ++d) o[d] = 0.f;
-      float m = -INFINITY, l = 0.f;
+      float m_ref = -INFINITY, l = 0.f;
       bool ok = true;
+
       for (int i = 0; i < n_blocks; ++i) {
         const int key0 = (kb_first + i) * BKV;
         if (ok) ok = mbar_wait(s_full, i & 1);
         fence_after_sync();
+        uint32_t raw[2][64];
+        tmem_ld_x64(lane_addr, raw[0]);
+        tmem_ld_x64(lane_addr + 64, raw[1]);
+        tmem_ld_wait();
+        fence_before_sync();
+        mbar_arrive(s_free);
         // every row sees every key of the block when the block lies inside all windows and below all diagonals
         const bool full = (key0 + BKV - 1 <= p0) && (window <= 0 || key0 >= p_last - window + 1);
-        // pass 1: the row's maximum over the block (scores stay in tensor memory).  The scale is
-        // positive, so the maximum is taken over the raw scores and scaled once.  Four running
-        // maxima (and four running sums below) keep the chains of dependent instructions short.
+        // the row's maximum over the block.  The scale is positive, so it is taken over the raw
+        // scores and scaled once.  Four running maxima (and sums below) keep the dependent chains short.
         float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < BKV; c += 64) {
-          uint32_t raw[64];
-          tmem_ld_x64(lane_addr + c, raw);
-          tmem_ld_wait();
+        for (int c = 0; c < 2; ++c) {
           if (full) {
 #pragma unroll
-            for (int j = 0; j < 64; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[j]));
+            for (int j = 0; j < 64; j += 2)
+              mx[(j >> 1) & 3] = max3(mx[(j >> 1) & 3], __uint_as_float(raw[c][j]), __uint_as_float(raw[c][j + 1]));
           } else {
 #pragma unroll
             for (int j = 0; j < 64; ++j) {
-              const int key = key0 + c + j;
-              if (key <= pos && key >= lo) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[j]));
+              const int key = key0 + c * 64 + j;
+              if (key <= pos && key >= lo) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[c][j]));
             }
           }
         }
-        const float m_raw = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        const float m_new = fmaxf(m, m_raw * scale_log2e);
-        const float m_use = m_new == -INFINITY ? 0.f : m_new;          // a row that sees nothing yet
-        const float alpha = fast_exp2(m - m_use);                       // 0 while m is -inf
-        const float neg_m = -m_use;
-        float ls[4] = {0.f, 0.f, 0.f, 0.f};
-        // pass 2: P = exp2(score * scale - m) as bfloat16 into the swizzled K-major tile: 16-byte
-        // chunk c of row r sits at c ^ (r % 8)
+        const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2e;
+        // move the reference only when the block's maximum is far above it (or it is the first
+        // key this row sees: -inf + TAU is -inf)
+        const bool moved = m_blk > m_ref + TAU;
+        float alpha = 1.f;
+        if (moved) {
+          alpha = fast_exp2(m_ref - m_blk);                       // 0 while the reference is -inf
+          m_ref = m_blk;
+          l *= alpha;
+        }
+        bool pv_waited = false;
+        if (i > 0 && __any_sync(0xffffffffu, moved)) {
+          // O holds blocks 0 .. i-1 once their last product is done; rescale this warp's rows
+          if (ok) ok = mbar_wait(pv_full, (i - 1) & 1);
+          pv_waited = true;
+          fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < BKV; c += 64) {
-          uint32_t raw[64];
-          tmem_ld_x64(lane_addr + c, raw);
-          tmem_ld_wait();
+          for (int c = 0; c < HS; c += 32) {
+            uint32_t o[32];
+            tmem_ld_x32(lane_addr + BKV + c, o);
+            tmem_ld_wait();
 #pragma unroll
-          for (int q8 = 0; q8 < 8; ++q8) {
-            uint32_t packed[4];
+            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+            tmem_st_x32(lane_addr + BKV + c, o);
+          }
+          tmem_st_wait();
+        }
+        const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;   // a row that sees nothing yet
+        // P = exp2(score * scale - reference) as bfloat16 pairs, in place of the scores
+        const uint64_t scale2 = pack_f32x2(scale_log2e, scale_log2e), neg_m2 = pack_f32x2(neg_m, neg_m);
+        uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};               // four pairs of running sums (0.f, 0.f)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float pa = fast_exp2(fmaf(__uint_as_float(raw[q8 * 8 + 2 * j]), scale_log2e, neg_m));
-              float pb = fast_exp2(fmaf(__uint_as_float(raw[q8 * 8 + 2 * j + 1]), scale_log2e, neg_m));
-              if (!full) {
-                const int key = key0 + c + q8 * 8 + 2 * j;
-                if (key > pos || key < lo) pa = 0.f;
-                if (key + 1 > pos || key + 1 < lo) pb = 0.f;
-              }
-              ls[j] += pa + pb;
-              const __nv_bfloat162 h2 = __floats2bfloat162_rn(pa, pb);
-              packed[j] = *reinterpret_cast<const uint32_t*>(&h2);
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float xa, xb;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(raw[c][2 * j]), __uint_as_float(raw[c][2 * j + 1])), scale2, neg_m2), xa, xb);
+            float pa = fast_exp2(xa), pb = fast_exp2(xb);
+            if (!full) {
+              const int key = key0 + c * 64 + 2 * j;
+              if (key > pos || key < lo) pa = 0.f;
+              if (key + 1 > pos || key + 1 < lo) pb = 0.f;
             }
-            const int cc = c / 8 + q8;                                  // 16-byte chunk of the row, 0..15
-            const int blk = cc / 8, chunk = cc % 8;
-            uint8_t* dst = p_s + blk * (ROWS * 128) + r * 128 + ((chunk ^ (r & 7)) * 16);
-            *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            ls2[j & 3] = add_f32x2(ls2[j & 3], pack_f32x2(pa, pb));
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(pa, pb);
+            raw[c][j] = *reinterpret_cast<const uint32_t*>(&h2);
           }
         }
-        const float l_blk = (ls[0] + ls[1]) + (ls[2] + ls[3]);
-        l = l * alpha + l_blk;
-        m = m_new;
+        {
+          float a0, a1, b0, b1;
+          unpack_f32x2(add_f32x2(ls2[0], ls2[1]), a0, a1);
+          unpack_f32x2(add_f32x2(ls2[2], ls2[3]), b0, b1);
+          l += (a0 + a1) + (b0 + b1);
+        }
+        if (i > 0 && !pv_waited && ok) ok = mbar_wait(pv_full, (i - 1) & 1);
+#pragma unroll
+        for (int cc = 0; cc < 16; ++cc) {
+          const int c = cc / 8, q8 = cc % 8;
+          uint8_t* dst = p_s + c * (ROWS * 128) + r * 128 + ((q8 ^ (r & 7)) * 16);
+          *reinterpret_cast<uint4*>(dst) = make_uint4(raw[c][q8 * 4], raw[c][q8 * 4 + 1], raw[c][q8 * 4 + 2], raw[c][q8 * 4 + 3]);
+        }
         fence_proxy_async();                  // the MMA reads P through the async proxy
-        fence_before_sync();
+        fence_before_sync();                  // and O, if it was rescaled, through tensor memory
         mbar_arrive(p_ready);
-        // O = O * alpha + O_blk
-        if (ok) ok = mbar_wait(pv_full, i & 1);
-        fence_after_sync();
-#pragma unroll
-        for (int c = 0; c < HS; c += 64) {
-          uint32_t raw[64];
-          tmem_ld_x64(lane_addr + BKV + c, raw);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 64; ++j) o[c + j] = fmaf(o[c + j], alpha, __uint_as_float(raw[j]));
-        }
-        fence_before_sync();
       }
+      if (ok) ok = mbar_wait(pv_full, (n_blocks - 1) & 1);
+      fence_after_sync();
       if (!ok && lane == 0) atomicExch(err_flag, ERR_S);
-      if (row_ok) {
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16* dst = out + (size_t)(t0 + tok) * out_stride + (size_t)(g * group + head) * HS;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = out + (size_t)(t0 + tok) * out_stride + (size_t)(g * group + head) * HS;
 #pragma unroll
-        for (int d = 0; d < HS; d += 8) {
-          uint4 u;
-          __nv_bfloat162 b0 = __floats2bfloat162_rn(o[d] * inv, o[d + 1] * inv), b1 = __floats2bfloat162_rn(o[d + 2] * inv, o[d + 3] * inv);
-          __nv_bfloat162 b2 = __floats2bfloat162_rn(o[d + 4] * inv, o[d + 5] * inv), b3 = __floats2bfloat162_rn(o[d + 6] * inv, o[d + 7] * inv);
-          u.x = *reinterpret_cast<uint32_t*>(&b0); u.y = *reinterpret_cast<uint32_t*>(&b1);
-          u.z = *reinterpret_cast<uint32_t*>(&b2); u.w = *reinterpret_cast<uint32_t*>(&b3);
-          *reinterpret_cast<uint4*>(dst + d) = u;
+      for (int c = 0; c < HS; c += 64) {
+        uint32_t o[64];
+        tmem_ld_x64(lane_addr + BKV + c, o);                       // the whole warp takes part, whatever its rows
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int d = 0; d < 64; d += 8) {
+            uint4 u;
+            __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(o[d]) * inv, __uint_as_float(o[d + 1]) * inv);
+            __nv_bfloat162 b1 = __floats2bfloat162_rn(__uint_as_float(o[d + 2]) * inv, __uint_as_float(o[d + 3]) * inv);
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[d + 4]) * inv, __uint_as_float(o[d + 5]) * inv);
+            __nv_bfloat162 b3 = __floats2bfloat162_rn(__uint_as_float(o[d + 6]) * inv, __uint_as_float(o[d + 7]) * inv);
+            u.x = *reinterpret_cast<uint32_t*>(&b0); u.y = *reinterpret_cast<uint32_t*>(&b1);
+            u.z = *reinterpret_cast<uint32_t*>(&b2); u.w = *reinterpret_cast<uint32_t*>(&b3);
+            *reinterpret_cast<uint4*>(dst + c + d) = u;
+          }
         }
       }
+      fence_before_sync();
     }
   }
 
