@@ -336,9 +336,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 // -> registers -> global) runs while the MMA thread already works on the next tile; the stage
 // ring keeps running across tiles.  Tiles are numbered with the row tile fastest, so CTAs that
 // run at the same time share the same few weight tiles in L2.  Normal mode only (P = rows of A).
+//
+// SWIGLU: W [2I, K] holds I gate rows followed by I up rows (N = 2I).  A tile then takes 128 gate
+// rows and the 128 up rows that belong to them (two TMA boxes per stage) as one 256-wide MMA;
+// the epilogue reads a gate column and its up column 128 columns apart and writes
+// silu(gate) * up to C [M, I].  The product itself never reaches memory.
 enum : int { ERR_P_PRODUCER = 4, ERR_P_MMA = 5, ERR_P_EPILOGUE = 6 };
 
-template <typename TOut>
+// silu(gate) * up in float32, as the stand-alone kernel computes it
+__device__ __forceinline__ float silu_times(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
+template <typename TOut, bool SWIGLU>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                           TOut* __restrict__ C, long long ldc, int M, int N, int K, int tile_q,
@@ -361,7 +369,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tiles = (M + BP - 1) / BP, n_tiles = (N + tile_q - 1) / tile_q;
+  const int inter = N / 2;                                 // SWIGLU: gate rows, and output columns
+  const int m_tiles = (M + BP - 1) / BP, n_tiles = SWIGLU ? (inter + 127) / 128 : (N + tile_q - 1) / tile_q;
   const int total_tiles = m_tiles * n_tiles;
   const int nkb = (K + BK - 1) / BK;
 
@@ -392,13 +401,15 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
       bool ok = true;
       int it = 0;                                             // k-blocks issued so far, over all tiles
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int p0 = (tile % m_tiles) * BP, q0 = (tile / m_tiles) * tile_q;
+        const int p0 = (tile % m_tiles) * BP, q0 = (tile / m_tiles) * (SWIGLU ? 128 : tile_q);
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1);
           if (!ok) break;
           mbar_arrive_expect_tx(&full_bar[s], stage_tx);
           tma_load_2d(smem_q + s * Q_STAGE_BYTES, &map_q, kb * BK, q0, &full_bar[s]);
+          // the up rows of these gate rows: rows 128.. of the stage (a box is 128 rows of 128 bytes)
+          if (SWIGLU) tma_load_2d(smem_q + s * Q_STAGE_BYTES + 128 * 128, &map_q, kb * BK, inter + q0, &full_bar[s]);
           tma_load_2d(smem_p + s * P_STAGE_BYTES, &map_p, kb * BK, p0, &full_bar[s]);
         }
       }
@@ -444,27 +455,36 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
     int n = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++n) {
       const int buf = n & 1;
-      const int p0 = (tile % m_tiles) * BP, q0 = (tile / m_tiles) * tile_q;
+      const int p0 = (tile % m_tiles) * BP, q0 = (tile / m_tiles) * (SWIGLU ? 128 : tile_q);
       const int p = p0 + quad * 32 + lane;
       if (ok) ok = mbar_wait(&acc_full[buf], (n >> 1) & 1);
       fence_after_sync();
 #pragma unroll 1
-      for (int c = 0; c < tile_q; c += 32) {
+      for (int c = 0; c < (SWIGLU ? 128 : tile_q); c += 32) {
         float v[32];
         if (ok) {
           uint32_t r[32];
           tmem_ld_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BNQ + c), r);
-          tmem_ld_wait();
+          if (SWIGLU) {
+            uint32_t u[32];
+            tmem_ld_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BNQ + 128 + c), u);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            for (int j = 0; j < 32; ++j) v[j] = silu_times(__uint_as_float(r[j]), __uint_as_float(u[j]));
+          } else {
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          }
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0.f;
         }
         if (p >= M) continue;
         const int q = q0 + c;
+        const int q_limit = SWIGLU ? inter : N;
         TOut* row = C + (long long)p * ldc + q;
-        const bool vec_ok = (q + 32 <= N) && ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
+        const bool vec_ok = (q + 32 <= q_limit) && ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
         if (vec_ok) {
           if (sizeof(TOut) == 2) {
 #pragma unroll
@@ -484,7 +504,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (q + j < N) store_one(row + j, v[j]);
+            if (q + j < q_limit) store_one(row + j, v[j]);
         }
       }
       fence_before_sync();
@@ -577,10 +597,10 @@ int launch_cfg(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long 
   LLMK_LAUNCH_CHECK("gemm_tc");
 }
 
-template <typename TOut>
+template <typename TOut, bool SWIGLU>
 int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long ldc, int M, int N, int K,
                       int tile_q, cudaStream_t stream) {
-  auto kern = gemm_tc_persistent_kernel<TOut>;
+  auto kern = gemm_tc_persistent_kernel<TOut, SWIGLU>;
   constexpr int smem = smem_bytes_for(256);
   static bool configured = false;
   if (!configured) {
@@ -588,7 +608,7 @@ int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, void* C, lon
     if (e != cudaSuccess) return llmk_fail((int)e, "gemm_tc: cannot set %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  const int tiles = ((M + BP - 1) / BP) * ((N + tile_q - 1) / tile_q);
+  const int tiles = ((M + BP - 1) / BP) * (SWIGLU ? (N / 2 + 127) / 128 : (N + tile_q - 1) / tile_q);
   launch_kernel(kern, dim3(tiles < 148 ? tiles : 148), dim3(THREADS), (size_t)smem, stream, mp, mq, (TOut*)C, ldc, M, N, K,
                 tile_q, g_err_flag);
   LLMK_LAUNCH_CHECK("gemm_tc_persistent");
@@ -635,12 +655,19 @@ LLMK_API int llmk_gemm_tc_supported(const void* A, const void* W, int M, int N, 
 // tile form a thread-block cluster, sum their results on chip and write C as for splits == 1.
 // cluster == 2 selects the persistent kernel (normal mode, one split): one CTA per SM walks over
 // the tiles with two accumulators in tensor memory.
+// swiglu != 0 (persistent kernel only): W [N = 2I, K] is I gate rows followed by I up rows and C
+// [M, I] (bfloat16) receives silu(gate) * up instead of the product.
 // swap != 0 puts the weights on the 128-row side of the MMA; tile is the other side's width
 // (16, 32, 64 or 128 when swapped; a multiple of 32 up to 256 otherwise).
 LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
                           long long ldc, int out_dtype, int swap, int tile, int splits, int kblocks_per_split,
-                          int cluster, cudaStream_t stream) {
+                          int cluster, int swiglu, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
+  if (swiglu) {
+    LLMK_REQUIRE(cluster == 2 && !swap && splits == 1 && N % 2 == 0 && (N / 2) % 8 == 0,
+                 "gemm_tc: silu(gate) * up in the epilogue needs the persistent kernel and an even N with N/2 a multiple of 8, got N=%d", N);
+    tile = 256;       // 128 gate rows and their 128 up rows
+  }
   LLMK_REQUIRE(llmk_gemm_tc_supported(A, W, M, N, K, lda, ldw), "gemm_tc: K=%d and the row pitches must be multiples of 8 and the bases 16-byte aligned", K);
   LLMK_REQUIRE(splits >= 1 && kblocks_per_split >= 1 && (long long)splits * kblocks_per_split * BK >= K,
                "gemm_tc: %d splits of %d k-blocks do not cover K=%d", splits, kblocks_per_split, K);
@@ -659,12 +686,16 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
   const long long ldp = swap ? ldw : lda, ldq = swap ? lda : ldw;
   const int p_rows = swap ? N : M, q_rows = swap ? M : N;
   if ((rc = get_map(&mp, P, p_rows, K, ldp, BP))) return rc;
-  if ((rc = get_map(&mq, Q, q_rows, K, ldq, tile))) return rc;
+  if ((rc = get_map(&mq, Q, q_rows, K, ldq, swiglu ? 128 : tile))) return rc;
   if (cluster == 2) {       // persistent kernel: normal mode, no split
     LLMK_REQUIRE(!swap && splits == 1 && tile % 32 == 0 && tile >= 32 && tile <= 256,
                  "gemm_tc: the persistent kernel takes the normal mode, one split and a tile of 32..256 in steps of 32");
-    if (out_dtype == LLMK_F32) return launch_persistent<float>(mp, mq, C, ldc, M, N, K, tile, stream);
-    if (out_dtype == LLMK_BF16) return launch_persistent<__nv_bfloat16>(mp, mq, C, ldc, M, N, K, tile, stream);
+    if (swiglu) {
+      if (out_dtype == LLMK_BF16) return launch_persistent<__nv_bfloat16, true>(mp, mq, C, ldc, M, N, K, tile, stream);
+      return llmk_fail(-1, "gemm_tc: silu(gate) * up is written as bfloat16 only");
+    }
+    if (out_dtype == LLMK_F32) return launch_persistent<float, false>(mp, mq, C, ldc, M, N, K, tile, stream);
+    if (out_dtype == LLMK_BF16) return launch_persistent<__nv_bfloat16, false>(mp, mq, C, ldc, M, N, K, tile, stream);
     return llmk_fail(-1, "gemm_tc: unsupported output kind %d", out_dtype);
   }
   const long long split_stride = (splits > 1 && !cluster) ? (long long)M * ldc : 0;

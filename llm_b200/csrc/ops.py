@@ -494,18 +494,42 @@ def gemm_fast(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, pl
         _check(lib.llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
                                 c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
                                 c_int(_kind(out.dtype)), c_int(int(swap)), c_int(tile), c_int(splits), c_int(per),
-                                c_int(int(cluster)), _stream()))
+                                c_int(int(cluster)), c_int(0), _stream()))
         return out
     part = _partials(a.device)
     _check(lib.llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(part), c_int(rows), c_int(n), c_int(k),
                             c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(n), c_int(_F32),
-                            c_int(int(swap)), c_int(tile), c_int(splits), c_int(per), c_int(0), _stream()))
+                            c_int(int(swap)), c_int(tile), c_int(splits), c_int(per), c_int(0), c_int(0), _stream()))
     if allow_partial:
         return PartialSum(part, splits, rows, n, out.dtype)
     assert out.is_contiguous()
     _check(lib.llmk_reduce_partials(_ptr(out), _ptr(part), c_longlong(rows * n), c_int(splits),
                                     c_int(_kind(out.dtype)), _stream()))
     return out
+
+
+def gemm_swiglu_available(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int) -> bool:
+    """Whether gemm_swiglu takes this problem: bfloat16 throughout, more rows than the swapped
+    mode serves (there K is split over CTAs and the activation kernel sums the splits), an even
+    number of weight rows."""
+    return (rows > 128 and out.dtype == torch.bfloat16 and w.shape[0] % 16 == 0
+            and gemm_fast_available(a, w, out, rows))
+
+
+def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int) -> None:
+    """out[:rows] = silu(a @ gate.T) * (a @ up.T) for w = [gate; up] stacked along its rows
+    ([2I, K]), out [rows, I] bfloat16.  One persistent tensor-core kernel: each tile multiplies by
+    128 gate rows and their 128 up rows and applies the activation in its epilogue, so the
+    product never reaches memory."""
+    _rows_contig(a, "a"); _rows_contig(w, "w"); _rows_contig(out, "out")
+    n, k = w.shape
+    assert a.shape[1] == k and out.shape[1] == n // 2 and n % 2 == 0
+    if not gemm_swiglu_available(a, w, out, rows):
+        raise KernelError(f"gemm_swiglu does not take {rows} rows of {a.dtype} -> {out.dtype}")
+    _check(load().llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
+                               c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
+                               c_int(_BF16), c_int(0), c_int(256), c_int(1), c_int(_ceil_div(k, 64)),
+                               c_int(2), c_int(1), _stream()))
 
 
 def set_pdl(on: bool) -> None:

@@ -2,7 +2,8 @@
 
 The reference runs gate and up as two products and the activation as a third kernel
 (model/modules/MLP.h:10-13, kernel/activation/SwiGLU.h:31-33); here gate and up are
-one product over a stacked weight.
+one product over a stacked weight, and with many rows (prompts) the product's epilogue applies
+the activation itself, so that the stacked product never reaches memory.
 """
 from __future__ import annotations
 
@@ -10,7 +11,7 @@ import torch
 
 from ..csrc import ops
 from .base import ParamInfo, Part, register_part
-from .linear import FUSE_PARTIALS, linear
+from .linear import FUSE_PARTIALS, linear, linear_swiglu
 
 
 class SwiGLU(Part):
@@ -36,10 +37,11 @@ class SwiGLU(Part):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         T, ws = ctx.n_tokens, ctx.workspace
-        gate_up = linear(x, self.w_gate_up, ws.get("gate_up", T, 2 * self.intermediate_size, self.dtype), T,
-                         allow_partial=FUSE_PARTIALS)
         act = ws.get("ffn_act", T, self.intermediate_size, self.dtype)
-        ops.silu_mul(act, gate_up, T)
+        if not linear_swiglu(x, self.w_gate_up, act, T):
+            gate_up = linear(x, self.w_gate_up, ws.get("gate_up", T, 2 * self.intermediate_size, self.dtype), T,
+                             allow_partial=FUSE_PARTIALS)
+            ops.silu_mul(act, gate_up, T)
         return linear(act, self.w_down, ws.get("ffn_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
 
 

@@ -31,3 +31,17 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int, 
         return ops.gemm_fast(x, weight, out, rows, allow_partial=allow_partial)
     ops.gemm_simt(x, weight, out, rows)
     return out
+
+
+def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int) -> bool:
+    """out[:rows] = silu(x @ gate.T) * (x @ up.T) for weight = [gate; up] stacked along its rows,
+    with the activation applied in the product's epilogue.  Returns False, having done nothing,
+    where that is not possible (float32, shapes the tensor-core kernel refuses, or so few rows
+    that the product splits its K dimension): the caller then runs the product and the activation
+    kernel."""
+    if rows == 0:
+        return True
+    if x.dtype != torch.bfloat16 or not ops.gemm_swiglu_available(x, weight, out, rows):
+        return False
+    ops.gemm_swiglu(x, weight, out, rows)
+    return True

@@ -179,6 +179,48 @@ def test_gemm_tensor_core_persistent(ops, M, N, K, tile, out_dtype):
     assert float(out2[M - 1, N - 1]) == 8.0 and float(out2.float().abs().sum()) == 8.0
 
 
+@pytest.mark.parametrize("M,I,K", [
+    (300, 272, 5 * 64 + 24),        # 9 tiles, a ragged last tile of gate rows that runs into the up rows
+    (2100, 976, 3 * 64),            # 136 tiles
+    (1300, 1048, 7 * 64 + 8),       # I no multiple of 16; more k-blocks than stages
+    (2048, 5632, 256)])             # 704 tiles: CTAs take four or five each
+def test_gemm_tensor_core_with_silu_epilogue(ops, M, I, K):
+    """silu(gate) * up written by the product's epilogue: a tile takes 128 gate rows and their up rows."""
+    torch.manual_seed(9)
+    a = torch.randn(M + 1, K, device=DEV).to(torch.bfloat16)
+    gate = (torch.randn(I, K, device=DEV) / math.sqrt(K) * 3).to(torch.bfloat16)
+    up = (torch.randn(I, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    w = torch.cat([gate, up]).contiguous()
+    out = torch.full((M + 1, I), 3.0, device=DEV, dtype=torch.bfloat16)
+    assert ops.gemm_swiglu_available(a, w, out, M)
+    ops.gemm_swiglu(a, w, out, M)
+    torch.cuda.synchronize()
+    assert ops.gemm_tc_take_error() == 0
+    g = a[:M].double() @ gate.double().T
+    u = a[:M].double() @ up.double().T
+    ref = g / (1 + torch.exp(-g)) * u
+    assert rel_err(out[:M], ref) < 1e-2
+    assert float(out[M:].float().min()) == 3.0 and float(out[M:].float().max()) == 3.0
+    # one large gate and up in the last row and column land exactly there
+    a2 = torch.zeros(M, K, device=DEV, dtype=torch.bfloat16)
+    w2 = torch.zeros(2 * I, K, device=DEV, dtype=torch.bfloat16)
+    a2[M - 1, K - 1] = 2.0
+    w2[I - 1, K - 1] = 8.0          # gate = 16: silu(16) = 16 to bfloat16 precision
+    w2[2 * I - 1, K - 1] = 0.5      # up = 1
+    out2 = torch.full((M, I), 1.0, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_swiglu(a2, w2, out2, M)
+    assert float(out2[M - 1, I - 1]) == 16.0 and float(out2.float().abs().sum()) == 16.0
+
+
+def test_gemm_silu_epilogue_is_not_offered_for_few_rows_or_float32(ops):
+    a = torch.zeros(8, 512, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(256, 512, device=DEV, dtype=torch.bfloat16)
+    assert not ops.gemm_swiglu_available(a, w, torch.zeros(8, 128, device=DEV, dtype=torch.bfloat16), 8)
+    a = torch.zeros(300, 512, device=DEV, dtype=torch.bfloat16)
+    assert not ops.gemm_swiglu_available(a, w, torch.zeros(300, 128, device=DEV), 300)
+    assert ops.gemm_swiglu_available(a, w, torch.zeros(300, 128, device=DEV, dtype=torch.bfloat16), 300)
+
+
 def test_gemm_tensor_core_refuses_unaligned_rows(ops):
     a = torch.zeros(4, 172, device=DEV, dtype=torch.bfloat16)
     w = torch.zeros(64, 172, device=DEV, dtype=torch.bfloat16)
