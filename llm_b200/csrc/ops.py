@@ -6,6 +6,7 @@ not on a CUDA device, they raise.
 from __future__ import annotations
 
 import ctypes
+import functools
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -230,6 +231,7 @@ def sample_rows(out: torch.Tensor, logits: torch.Tensor, rows: int, temperature=
 
 
 _ATTN_PARTIALS = {}
+_ATTN_PARTIALS_RETIRED = []      # outgrown buffers stay alive: captured graphs may still hold their addresses
 
 
 def _attn_partials(device, n_floats: int) -> torch.Tensor:
@@ -237,6 +239,8 @@ def _attn_partials(device, n_floats: int) -> torch.Tensor:
     that the kernel expects to be zero and leaves zero."""
     buf = _ATTN_PARTIALS.get(device)
     if buf is None or buf.numel() < n_floats:
+        if buf is not None:
+            _ATTN_PARTIALS_RETIRED.append(buf)
         buf = torch.zeros(max(n_floats, 1 << 20), dtype=torch.float32, device=device)
         _ATTN_PARTIALS[device] = buf
     return buf
@@ -413,6 +417,11 @@ PERSISTENT_GEMM = True
 
 
 def plan_gemm(M: int, N: int, K: int, fused_reduce: bool = False):
+    return _plan_gemm(M, N, K, fused_reduce, PERSISTENT_GEMM)
+
+
+@functools.lru_cache(maxsize=4096)
+def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool):
     """(swap, tile, splits, k-blocks per split, mode) for the tensor-core product; mode 0 = one
     CTA per tile, 1 = the splits of a tile sum on chip in a cluster, 2 = persistent CTAs.
 
@@ -447,7 +456,7 @@ def plan_gemm(M: int, N: int, K: int, fused_reduce: bool = False):
                 break
             waves = _ceil_div(tiles * s, _SMS)
             cost = waves * (per * t_kb + 2.5)
-            if PERSISTENT_GEMM and not swap and s == 1 and tiles > _SMS:
+            if persistent and not swap and s == 1 and tiles > _SMS:
                 # more than one wave of tiles: one CTA per SM walks over them and drains one
                 # accumulator while the next tile's products run, so the fixed cost is paid once
                 cluster = 2

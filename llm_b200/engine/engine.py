@@ -69,6 +69,8 @@ class _MetaLayout:
 
 
 class Engine:
+    MAX_PROMPT_GRAPHS = 64        # captured shapes of steps that bring prompt portions
+
     def __init__(self, model_dir: Optional[str], options: Optional[EngineOptions] = None, *,
                  random_config: Optional[dict] = None, random_seed: int = 0):
         """model_dir: a folder with config.json and model.safetensors.  Without a folder,
@@ -110,7 +112,9 @@ class Engine:
 
         self._init_cache()
         self._init_buffers()
-        self._graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
+        self._graphs: Dict[tuple, tuple] = {}            # key -> (graph, kernel launches inside)
+        self._graph_seen: Dict[tuple, int] = {}          # how often a shape that is not yet captured has come
+        self._prompt_graphs = 0
         self.counters = {"steps": 0, "tokens": 0, "graph_captures": 0, "graph_replays": 0}
 
     # ---- set-up -------------------------------------------------------------
@@ -371,14 +375,22 @@ class Engine:
         R = ctx.n_logit_rows
         if R:
             self._logit_buffers(R)
-        # A step of single tokens has launch parameters that depend on the batch size alone
-        # and on the bucket of the longest context (everything else is read from the metadata
-        # buffer), so it is captured once per (entries, rows, bucket) and replayed: the reference captures per GraphShape{batch, tokens}
-        # the same way (runtime/LLM.h:63-72,192-201).
-        graphable = (self.options.use_cuda_graphs and ctx.decode_only and R in (0, ctx.n_entries))
+        # The launch parameters of a step depend only on its numbers of entries, tokens and wanted
+        # rows and, for a step of single tokens, on the bucket of the longest context; everything
+        # else is read from the metadata buffer on the device.  So a step is captured once per such
+        # key and replayed (the reference captures per GraphShape{batch, tokens} the same way,
+        # runtime/LLM.h:63-72,192-201): steps of single tokens at once, other shapes when they come
+        # a second time (a portion of the full token budget recurs, a ragged last portion does not).
+        graphable = self.options.use_cuda_graphs
         if graphable:
-            key = (ctx.n_entries, R, ctx.kv_bucket)     # kernels size their grids by the bucket
+            key = (ctx.n_entries, ctx.n_tokens, R, ctx.kv_bucket if ctx.decode_only else 0)
             entry = self._graphs.get(key)
+            if entry is None and not ctx.decode_only:
+                seen = self._graph_seen.get(key, 0)
+                self._graph_seen[key] = seen + 1
+                if seen == 0 or self._prompt_graphs >= self.MAX_PROMPT_GRAPHS:
+                    graphable = False
+        if graphable:
             if entry is not None:
                 entry[0].replay()
                 ops.count_launches(entry[1])
@@ -393,6 +405,8 @@ class Engine:
                 self._graphs[key] = (graph, ops.launch_count() - before)
                 ops.count_launches(-(ops.launch_count() - before))
                 self.counters["graph_captures"] += 1
+                if not ctx.decode_only:
+                    self._prompt_graphs += 1
         else:
             self._forward(ctx)
         self.counters["steps"] += 1

@@ -91,3 +91,57 @@ def test_greedy_generation_matches_plain(models, dtype):
                 assert float(row.max() - row[tok]) <= 2 * TOL[dtype] * float(row.abs().max())
                 ids.append(tok)
     llm.engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+def test_recurring_prompt_shapes_replayed_from_graphs_match_plain(models, name, dtype):
+    """With CUDA graphs on, a step shape (entries, tokens, wanted rows) that comes a second time is
+    captured and replayed from then on, for prompt portions as for decoded tokens.  The same
+    requests in portions of one size, twice over with pages used again, and mixed with decoded
+    tokens of other requests: every logit against the plain implementation."""
+    from llm_b200.config import EngineOptions
+    from llm_b200.engine.engine import Engine, StepEntry
+    d, cfg, page, reqs, ref = models(name, dtype)
+    longest = max(len(t) for t in reqs.values())
+    eng = Engine(d, EngineOptions(dtype=dtype, kv_block_size=page, max_num_seqs=4, max_num_batched_tokens=512,
+                                  num_kv_blocks=2 * ((longest + page - 1) // page) + 2, use_cuda_graphs=True))
+    chunk = 24
+    for round_ in range(2):
+        got = {}
+        for rid, toks in reqs.items():
+            rows = []
+            for a in range(0, len(toks), chunk):
+                part = toks[a:a + chunk]
+                rows.append(eng.step([StepEntry(rid, part, list(range(len(part))))]).double().cpu().clone())
+            got[rid] = torch.cat(rows)
+            eng.release(rid)
+        compare(got, ref, dtype, f"portions of {chunk}, round {round_}")
+    assert eng.counters["graph_replays"] > 0 and eng.counters["graph_captures"] >= 1
+    # a portion of one request beside a decoded token of another, the same shape again and again
+    ids = list(reqs)
+    long_id = max(ids, key=lambda r: len(reqs[r]))
+    short_id = min(ids, key=lambda r: len(reqs[r]))
+    before = eng.counters["graph_replays"]
+    got = {long_id: [], short_id: []}
+    lt, st = reqs[long_id], reqs[short_id]
+    got[short_id].append(eng.step([StepEntry(short_id, st[:1], [0])]).double().cpu().clone())
+    at, k = 0, 1
+    while at < len(lt):
+        part = lt[at:at + 16]
+        entries = [StepEntry(long_id, part, list(range(len(part))))]
+        if k < len(st):
+            entries.append(StepEntry(short_id, [st[k]], [0]))
+        out = eng.step(entries).double().cpu().clone()
+        got[long_id].append(out[:len(part)])
+        if k < len(st):
+            got[short_id].append(out[len(part):])
+            k += 1
+        at += len(part)
+    while k < len(st):
+        got[short_id].append(eng.step([StepEntry(short_id, [st[k]], [0])]).double().cpu().clone())
+        k += 1
+    compare({r: torch.cat(v) for r, v in got.items()}, {r: ref[r] for r in got}, dtype, "portion beside a decoded token")
+    if len(lt) >= 4 * 16 and len(st) > 4:
+        assert eng.counters["graph_replays"] > before
+    eng.cache.check()
