@@ -76,9 +76,14 @@ constexpr int P_STAGE_BYTES = BP * BK * 2;
 __host__ __device__ constexpr int q_stage_bytes(int bnq) { return bnq * BK * 2; }
 // Narrow tiles keep the ring at six stages so that two CTAs fit on an SM: the CTAs of the next
 // product can then stage their weights while this one drains.
-__host__ __device__ constexpr int stages_for(int bnq) { return bnq >= 256 ? 4 : 6; }
-__host__ __device__ constexpr int smem_bytes_for(int bnq) {
-  return stages_for(bnq) * (P_STAGE_BYTES + q_stage_bytes(bnq)) + 1024 /* alignment */ + 256 /* barriers */;
+// Stages of the ring.  In the swapped mode (few rows, bound by the weights' way from memory) two
+// CTAs share an SM, so that twice as many CTAs stream weights at a time: their rings are sized to
+// about 100 KB each.  In the normal mode one CTA has the SM.
+__host__ __device__ constexpr int stages_for(int bnq, bool swap = false) {
+  return bnq >= 256 ? 4 : !swap ? 6 : bnq <= 16 ? 6 : bnq <= 32 ? 5 : bnq <= 64 ? 4 : 3;
+}
+__host__ __device__ constexpr int smem_bytes_for(int bnq, bool swap = false) {
+  return stages_for(bnq, swap) * (P_STAGE_BYTES + q_stage_bytes(bnq)) + 1024 /* alignment */ + 256 /* barriers */;
 }
 __host__ __device__ constexpr uint32_t tmem_cols_for(int bnq) { return bnq < 32 ? 32 : bnq; }
 
@@ -93,13 +98,13 @@ enum : int { ERR_PRODUCER = 1, ERR_MMA = 2, ERR_EPILOGUE = 3 };
 // kernel to sum, each CTA hands its accumulator to the first CTA of the cluster through
 // distributed shared memory; that CTA adds them in the order of the splits and stores the result.
 template <int BNQ, bool SWAP, typename TOut, bool CLUSTER>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, SWAP ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                TOut* __restrict__ C, long long ldc, long long split_stride, int M, int N, int K,
                int kblocks_per_split, int tile_q, int* __restrict__ err_flag) {
   // BNQ sizes the stages and the tensor memory; tile_q <= BNQ (a multiple of 32, or 16 = BNQ) is
   // the width actually computed, chosen on the host so that the grid fills whole waves.
-  constexpr int STAGES = stages_for(BNQ);
+  constexpr int STAGES = stages_for(BNQ, SWAP);
   constexpr int Q_STAGE_BYTES = q_stage_bytes(BNQ);
   constexpr uint32_t TMEM_COLS = tmem_cols_for(BNQ);
   const uint32_t IDESC = idesc_bf16_f32(BP, tile_q);
@@ -566,7 +571,7 @@ template <int BNQ, bool SWAP, typename TOut, bool CLUSTER>
 int launch_cfg(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long ldc, long long split_stride, int M,
                int N, int K, int splits, int kb_per_split, int tile_q, cudaStream_t stream) {
   auto kern = gemm_tc_kernel<BNQ, SWAP, TOut, CLUSTER>;
-  constexpr int smem = smem_bytes_for(BNQ);
+  constexpr int smem = smem_bytes_for(BNQ, SWAP);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -675,7 +680,7 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
   LLMK_REQUIRE(splits == 1 || cluster || out_dtype == LLMK_F32, "gemm_tc: split-K without a cluster needs a float32 output");
   if (cluster == 1) {
     LLMK_REQUIRE(swap && tile <= 64 && splits <= 8, "gemm_tc: cluster reduction needs the swapped mode, a tile up to 64 and at most 8 splits");
-    LLMK_REQUIRE((long long)(splits - 1) * tile * BP * 4 <= (long long)stages_for(tile) * (P_STAGE_BYTES + q_stage_bytes(tile)),
+    LLMK_REQUIRE((long long)(splits - 1) * tile * BP * 4 <= (long long)stages_for(tile, true) * (P_STAGE_BYTES + q_stage_bytes(tile)),
                  "gemm_tc: %d splits of a %d-row tile do not fit the stage ring for the on-chip sum", splits, tile);
   }
   LLMK_REQUIRE(splits <= 65535, "gemm_tc: too many splits");

@@ -404,7 +404,7 @@ def _ceil_div(a: int, b: int) -> int:
     return -(-a // b)
 
 
-_RING_BYTES = {16: 6 * (16384 + 2048), 32: 6 * (16384 + 4096), 64: 6 * (16384 + 8192)}
+_RING_BYTES = {16: 6 * (16384 + 2048), 32: 5 * (16384 + 4096), 64: 4 * (16384 + 8192)}
 
 
 def cluster_fits(tile: int, splits: int) -> bool:
@@ -434,40 +434,71 @@ def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool):
     tensor-core time and its share of HBM time; times the number of waves; plus the sum."""
     kb = _ceil_div(K, 64)
     if M <= 128:
-        options = [(True, 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128, _ceil_div(N, 128))]
-    else:
-        options = [(False, t, _ceil_div(M, 128) * _ceil_div(N, t)) for t in (256, 224, 192, 160, 128)]
+        return _plan_swapped(M, N, kb, fused_reduce)
+    options = [(False, t, _ceil_div(M, 128) * _ceil_div(N, t)) for t in (256, 224, 192, 160, 128)]
     best = None
     for swap, tile, tiles in options:
         # us per k-block at one SM's tensor peak; a tile of 128 or less reads as many bytes from
         # shared memory per MMA as the tensor core consumes and runs at about two thirds of that
-        t_mma = 128 * tile * 64 * 2 / 15.2e6 * (1.5 if (not swap and tile <= 128) else 1.0)
-        t_mem = (128 + tile) * 128 / 45e3 if swap else 0.0          # us per k-block at one SM's HBM share
-        t_kb = max(t_mma, t_mem)
+        t_kb = 128 * tile * 64 * 2 / 15.2e6 * (1.5 if tile <= 128 else 1.0)
         for s in range(1, min(kb, 32) + 1):
             per = _ceil_div(kb, s)
             if _ceil_div(kb, per) != s:
                 continue
-            # On-chip sums through a cluster measured slower at decode sizes than partial results plus
-            # a reduction kernel: a cluster needs all its CTAs scheduled at once, which takes away
-            # the early start of the next product's weight loads.  Kept as an option of gemm_fast.
-            cluster = 0
-            if s > 1 and not cluster and s * M * N * 4 > _PARTIAL_BYTES:
+            if s > 1 and s * M * N * 4 > _PARTIAL_BYTES:
                 break
+            mode = 0
             waves = _ceil_div(tiles * s, _SMS)
             cost = waves * (per * t_kb + 2.5)
-            if persistent and not swap and s == 1 and tiles > _SMS:
+            if persistent and s == 1 and tiles > _SMS:
                 # more than one wave of tiles: one CTA per SM walks over them and drains one
                 # accumulator while the next tile's products run, so the fixed cost is paid once
-                cluster = 2
+                mode = 2
                 cost = waves * per * t_kb + 2.5
-            if cluster == 1:
-                cost += 0.8
-            elif s > 1:
+            if s > 1:
                 traffic = (2 * s + 1) * M * N * 4 / 4e6               # partials written and read back, us
                 cost += traffic + (0.5 if fused_reduce else 3.0)
             if best is None or cost < best[0] - 1e-9:
-                best = (cost, swap, tile, s, per, cluster)
+                best = (cost, swap, tile, s, per, mode)
+    return best[1:]
+
+
+_SWAPPED_STAGES = {16: 6, 32: 5, 64: 4, 128: 3}      # as stages_for() in gemm_tc.cu
+
+
+def _plan_swapped(M: int, N: int, kb: int, fused_reduce: bool):
+    """The swapped mode (up to 128 rows): a stream of weights.  Two CTAs share an SM, so up to 296
+    run at a time.  A CTA alone is bound by what its ring keeps in flight (stages x stage bytes per
+    memory latency of about 2 us), the CTAs of one SM by its way to L2, all CTAs together by HBM;
+    the constants were fitted to timings of the five products of the 1.1B shape at 16, 32, 64 and
+    128 rows (the plans picked this way are within 1 % of the best measured ones in sum).  On-chip sums through a cluster measured
+    slower at decode sizes than partial results plus a summing consumer (a cluster needs all its
+    CTAs scheduled at once, which takes away the early start of the next product's weight loads);
+    they stay an option of gemm_fast."""
+    tile = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+    tiles = _ceil_div(N, 128)
+    stage_bytes = (128 + tile) * 128
+    t_mma = 128 * tile * 64 * 2 / 15.2e6
+    best = None
+    for s in range(1, min(kb, 32) + 1):
+        per = _ceil_div(kb, s)
+        if _ceil_div(kb, per) != s:
+            continue
+        if s > 1 and s * M * N * 4 > _PARTIAL_BYTES:
+            break
+        n_cta = tiles * s
+        rounds = _ceil_div(n_cta, 2 * _SMS)
+        conc = n_cta if rounds == 1 else 2 * _SMS
+        per_sm = min(2, _ceil_div(n_cta, _SMS))           # CTAs on the fullest SM: they share its tensor pipe and its way to L2
+        t_kb = max(t_mma * per_sm, 2.3 / _SWAPPED_STAGES[tile], stage_bytes * conc / 8.0e6, stage_bytes * per_sm / 80e3)
+        cost = rounds * per * t_kb + 1.8
+        if s > 1:
+            cost += s * M * N * 4 / 7e6                   # partial results written
+            # and summed: by their consumer (four splits' loads in flight at a time, so every
+            # further four splits cost it another trip to L2), or by a kernel of their own
+            cost += 0.5 * _ceil_div(s, 4) + s * M * N * 4 / 7e6 if fused_reduce else 3.0
+        if best is None or cost < best[0] - 1e-9:
+            best = (cost, True, tile, s, per, 0)
     return best[1:]
 
 

@@ -233,6 +233,7 @@ class Engine:
             raise StepError(f"{len(entries)} entries exceed max_num_seqs {self.max_entries}")
         seen = set()
         n_tokens = n_rows = 0
+        token_arrays = []                                  # each entry's tokens, checked and converted once (an int for one token)
         for e in entries:
             if e.request_id in seen:
                 raise StepError(f"request {e.request_id!r} appears twice in one step")
@@ -246,8 +247,20 @@ class Engine:
             if e.feed is not None:
                 if n != 1 or feed_source is None or not (0 <= e.feed < feed_source.numel()):
                     raise StepError(f"request {e.request_id!r}: a fed entry brings one token from a row of feed_source")
-            elif min(e.tokens) < 0 or max(e.tokens) >= self.vocab:
-                raise StepError(f"request {e.request_id!r}: token id outside [0, {self.vocab})")
+                token_arrays.append(0)
+            elif n == 1:
+                tok = e.tokens[0]
+                if not (0 <= tok < self.vocab):
+                    raise StepError(f"request {e.request_id!r}: token id outside [0, {self.vocab})")
+                token_arrays.append(int(tok))
+            else:
+                try:
+                    arr = np.asarray(e.tokens, dtype=np.int64)
+                except (OverflowError, TypeError, ValueError):
+                    raise StepError(f"request {e.request_id!r}: token ids must be integers in [0, {self.vocab})") from None
+                if arr.ndim != 1 or int(arr.min()) < 0 or int(arr.max()) >= self.vocab:
+                    raise StepError(f"request {e.request_id!r}: token id outside [0, {self.vocab})")
+                token_arrays.append(arr)
             n_tokens += n
             n_rows += len(e.want)
         if n_tokens > self.max_tokens:
@@ -299,12 +312,11 @@ class Engine:
         if T == B:                                  # one token each: no repeats needed
             entry_of = np.arange(B, dtype=np.int64)
             pos = starts
-            host[lay.token_ids: lay.token_ids + T] = [e.tokens[0] if e.feed is None else 0 for e in entries]
+            host[lay.token_ids: lay.token_ids + T] = token_arrays
         else:
             entry_of = np.repeat(np.arange(B, dtype=np.int64), ns)
             pos = starts[entry_of] + (np.arange(T, dtype=np.int64) - cu[entry_of])
-            host[lay.token_ids: lay.token_ids + T] = np.concatenate(
-                [np.asarray(e.tokens if e.feed is None else [0], dtype=np.int32) for e in entries])
+            host[lay.token_ids: lay.token_ids + T] = np.concatenate([np.atleast_1d(a) for a in token_arrays])
         host[lay.positions: lay.positions + T] = pos
         host[lay.token_entry: lay.token_entry + T] = entry_of
         host[lay.cu_tokens: lay.cu_tokens + B + 1] = cu
