@@ -374,8 +374,9 @@ int launch_decode_mma(void* out, long long out_stride, const void* q, long long 
   const int recv_bytes = (splits - 1) * group_rows * head_dim * 4;
   const bool cluster = splits >= 2 && splits <= 8 && (long long)splits * n_kv * n_entries <= 2 * 148 &&
                        recv_bytes <= RECV_LIMIT;
-  // per warp two stages (one in a cluster) of a tile of keys and a tile of values
-  const int stage_bytes = 4 * (cluster ? 1 : 2) * 2 * decode_mma::TILE * head_dim * 2;
+  // per warp a few stages (one in a cluster; three at head size 64, else two) of a tile of keys
+  // and a tile of values: NST in the kernel
+  const int stage_bytes = 4 * (cluster ? 1 : head_dim == 64 ? 3 : 2) * 2 * decode_mma::TILE * head_dim * 2;
   using Kernel = decltype(&decode_mma::decode_attention_mma_kernel<64, false, FUSED>);
   const Kernel kern = head_dim == 64
       ? (cluster ? decode_mma::decode_attention_mma_kernel<64, true, FUSED> : decode_mma::decode_attention_mma_kernel<64, false, FUSED>)
@@ -432,7 +433,8 @@ LLMK_API int llmk_paged_attention_decode(void* out, long long out_stride, const 
   LLMK_REQUIRE((long long)n_entries * n_kv <= COUNTER_WORDS, "attention_decode: %d entries x %d kv heads exceed %d counters",
                n_entries, n_kv, COUNTER_WORDS);
   LLMK_REQUIRE(page_size > 0 && window >= 0, "attention_decode: bad page_size %d or window %d", page_size, window);
-  if (dtype == LLMK_BF16 && (head_dim == 64 || head_dim == 128) && q_stride % 2 == 0 && (uintptr_t)q % 4 == 0) {
+  if (dtype == LLMK_BF16 && (head_dim == 64 || head_dim == 128) && q_stride % 2 == 0 && (uintptr_t)q % 4 == 0 &&
+      (page_size & (page_size - 1)) == 0) {
     // bfloat16 with a head size of 64 or 128: the query heads of a group as rows of warp-level MMAs
     return launch_decode_mma<false>(out, out_stride, q, q_stride, k_pages, v_pages, block_table, table_width, kv_lens,
                                     n_entries, n_heads, n_kv, head_dim, page_size, scale, window, splits, scratch,
@@ -484,7 +486,8 @@ LLMK_API int llmk_decode_attention_fused(void* out, long long out_stride, const 
   LLMK_REQUIRE(n_kv <= 65535 && n_entries <= 65535, "decode_attention_fused: grid too large");
   LLMK_REQUIRE((long long)n_entries * n_kv <= COUNTER_WORDS, "decode_attention_fused: %d entries x %d kv heads exceed %d counters",
                n_entries, n_kv, COUNTER_WORDS);
-  LLMK_REQUIRE(page_size > 0 && window >= 0, "decode_attention_fused: bad page_size %d or window %d", page_size, window);
+  LLMK_REQUIRE(page_size > 0 && (page_size & (page_size - 1)) == 0 && window >= 0,
+               "decode_attention_fused: the page size %d must be a power of two, the window %d not negative", page_size, window);
   LLMK_REQUIRE(src_stride >= (long long)(n_heads + (write_kv ? 2 * n_kv : 0)) * head_dim,
                "decode_attention_fused: a row of %lld values does not hold the heads", src_stride);
   decode_mma::FusedQkv f{{(const __nv_bfloat16*)qkv, partials, qkv_splits, split_stride}, src_stride, cos_table, sin_table, write_kv};

@@ -44,7 +44,13 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+// Wait until at most n of the most recent groups are still in flight (n = 0..3).
+__device__ __forceinline__ void cp_async_wait_pending(int n) {
+  if (n <= 0) asm volatile("cp.async.wait_all;" ::: "memory");
+  else if (n == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
+  else if (n == 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+  else asm volatile("cp.async.wait_group 3;" ::: "memory");
+}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -110,11 +116,11 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
   constexpr int DT = HS / 8;                   // 8-wide tiles of the output row
   constexpr int CH = HS / 8;                   // 16-byte chunks of a row
   constexpr int V_BYTES = TILE * HS * 2;       // one tile of keys, or of values
-  // Stages of (keys, values) per warp.  Two let the next tile fly while one is computed, which
-  // pays for long ranges.  A cluster is only formed for short ranges on a small grid; there one
+  // Stages of (keys, values) per warp.  Several let the next tiles fly while one is computed,
+  // which pays for long ranges (three where two CTAs then still fit on an SM).  A cluster is only formed for short ranges on a small grid; there one
   // stage keeps the CTA small enough to become resident beside the CTAs of the kernel before it,
   // which is what lets its early requests overlap that kernel.
-  constexpr int NST = CLUSTER ? 1 : 2;
+  constexpr int NST = CLUSTER ? 1 : (HS == 64 ? 3 : 2);
   constexpr int WARP_BYTES = NST * 2 * V_BYTES;
   constexpr int RANGES = CLUSTER ? 8 : 64;     // most ranges that a merge in shared memory takes
   static_assert(4 * WARP_BYTES >= 4 * ROWS * HS * 4, "the warps' results are merged in the stage buffers");
@@ -140,6 +146,13 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
   const int k_end = min(pos + 1, k_begin + chunk);
   const int* table = block_table + (size_t)e * table_width;
   const int qrow = lane >> 2, qcol = (lane & 3) * 2;
+  // the row of key k of this request and kv head in the pages.  The page size is a power of two
+  // (the host sends other sizes to the CUDA-core kernel): a division per row of every tile would
+  // cost more than the tile's arithmetic
+  const int page_shift = __ffs(page_size) - 1;
+  auto row_of = [&](int k) -> size_t {
+    return ((((size_t)table[k >> page_shift] * n_kv + g) << page_shift) + (k & (page_size - 1))) * HS;
+  };
   uint8_t* w_buf = vbuf + warp * WARP_BYTES;                 // stage st: keys at st * 2 * V_BYTES, values V_BYTES further
   const uint32_t w_addr = (uint32_t)__cvta_generic_to_shared(w_buf);
   const int t_first = k_begin + warp * TILE;                // this warp's first tile
@@ -157,7 +170,7 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
       const int kp = t + kl;
       const bool valid = kp < k_end;
       const int kq = valid ? kp : k_begin;
-      const size_t row = (((size_t)table[kq / page_size] * n_kv + g) * page_size + kq % page_size) * HS;
+      const size_t row = row_of(kq);
       const int cs = (c & ~7) | ((c ^ kl) & 7);
       cp_async_16(dst + kl * (HS * 2) + cs * 16, k_pages + row + c * 8, valid);
       cp_async_16(dst + V_BYTES + kl * (HS * 2) + cs * 16, v_pages + row + c * 8, valid);
@@ -166,18 +179,19 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
   };
 
   // Lengths and block tables were copied before the step's first kernel, and every key but the
-  // newest was stored by an earlier step.  So each warp requests its first two tiles, and the
+  // newest was stored by an earlier step.  So each warp requests its first tiles, and the
   // CTA asks the rest of its range into L2, while the kernels before this one still run; only
   // the queries and the newest key and value (stored by a kernel of this step, or by this one)
   // have to wait.  The newest row of a tile is replaced after it has landed, see below.
-  if (n_tiles > 0) stage_tile(0);
-  if (NST > 1 && n_tiles > 1) stage_tile(1);
+#pragma unroll
+  for (int j = 0; j < NST; ++j)
+    if (j < n_tiles) stage_tile(j);
   {
     constexpr int LINES = HS * 2 / 128;                    // 128-byte lines per row
     const int n_rows = max(0, k_end - k_begin - NST * 4 * TILE);
     for (int i = tid; i < n_rows * LINES * 2; i += THREADS) {
       const int which = i & 1, line = (i >> 1) % LINES, kp = k_begin + NST * 4 * TILE + (i >> 1) / LINES;
-      const size_t row = (((size_t)table[kp / page_size] * n_kv + g) * page_size + kp % page_size) * HS;
+      const size_t row = row_of(kp);
       const __nv_bfloat16* src = (which ? v_pages : k_pages) + row + line * 64;
       asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
     }
@@ -186,14 +200,14 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
 
   // the newest key and value are read, once they are valid, from the pages, or from this CTA's
   // shared copy when it computes them itself
-  const size_t new_row = (((size_t)table[pos / page_size] * n_kv + g) * page_size + pos % page_size) * HS;
+  const size_t new_row = row_of(pos);
   const bool owner = FUSED && fused.write_kv && k_begin <= pos && pos < k_end;
   // FUSED, owner: the last threads sum the newest token's key (two pairs each) and value (two
   // elements each); their loads are issued here and used after the queries' loads below
   const int kv_item = THREADS - 1 - tid;
   const bool does_k = owner && kv_item < HS / 4, does_v = owner && !does_k && kv_item < HS / 4 + HS / 2;
   float2 nk_a = make_float2(0.f, 0.f), nk_b = nk_a, nv = nk_a;
-  if (FUSED) {
+  if constexpr (FUSED) {
     const size_t src_row = (size_t)e * fused.src_stride;
     if (does_k) {
       const size_t h = src_row + (size_t)(n_heads + g) * HS + kv_item * 2;
@@ -215,7 +229,7 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
     // Q fragments: rows = heads, straight from global memory (4 bytes = 2 bf16 per load)
     uint32_t qf[KS][4];
     const __nv_bfloat16* q0;
-    if (FUSED) {
+    if constexpr (FUSED) {
       // the pass's queries: summed, rotated, rounded to bfloat16 into shared memory; two pairs
       // (i, i+1 and their partners half a head further) per item, all loads issued before any use
       constexpr int ITEMS = ROWS * (HS / 4) / THREADS;
@@ -283,13 +297,14 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;        // rows qrow and qrow + 8 (l: this lane's share)
 
     if (h0 > 0) {                                                 // a later pass requests its tiles again
-      if (n_tiles > 0) stage_tile(0);
-      if (NST > 1 && n_tiles > 1) stage_tile(1);
+#pragma unroll
+      for (int j = 0; j < NST; ++j)
+        if (j < n_tiles) stage_tile(j);
     }
     for (int j = 0; j < n_tiles; ++j) {
       const int t = t_first + j * 4 * TILE;
       const uint32_t k_addr = w_addr + (j % NST) * 2 * V_BYTES, v_addr = k_addr + V_BYTES;
-      if (NST > 1 && j + 1 < n_tiles) cp_async_wait_but_one(); else cp_async_wait_all();
+      cp_async_wait_pending(min(n_tiles - 1 - j, NST - 1));          // tile j has landed; later ones may still fly
       __syncwarp();
       if (pos < t + TILE) {                                       // pos >= t: the range ends at pos
         // The newest row: not valid when the tile was requested early, and a copy of its line

@@ -277,10 +277,10 @@ def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Te
         c_void_p(buf.data_ptr()), c_int(_kind(q.dtype)), _stream()))
 
 
-def decode_attention_fused_supported(qkv, cos, sin, head_dim: int) -> bool:
+def decode_attention_fused_supported(qkv, cos, sin, head_dim: int, page_size: int = 16) -> bool:
     """Whether one kernel can rotate, store and attend for a decode step: bfloat16, head size 64
-    or 128, rows that start on 16-byte boundaries."""
-    if qkv.dtype != torch.bfloat16:
+    or 128, pages of a power of two, rows that start on 16-byte boundaries."""
+    if qkv.dtype != torch.bfloat16 or page_size & (page_size - 1):
         return False
     d, parts, _, stride = _split_args(qkv)
     src_stride = qkv.cols if isinstance(qkv, PartialSum) else qkv.stride(0)
@@ -380,7 +380,7 @@ def rope_store_attend(out, qkv, cos, sin, k_pages, v_pages, group, ctx, n_heads:
     step in bfloat16 with a head size of 64 or 128 runs as one kernel, everything else as the
     rotate-and-store kernel followed by the attention kernel that fits the batch."""
     if (FUSE_DECODE_ATTENTION and ctx.decode_only and ctx.n_tokens == ctx.n_entries
-            and decode_attention_fused_supported(qkv, cos, sin, head_dim)):
+            and decode_attention_fused_supported(qkv, cos, sin, head_dim, k_pages.shape[2])):
         max_keys = min(ctx.kv_bucket or 1 << 30, group.block_table.shape[1] * k_pages.shape[2])
         if window:
             max_keys = min(max_keys, window)

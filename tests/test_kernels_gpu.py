@@ -359,7 +359,8 @@ def test_sampling_kernel(ops):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("NH,NKV,HS,page,window,splits", [(4, 2, 16, 16, 0, 3), (3, 1, 32, 8, 0, 1), (6, 3, 48, 32, 19, 4),
                                                           (32, 4, 64, 16, 0, 7), (2, 1, 128, 64, 100, 32), (12, 1, 256, 16, 0, 5),
-                                                          (10, 10, 80, 16, 0, 2)])
+                                                          (10, 10, 80, 16, 0, 2),
+                                                          (8, 2, 64, 24, 0, 3)])     # pages of no power of two
 def test_decode_attention_matches_the_general_kernel_and_plain(ops, dtype, NH, NKV, HS, page, window, splits):
     """Requests of very different lengths in one decode batch, pages in shuffled order."""
     torch.manual_seed(11)
@@ -479,6 +480,9 @@ def test_decode_attention_fused_refuses_other_sizes(ops):
     assert not ops.decode_attention_fused_supported(torch.zeros(2, 64 * 3, device=DEV), cos, cos, 64)
     odd = torch.zeros(2, 64 * 3 + 4, device=DEV, dtype=torch.bfloat16)
     assert not ops.decode_attention_fused_supported(odd, cos, cos, 64)
+    ok = torch.zeros(2, 64 * 3, device=DEV, dtype=torch.bfloat16)
+    assert ops.decode_attention_fused_supported(ok, cos, cos, 64, page_size=32)
+    assert not ops.decode_attention_fused_supported(ok, cos, cos, 64, page_size=24)      # pages of no power of two
 
 
 def test_consumers_sum_split_k_partials_themselves(ops):
