@@ -328,6 +328,98 @@ def test_attention_finds_a_far_key_and_respects_the_window_edge(ops):
         assert close == sees, (window, sees)
 
 
+def _far_key_cache(n, far, HS, page, n_pages, seed):
+    """A cache of n keys with small random keys and one key at `far` that a query (50, 0, ...)
+    scores overwhelmingly; pages in reversed order."""
+    torch.manual_seed(seed)
+    k = (torch.randn(n, HS) * 0.1).to(torch.bfloat16)
+    v = torch.randn(n, HS).to(torch.bfloat16)
+    k[far] = 0
+    k[far, 0] = 50.0
+    kp = torch.zeros(n_pages, 1, page, HS, dtype=torch.bfloat16)
+    vp = torch.zeros_like(kp)
+    table = list(range(n_pages - 1, n_pages - 1 - (-(-n // page)), -1))
+    for p in range(n):
+        kp[table[p // page], 0, p % page] = k[p]
+        vp[table[p // page], 0, p % page] = v[p]
+    bt = torch.tensor([table + [0] * (n_pages - len(table))], dtype=torch.int32, device=DEV)
+    return k, v, kp.to(DEV), vp.to(DEV), bt
+
+
+@pytest.mark.parametrize("HS,page", [(64, 16), (128, 32)])
+@pytest.mark.parametrize("splits", [1, 4, 12])        # one range; ranges merged in a cluster; merged through the scratch
+def test_decode_kernels_find_a_far_key_and_respect_the_window_edge(ops, HS, page, splits):
+    """The bfloat16 decode kernels (queries given, and the fused kernel that rotates and stores):
+    a key hundreds of positions back, in another range and another page than the query, must come
+    through, and must vanish exactly when the window no longer reaches it; and when the newest key
+    (the one that the fused kernel stores itself) dominates, its value comes through."""
+    n, far, G = 700, 37, 2
+    k, v, kp, vp, bt = _far_key_cache(n, far, HS, page, 48, 21)
+    kv_lens = torch.tensor([n], dtype=torch.int32, device=DEV)
+    q = torch.zeros(1, G * HS, device=DEV, dtype=torch.bfloat16)
+    q[0, 0] = 50.0
+    q[0, HS] = 50.0
+    cos = torch.ones(n, HS // 2, device=DEV)
+    sin = torch.zeros(n, HS // 2, device=DEV)
+    for window, sees in ((0, True), (n - far, True), (n - far - 1, False)):
+        out = torch.zeros(1, G * HS, device=DEV, dtype=torch.bfloat16)
+        ops.paged_attention_decode(out, q, kp, vp, bt, kv_lens, 1, G, 1, HS, window, 1.0, splits=splits)
+        for h in range(G):
+            close = float((out[0, h * HS:(h + 1) * HS].float().cpu() - v[far].float()).abs().max()) < 2e-2
+            assert close == sees, ("queries given", window, h)
+        # the fused kernel: the row brings q, a small new key and a new value for position n - 1
+        row = torch.zeros(1, (G + 2) * HS, device=DEV, dtype=torch.bfloat16)
+        row[0, :G * HS] = q[0]
+        row[0, G * HS:(G + 1) * HS] = k[n - 1].to(DEV)
+        row[0, (G + 1) * HS:] = v[n - 1].to(DEV)
+        kp2, vp2 = kp.clone(), vp.clone()
+        slot_page, slot_off = int(bt[0, (n - 1) // page]), (n - 1) % page
+        kp2[slot_page, 0, slot_off] = 0
+        vp2[slot_page, 0, slot_off] = 0
+        out2 = torch.zeros_like(out)
+        ops.decode_attention_fused(out2, row, cos, sin, kp2, vp2, bt, kv_lens, 1, G, 1, HS, window, 1.0, splits=splits)
+        for h in range(G):
+            close = float((out2[0, h * HS:(h + 1) * HS].float().cpu() - v[far].float()).abs().max()) < 2e-2
+            assert close == sees, ("fused", window, h)
+        assert torch.equal(kp2, kp) and torch.equal(vp2, vp)           # the newest key and value landed in their place
+    # the newest key dominates: only the fused kernel's own copy of it can give its value
+    row = torch.zeros(1, (G + 2) * HS, device=DEV, dtype=torch.bfloat16)
+    row[0, 0] = 50.0
+    row[0, HS] = 50.0
+    row[0, G * HS] = 60.0
+    v_new = torch.randn(HS).to(torch.bfloat16)
+    row[0, (G + 1) * HS:] = v_new.to(DEV)
+    out3 = torch.zeros(1, G * HS, device=DEV, dtype=torch.bfloat16)
+    ops.decode_attention_fused(out3, row, cos, sin, kp.clone(), vp.clone(), bt, kv_lens, 1, G, 1, HS, 0, 1.0, splits=splits)
+    for h in range(G):
+        assert float((out3[0, h * HS:(h + 1) * HS].float().cpu() - v_new.float()).abs().max()) < 2e-2
+
+
+@pytest.mark.parametrize("HS,page", [(64, 16), (128, 64)])
+def test_tensor_core_attention_finds_a_far_key_and_respects_the_window_edge(ops, HS, page):
+    """The prompt kernel: 40 new tokens after 660 cached ones, every query scoring one far key
+    overwhelmingly.  Each row must return that key's value exactly as long as its own window
+    reaches the key."""
+    n, far, G, T = 700, 37, 2, 40
+    k, v, kp, vp, bt = _far_key_cache(n, far, HS, page, 48, 22)
+    q = torch.zeros(T, G * HS, device=DEV, dtype=torch.bfloat16)
+    q[:, 0] = 50.0
+    q[:, HS] = 50.0
+    cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    kv_lens = torch.tensor([n], dtype=torch.int32, device=DEV)
+    first = n - T                                                  # position of the first new token
+    for window in (0, n - far, first - far + 20, first - far):
+        out = torch.zeros(T, G * HS, device=DEV, dtype=torch.bfloat16)
+        ops.attention_tc(out, q, kp, vp, bt, cu, kv_lens, T, 1, G, 1, HS, window, 1.0)
+        torch.cuda.synchronize()
+        assert ops.attention_tc_take_error() == 0
+        for t in range(T):
+            sees = window == 0 or (first + t) - window + 1 <= far
+            for h in range(G):
+                close = float((out[t, h * HS:(h + 1) * HS].float().cpu() - v[far].float()).abs().max()) < 2e-2
+                assert close == sees, (window, t, h)
+
+
 def test_sampling_kernel(ops):
     import plain_llama
     torch.manual_seed(9)
