@@ -14,7 +14,6 @@
 // one row used and no split (kernel/attention/attention_NH_32_NKV_4_HS_64.h:374-386).
 // Softmax and all sums are float32; visible keys are max(0, pos-window+1) .. pos.
 #include "common.cuh"
-#include "attention_decode_mma.cuh"
 
 namespace {
 
@@ -357,63 +356,6 @@ LLMK_API long long llmk_paged_attention_decode_scratch(int n_entries, int n_head
   return COUNTER_WORDS + (long long)n_entries * n_heads * splits * (head_dim + 2);
 }
 
-namespace {
-
-template <bool FUSED>
-int launch_decode_mma(void* out, long long out_stride, const void* q, long long q_stride, const void* k_pages,
-                      const void* v_pages, const int* block_table, int table_width, const int* kv_lens,
-                      int n_entries, int n_heads, int n_kv, int head_dim, int page_size, float scale, int window,
-                      int splits, float* scratch, decode_mma::FusedQkv fused, cudaStream_t stream) {
-  dim3 grid(splits, n_kv, n_entries);
-  const float scale_log2e = scale * 1.4426950408889634f;
-  const int group_rows = n_heads / n_kv < decode_mma::ROWS ? n_heads / n_kv : decode_mma::ROWS;
-  // 2 to 8 ranges whose shares fit the first CTA's receive buffer, and a grid of at most two
-  // waves: merge inside a cluster, no scratch.  (Measured at 64 requests, 512 CTAs: 30 us with
-  // clusters against 23 us with the counter-based merge; at 8 requests 9.3 us against 13.5 us.)
-  constexpr int RECV_LIMIT = 64 * 1024;
-  const int recv_bytes = (splits - 1) * group_rows * head_dim * 4;
-  const bool cluster = splits >= 2 && splits <= 8 && (long long)splits * n_kv * n_entries <= 2 * 148 &&
-                       recv_bytes <= RECV_LIMIT;
-  // per warp a few stages (one in a cluster; three at head size 64, else two) of a tile of keys
-  // and a tile of values: NST in the kernel
-  const int stage_bytes = 4 * (cluster ? 1 : head_dim == 64 ? 3 : 2) * 2 * decode_mma::TILE * head_dim * 2;
-  using Kernel = decltype(&decode_mma::decode_attention_mma_kernel<64, false, FUSED>);
-  const Kernel kern = head_dim == 64
-      ? (cluster ? decode_mma::decode_attention_mma_kernel<64, true, FUSED> : decode_mma::decode_attention_mma_kernel<64, false, FUSED>)
-      : (cluster ? decode_mma::decode_attention_mma_kernel<128, true, FUSED> : decode_mma::decode_attention_mma_kernel<128, false, FUSED>);
-  static bool configured[2][2] = {{false, false}, {false, false}};
-  if (!configured[head_dim == 128][cluster]) {
-    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, stage_bytes + (cluster ? RECV_LIMIT : 0));
-    if (err != cudaSuccess) return llmk_fail((int)err, "attention_decode: cannot set the shared memory size: %s", cudaGetErrorString(err));
-    configured[head_dim == 128][cluster] = true;
-  }
-  if (cluster) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(decode_mma::THREADS);
-    cfg.dynamicSmemBytes = (size_t)(stage_bytes + recv_bytes);
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = splits;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = llmk_pdl_enabled() ? 2 : 1;
-    cudaLaunchKernelEx(&cfg, kern, (__nv_bfloat16*)out, out_stride, scratch, (const __nv_bfloat16*)q, q_stride,
-                       (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table, table_width, kv_lens, n_heads,
-                       n_kv, page_size, window, scale_log2e, splits, fused);
-  } else {
-    launch_kernel(kern, grid, dim3(decode_mma::THREADS), (size_t)stage_bytes, stream, (__nv_bfloat16*)out, out_stride, scratch,
-                  (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table,
-                  table_width, kv_lens, n_heads, n_kv, page_size, window, scale_log2e, splits, fused);
-  }
-  LLMK_LAUNCH_CHECK("attention_decode_mma");
-}
-
-}  // namespace
 
 // One query token per batch entry: q [entries, q_stride] (head h at column h*head_dim),
 // kv_lens[e] = keys of entry e including the new token.  `scratch` holds
@@ -433,13 +375,6 @@ LLMK_API int llmk_paged_attention_decode(void* out, long long out_stride, const 
   LLMK_REQUIRE((long long)n_entries * n_kv <= COUNTER_WORDS, "attention_decode: %d entries x %d kv heads exceed %d counters",
                n_entries, n_kv, COUNTER_WORDS);
   LLMK_REQUIRE(page_size > 0 && window >= 0, "attention_decode: bad page_size %d or window %d", page_size, window);
-  if (dtype == LLMK_BF16 && (head_dim == 64 || head_dim == 128) && q_stride % 2 == 0 && (uintptr_t)q % 4 == 0 &&
-      (page_size & (page_size - 1)) == 0) {
-    // bfloat16 with a head size of 64 or 128: the query heads of a group as rows of warp-level MMAs
-    return launch_decode_mma<false>(out, out_stride, q, q_stride, k_pages, v_pages, block_table, table_width, kv_lens,
-                                    n_entries, n_heads, n_kv, head_dim, page_size, scale, window, splits, scratch,
-                                    decode_mma::FusedQkv{}, stream);
-  }
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     dim3 grid(splits, n_kv, n_entries);
@@ -451,48 +386,6 @@ LLMK_API int llmk_paged_attention_decode(void* out, long long out_stride, const 
                   page_size, window, scale, splits);
     LLMK_LAUNCH_CHECK("attention_decode");
   });
-}
-
-// Whether the fused rotate-store-attend kernel takes these sizes and pointers.
-LLMK_API int llmk_decode_attention_fused_supported(const void* qkv, const float* partials, long long split_stride,
-                                                   long long src_stride, const float* cos_table,
-                                                   const float* sin_table, int head_dim, int dtype) {
-  if (dtype != LLMK_BF16 || (head_dim != 64 && head_dim != 128)) return 0;
-  if ((qkv != nullptr) == (partials != nullptr)) return 0;
-  decode_mma::FusedQkv f{{(const __nv_bfloat16*)qkv, partials, 1, split_stride}, src_stride, cos_table, sin_table, 1};
-  if (!f.src.vector_ok() || src_stride % 8) return 0;
-  if ((uintptr_t)cos_table % 16 || (uintptr_t)sin_table % 16 || ((cos_table != nullptr) != (sin_table != nullptr))) return 0;
-  return 1;
-}
-
-// A decode step's rotation, cache store and attention in one kernel (bfloat16, head size 64 or
-// 128).  Row e of the source holds entry e's q heads, k heads and v heads (the k and v heads
-// only when write_kv != 0): a tensor qkv [entries, src_stride] or the float32 partial results
-// [qkv_splits][entries][src_stride] of a split-K product.  kv_lens[e] counts the new token, whose
-// position is kv_lens[e] - 1; its rotated key and its value are stored at that position's place
-// in the entry's block table.  Scratch and splits as for llmk_paged_attention_decode.
-LLMK_API int llmk_decode_attention_fused(void* out, long long out_stride, const void* qkv, const float* partials,
-                                         int qkv_splits, long long split_stride, long long src_stride,
-                                         const float* cos_table, const float* sin_table, void* k_pages,
-                                         void* v_pages, const int* block_table, int table_width, const int* kv_lens,
-                                         int n_entries, int n_heads, int n_kv, int head_dim, int page_size,
-                                         int window, float scale, int splits, int write_kv, float* scratch,
-                                         cudaStream_t stream) {
-  if (n_entries == 0) return 0;
-  LLMK_REQUIRE(llmk_decode_attention_fused_supported(qkv, partials, split_stride, src_stride, cos_table, sin_table, head_dim, LLMK_BF16),
-               "decode_attention_fused: needs bfloat16, a head size of 64 or 128 (got %d) and 16-byte aligned rows", head_dim);
-  LLMK_REQUIRE(n_kv > 0 && n_heads % n_kv == 0, "decode_attention_fused: %d query heads do not divide into %d kv heads", n_heads, n_kv);
-  LLMK_REQUIRE(splits >= 1 && splits <= 64, "decode_attention_fused: splits %d must be 1 to 64", splits);
-  LLMK_REQUIRE(n_kv <= 65535 && n_entries <= 65535, "decode_attention_fused: grid too large");
-  LLMK_REQUIRE((long long)n_entries * n_kv <= COUNTER_WORDS, "decode_attention_fused: %d entries x %d kv heads exceed %d counters",
-               n_entries, n_kv, COUNTER_WORDS);
-  LLMK_REQUIRE(page_size > 0 && (page_size & (page_size - 1)) == 0 && window >= 0,
-               "decode_attention_fused: the page size %d must be a power of two, the window %d not negative", page_size, window);
-  LLMK_REQUIRE(src_stride >= (long long)(n_heads + (write_kv ? 2 * n_kv : 0)) * head_dim,
-               "decode_attention_fused: a row of %lld values does not hold the heads", src_stride);
-  decode_mma::FusedQkv f{{(const __nv_bfloat16*)qkv, partials, qkv_splits, split_stride}, src_stride, cos_table, sin_table, write_kv};
-  return launch_decode_mma<true>(out, out_stride, nullptr, 0, k_pages, v_pages, block_table, table_width, kv_lens,
-                                 n_entries, n_heads, n_kv, head_dim, page_size, scale, window, splits, scratch, f, stream);
 }
 
 // ---- the variant that allocates nothing (declared in no_alloc.h) ----------------

@@ -1,9 +1,12 @@
-"""Builds the kernel library for sm_100a with nvcc and loads it with ctypes.
+"""Builds the kernel libraries for sm_100a with nvcc and loads them with ctypes.
 
 The kernels have a C interface and use no torch headers, so a file compiles in
-seconds.  The library is built in-tree (llm_b200/csrc/_build) at the first call,
-or in a temporary folder when the tree is read-only, and rebuilt when a source or
-a flag changes.  While nvcc runs, a line is printed now and then.
+seconds.  There are two libraries: the plain one (everything a float32 model needs,
+and what a bfloat16 model runs on the CUDA cores) and the tensor-core one (bfloat16
+products and attention), which is only built and loaded when a bfloat16 model asks for
+it.  A library is built in-tree (llm_b200/csrc/_build) at its first use, or in a
+temporary folder when the tree is read-only, and rebuilt when a source or a flag
+changes.  While nvcc runs, a line is printed now and then.
 """
 from __future__ import annotations
 
@@ -20,6 +23,12 @@ from concurrent.futures import ThreadPoolExecutor
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libllm_b200_kernels.so"
+GROUPS = {
+    # group -> (library file, sources); runtime.cu (error text, switches) is linked into both
+    "plain": (LIB_NAME, ["runtime.cu", "rows.cu", "gemm_simt.cu", "rope_cache.cu", "attention_generic.cu",
+                         "attention_decode.cu", "sampling.cu"]),
+    "tensor": ("libllm_b200_tensor.so", ["runtime.cu", "gemm_tc.cu", "attention_tc.cu", "attention_decode_mma.cu"]),
+}
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -34,8 +43,16 @@ class KernelBuildError(RuntimeError):
     pass
 
 
-def sources():
-    return sorted(f for f in os.listdir(_HERE) if f.endswith(".cu"))
+def sources(group: str = None):
+    """The CUDA files of a group, or of all groups."""
+    if group is not None:
+        return list(GROUPS[group][1])
+    every = sorted(f for f in os.listdir(_HERE) if f.endswith(".cu"))
+    listed = {f for _, files in GROUPS.values() for f in files}
+    stray = [f for f in every if f not in listed]
+    if stray:
+        raise KernelBuildError(f"CUDA files that belong to no library: {stray}")
+    return every
 
 
 def _headers():
@@ -49,17 +66,30 @@ def _find_nvcc() -> str:
     raise KernelBuildError("nvcc not found (looked at $LLM_B200_NVCC, PATH and /usr/local/cuda/bin)")
 
 
-def _digest() -> str:
+def _digest(group: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    for name in sources() + _headers():
+    for name in sources(group) + _headers():
         h.update(name.encode())
         with open(os.path.join(_HERE, name), "rb") as f:
             h.update(f.read())
     return h.hexdigest()
 
 
+_BUILD_DIR = None
+_DIR_LOCK = threading.Lock()
+
+
 def _build_dir() -> str:
+    """Where objects and libraries go; chosen once per process."""
+    global _BUILD_DIR
+    with _DIR_LOCK:
+        if _BUILD_DIR is None:
+            _BUILD_DIR = _choose_build_dir()
+        return _BUILD_DIR
+
+
+def _choose_build_dir() -> str:
     d = os.environ.get("LLM_B200_BUILD_DIR") or os.path.join(_HERE, "_build")
     try:
         os.makedirs(d, exist_ok=True)
@@ -78,24 +108,30 @@ def _say(msg: str) -> None:
     print(f"[llm_b200] {msg}", file=sys.stderr, flush=True)
 
 
-def library_path() -> str:
-    return os.path.join(_build_dir(), LIB_NAME)
+def library_path(group: str = "plain") -> str:
+    return os.path.join(_build_dir(), GROUPS[group][0])
 
 
-def build(force: bool = False, verbose: bool = True) -> str:
-    """Compile what is stale and return the path of the shared library."""
+def build(force: bool = False, verbose: bool = True, group: str = None) -> str:
+    """Compile what is stale of one library (or, without a group, of both) and return the path of
+    the shared library (of the plain one when both are built)."""
+    if group is None:
+        sources()                                   # every file belongs to a library
+        with ThreadPoolExecutor(max_workers=len(GROUPS)) as pool:      # the libraries side by side
+            paths = list(pool.map(lambda g: build(force, verbose, g), GROUPS))
+        return paths[0]
     bdir = _build_dir()
-    lib = os.path.join(bdir, LIB_NAME)
-    stamp = os.path.join(bdir, "sources.sha256")
-    digest = _digest()
+    lib = os.path.join(bdir, GROUPS[group][0])
+    stamp = os.path.join(bdir, f"{group}.sha256")
+    digest = _digest(group)
     if not force and os.path.isfile(lib) and os.path.isfile(stamp):
         with open(stamp) as f:
             if f.read().strip() == digest:
                 return lib
     nvcc = _find_nvcc()
-    srcs = sources()
+    srcs = sources(group)
     if verbose:
-        _say(f"compiling {len(srcs)} CUDA files for sm_100a into {bdir} (first call only)")
+        _say(f"compiling the {group} kernel library: {len(srcs)} CUDA files for sm_100a into {bdir} (first use only)")
     t0 = time.time()
     done = []
     stop = threading.Event()
@@ -105,7 +141,7 @@ def build(force: bool = False, verbose: bool = True) -> str:
             _say(f"  ... still compiling: {len(done)}/{len(srcs)} files done after {time.time() - t0:.0f} s")
 
     def compile_one(name: str) -> str:
-        obj = os.path.join(bdir, name[:-3] + ".o")
+        obj = os.path.join(bdir, f"{group}_{name[:-3]}.o")      # a file that both libraries carry is compiled for each
         cmd = [nvcc, *NVCC_FLAGS, "-I", _HERE, "-c", os.path.join(_HERE, name), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
@@ -132,27 +168,35 @@ def build(force: bool = False, verbose: bool = True) -> str:
     finally:
         stop.set()
     if verbose:
-        _say(f"kernel library ready after {time.time() - t0:.0f} s")
+        _say(f"{group} kernel library ready after {time.time() - t0:.0f} s")
     return lib
 
 
-_LIB = None
+_LIBS = {}
 _LOCK = threading.Lock()
 
 
-def load() -> ctypes.CDLL:
-    """The kernel library, built if needed.  Raises if it cannot be had: there is no
+def load(group: str = "plain") -> ctypes.CDLL:
+    """A kernel library, built if needed.  Raises if it cannot be had: there is no
     other implementation to fall back to."""
-    global _LIB
+    lib = _LIBS.get(group)
+    if lib is not None:
+        return lib
     with _LOCK:
-        if _LIB is None:
-            path = build()
+        if group not in _LIBS:
+            path = build(group=group)
             try:
-                _LIB = ctypes.CDLL(path)
+                lib = ctypes.CDLL(path)
             except OSError as e:
                 raise KernelBuildError(f"cannot load {path}: {e}") from e
-            _LIB.llmk_last_error.restype = ctypes.c_char_p
-        return _LIB
+            lib.llmk_last_error.restype = ctypes.c_char_p
+            _LIBS[group] = lib
+        return _LIBS[group]
+
+
+def load_tensor() -> ctypes.CDLL:
+    """The tensor-core library (bfloat16 products and attention)."""
+    return load("tensor")
 
 
 if __name__ == "__main__":

@@ -11,7 +11,7 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
-from .build import load
+from .build import load, load_tensor
 
 _F32, _BF16 = 0, 1
 
@@ -86,12 +86,17 @@ def count_launches(n: int) -> None:
     _LAUNCHES += n
 
 
-def _check(code: int) -> None:
+def _check(code: int, tensor: bool = False) -> None:
+    """Count a launch; raise with the text of the library that reported an error."""
     global _LAUNCHES
     _LAUNCHES += 1
     if code != 0:
-        msg = load().llmk_last_error().decode("utf-8", "replace")
+        msg = (load_tensor() if tensor else load()).llmk_last_error().decode("utf-8", "replace")
         raise KernelError(f"kernel call failed ({code}): {msg}")
+
+
+def _check_t(code: int) -> None:
+    _check(code, tensor=True)
 
 
 def _rows_contig(t: torch.Tensor, name: str) -> None:
@@ -266,15 +271,24 @@ def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Te
     page = k_pages.shape[2]
     if splits is None:
         splits = decode_splits(n_entries, n_kv, block_table.shape[1] * page)
+    buf = _attn_partials(q.device, _decode_scratch_floats(n_entries, n_heads, head_dim, splits))
+    args = (_ptr(out), c_longlong(out.stride(0)), _ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
+            _ptr(block_table), c_int(block_table.shape[1]), _ptr(kv_lens), c_int(n_entries), c_int(n_heads),
+            c_int(n_kv), c_int(head_dim), c_int(page), c_int(window or 0), c_float(scale), c_int(splits),
+            c_void_p(buf.data_ptr()), c_int(_kind(q.dtype)), _stream())
+    # bfloat16 with a head size of 64 or 128 and pages of a power of two: the query heads of a
+    # group as rows of warp-level MMAs (tensor-core library); everything else on the CUDA cores
+    if (q.dtype == torch.bfloat16 and head_dim in (64, 128) and page & (page - 1) == 0
+            and q.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0):
+        _check_t(load_tensor().llmk_paged_attention_decode_mma(*args))
+    else:
+        _check(load().llmk_paged_attention_decode(*args))
+
+
+def _decode_scratch_floats(n_entries: int, n_heads: int, head_dim: int, splits: int) -> int:
     lib = load()
     lib.llmk_paged_attention_decode_scratch.restype = c_longlong
-    need = lib.llmk_paged_attention_decode_scratch(c_int(n_entries), c_int(n_heads), c_int(head_dim), c_int(splits))
-    buf = _attn_partials(q.device, int(need))
-    _check(lib.llmk_paged_attention_decode(
-        _ptr(out), c_longlong(out.stride(0)), _ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
-        _ptr(block_table), c_int(block_table.shape[1]), _ptr(kv_lens), c_int(n_entries), c_int(n_heads),
-        c_int(n_kv), c_int(head_dim), c_int(page), c_int(window or 0), c_float(scale), c_int(splits),
-        c_void_p(buf.data_ptr()), c_int(_kind(q.dtype)), _stream()))
+    return int(lib.llmk_paged_attention_decode_scratch(c_int(n_entries), c_int(n_heads), c_int(head_dim), c_int(splits)))
 
 
 def decode_attention_fused_supported(qkv, cos, sin, head_dim: int, page_size: int = 16) -> bool:
@@ -284,7 +298,7 @@ def decode_attention_fused_supported(qkv, cos, sin, head_dim: int, page_size: in
         return False
     d, parts, _, stride = _split_args(qkv)
     src_stride = qkv.cols if isinstance(qkv, PartialSum) else qkv.stride(0)
-    return bool(load().llmk_decode_attention_fused_supported(d, parts, stride, c_longlong(src_stride), _ptr(cos),
+    return bool(load_tensor().llmk_decode_attention_fused_supported(d, parts, stride, c_longlong(src_stride), _ptr(cos),
                                                              _ptr(sin), c_int(head_dim), c_int(_BF16)))
 
 
@@ -302,15 +316,13 @@ def decode_attention_fused(out: torch.Tensor, qkv, cos, sin, k_pages: torch.Tens
     page = k_pages.shape[2]
     if splits is None:
         splits = decode_splits(n_entries, n_kv, block_table.shape[1] * page)
-    lib = load()
-    lib.llmk_paged_attention_decode_scratch.restype = c_longlong
-    need = lib.llmk_paged_attention_decode_scratch(c_int(n_entries), c_int(n_heads), c_int(head_dim), c_int(splits))
-    buf = _attn_partials(out.device, int(need))
+    lib = load_tensor()
+    buf = _attn_partials(out.device, _decode_scratch_floats(n_entries, n_heads, head_dim, splits))
     d, parts, qkv_splits, stride = _split_args(qkv)
     src_stride = qkv.cols if isinstance(qkv, PartialSum) else qkv.stride(0)
     if isinstance(qkv, PartialSum):
         assert qkv.rows == n_entries
-    _check(lib.llmk_decode_attention_fused(
+    _check_t(lib.llmk_decode_attention_fused(
         _ptr(out), c_longlong(out.stride(0)), d, parts, qkv_splits, stride, c_longlong(src_stride), _ptr(cos),
         _ptr(sin), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), c_int(block_table.shape[1]), _ptr(kv_lens),
         c_int(n_entries), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(page), c_int(window or 0),
@@ -322,7 +334,7 @@ def attention_tc_supported(dtype, n_heads: int, n_kv: int, head_dim: int, page_s
     of 16 to 128 tokens, at most 128 query heads per kv head)."""
     if dtype != torch.bfloat16:
         return False
-    return bool(load().llmk_attention_tc_supported(c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(page_size)))
+    return bool(load_tensor().llmk_attention_tc_supported(c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(page_size)))
 
 
 def attention_tc(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -335,7 +347,7 @@ def attention_tc(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pa
     assert block_table.dim() == 2 and block_table.is_contiguous() and block_table.dtype == torch.int32
     assert cu_tokens.dtype == torch.int32 and kv_lens.dtype == torch.int32
     assert k_pages.is_contiguous() and v_pages.is_contiguous()
-    _check(load().llmk_attention_tc(
+    _check_t(load_tensor().llmk_attention_tc(
         _ptr(out), c_longlong(out.stride(0)), _ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
         c_int(k_pages.shape[0]), _ptr(block_table), c_int(block_table.shape[1]), _ptr(cu_tokens), _ptr(kv_lens),
         c_int(n_tokens), c_int(n_entries), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(k_pages.shape[2]),
@@ -344,7 +356,7 @@ def attention_tc(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pa
 
 def attention_tc_take_error() -> int:
     """The code the tensor-core attention left when one of its bounded waits gave up (0 = none)."""
-    return int(load().llmk_attention_tc_take_error())
+    return int(load_tensor().llmk_attention_tc_take_error())
 
 
 def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: int, head_dim: int,
@@ -515,7 +527,7 @@ def gemm_fast_available(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, row
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         return False
     n, k = w.shape
-    return bool(load().llmk_gemm_tc_supported(_ptr(a), _ptr(w), c_int(rows), c_int(n), c_int(k),
+    return bool(load_tensor().llmk_gemm_tc_supported(_ptr(a), _ptr(w), c_int(rows), c_int(n), c_int(k),
                                               c_longlong(a.stride(0)), c_longlong(w.stride(0))))
 
 
@@ -529,21 +541,21 @@ def gemm_fast(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, pl
     plan = plan or plan_gemm(rows, n, k, fused_reduce=allow_partial)
     swap, tile, splits, per = plan[:4]
     cluster = int(plan[4]) if len(plan) > 4 else 0
-    lib = load()
+    lib = load_tensor()
     if splits == 1 or cluster:
-        _check(lib.llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
+        _check_t(lib.llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
                                 c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
                                 c_int(_kind(out.dtype)), c_int(int(swap)), c_int(tile), c_int(splits), c_int(per),
                                 c_int(int(cluster)), c_int(0), _stream()))
         return out
     part = _partials(a.device)
-    _check(lib.llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(part), c_int(rows), c_int(n), c_int(k),
+    _check_t(lib.llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(part), c_int(rows), c_int(n), c_int(k),
                             c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(n), c_int(_F32),
                             c_int(int(swap)), c_int(tile), c_int(splits), c_int(per), c_int(0), c_int(0), _stream()))
     if allow_partial:
         return PartialSum(part, splits, rows, n, out.dtype)
     assert out.is_contiguous()
-    _check(lib.llmk_reduce_partials(_ptr(out), _ptr(part), c_longlong(rows * n), c_int(splits),
+    _check_t(lib.llmk_reduce_partials(_ptr(out), _ptr(part), c_longlong(rows * n), c_int(splits),
                                     c_int(_kind(out.dtype)), _stream()))
     return out
 
@@ -566,17 +578,19 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int) 
     assert a.shape[1] == k and out.shape[1] == n // 2 and n % 2 == 0
     if not gemm_swiglu_available(a, w, out, rows):
         raise KernelError(f"gemm_swiglu does not take {rows} rows of {a.dtype} -> {out.dtype}")
-    _check(load().llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
+    _check_t(load_tensor().llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
                                c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
                                c_int(_BF16), c_int(0), c_int(256), c_int(1), c_int(_ceil_div(k, 64)),
                                c_int(2), c_int(1), _stream()))
 
 
 def set_pdl(on: bool) -> None:
-    """Programmatic dependent launch between the kernels of a step (on by default)."""
+    """Programmatic dependent launch between the kernels of a step (on by default); set in both
+    kernel libraries."""
     load().llmk_set_pdl(c_int(int(on)))
+    load_tensor().llmk_set_pdl(c_int(int(on)))
 
 
 def gemm_tc_take_error() -> int:
     """The code a tensor-core kernel left when one of its bounded waits gave up (0 = none)."""
-    return int(load().llmk_gemm_tc_take_error())
+    return int(load_tensor().llmk_gemm_tc_take_error())

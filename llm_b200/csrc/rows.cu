@@ -3,29 +3,7 @@
 // sums, the reciprocal root and the scaling are float32 as well.  An input that comes
 // from a split-K product may be given as its float32 partial results, which are summed
 // here in a fixed order instead of by a kernel of their own.
-#include <stdarg.h>
-#include <stdio.h>
-
 #include "common.cuh"
-
-// ---- error channel and switches ----------------------------------------------
-static thread_local char g_last_error[512] = "";
-static bool g_pdl = true;
-
-int llmk_fail(int code, const char* fmt, ...) {
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
-  va_end(ap);
-  return code;
-}
-
-bool llmk_pdl_enabled() { return g_pdl; }
-
-LLMK_API const char* llmk_last_error() { return g_last_error; }
-LLMK_API int llmk_abi_version() { return 2; }
-// Programmatic dependent launch between the kernels of a step (on by default).
-LLMK_API void llmk_set_pdl(int on) { g_pdl = on != 0; }
 
 // ---- embedding --------------------------------------------------------------
 // resid[t, :] = table[ids[t], :]   (the reference copies rows without scaling,

@@ -21,7 +21,7 @@ from ..cache.storage import CacheStorage, StateStorage, bytes_per_page
 from ..config.engine_options import EngineOptions
 from ..config.model_config import load_config, parse_config
 from ..csrc import ops
-from ..csrc.build import load as load_kernels
+from ..csrc.build import build as build_kernels, load as load_kernels
 from ..parts.base import ResidualStream
 from ..weights.loader import load_tensors, random_tensors_on_device
 from .context import GroupView, LayerView, StepContext, Workspace
@@ -80,6 +80,11 @@ class Engine:
         options.validate()
         if not torch.cuda.is_available():
             raise RuntimeError("llm_b200 needs a CUDA device: there is no CPU path")
+        # the plain kernel library; a bfloat16 model also needs the tensor-core one (when both
+        # have to be compiled first, they are compiled side by side)
+        if options.dtype == "bfloat16":
+            build_kernels()
+            load_kernels("tensor")
         load_kernels()
         self.device = torch.device(options.device)
         torch.cuda.set_device(self.device)
