@@ -129,6 +129,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   float acc[CLUSTER ? BNQ : 1];          // the accumulator row of an epilogue thread, kept across the cluster barriers
   static_assert(!CLUSTER || (SWAP && BNQ <= 64), "cluster reduction is for the swapped mode with up to 64 rows");
 
+  // The weights do not depend on earlier kernels: their tiles of the first pass over the ring
+  // are requested before waiting for the previous kernel (the activations after), and as early
+  // as can be: by the thread that has just initialised the barriers, before the CTA's first
+  // barrier and while warp 1 still allocates tensor memory.  The earlier they are asked for, the
+  // more of their way from memory is hidden behind the kernel before this one.
+  uint8_t* smem_w = SWAP ? smem_p : smem_q;
+  uint8_t* smem_a = SWAP ? smem_q : smem_p;
+  const CUtensorMap* map_w = SWAP ? &map_p : &map_q;
+  const CUtensorMap* map_a = SWAP ? &map_q : &map_p;
+  constexpr int W_STAGE = SWAP ? P_STAGE_BYTES : Q_STAGE_BYTES;
+  constexpr int A_STAGE = SWAP ? Q_STAGE_BYTES : P_STAGE_BYTES;
+  const int w0 = SWAP ? p0 : q0, a0 = SWAP ? q0 : p0;
+  const int pre = min(nkb, STAGES);
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -136,8 +150,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     }
     mbar_init(accum_bar, 1);
     fence_mbar_init();
-    prefetch_tensormap(&map_p);
-    prefetch_tensormap(&map_q);
+    for (int i = 0; i < pre; ++i) {
+      mbar_arrive_expect_tx(&full_bar[i], stage_tx);
+      tma_load_2d(smem_w + i * W_STAGE, map_w, (kb_begin + i) * BK, w0, &full_bar[i]);
+    }
+    prefetch_tensormap(map_a);
   }
   if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
   fence_before_sync();
@@ -145,24 +162,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  pdl_launch_dependents();
   if (warp == 0) {
     if (lane == 0) {
       // ---- producer: TMA loads into the ring ----
-      // The weights do not depend on earlier kernels: their tiles of the first pass over the
-      // ring are requested before waiting for the previous kernel, the activations after.
-      uint8_t* smem_w = SWAP ? smem_p : smem_q;
-      uint8_t* smem_a = SWAP ? smem_q : smem_p;
-      const CUtensorMap* map_w = SWAP ? &map_p : &map_q;
-      const CUtensorMap* map_a = SWAP ? &map_q : &map_p;
-      constexpr int W_STAGE = SWAP ? P_STAGE_BYTES : Q_STAGE_BYTES;
-      constexpr int A_STAGE = SWAP ? Q_STAGE_BYTES : P_STAGE_BYTES;
-      const int w0 = SWAP ? p0 : q0, a0 = SWAP ? q0 : p0;
-      const int pre = min(nkb, STAGES);
-      for (int i = 0; i < pre; ++i) {
-        mbar_arrive_expect_tx(&full_bar[i], stage_tx);
-        tma_load_2d(smem_w + i * W_STAGE, map_w, (kb_begin + i) * BK, w0, &full_bar[i]);
-      }
       pdl_wait();
       for (int i = 0; i < pre; ++i)
         tma_load_2d(smem_a + i * A_STAGE, map_a, (kb_begin + i) * BK, a0, &full_bar[i]);
