@@ -28,7 +28,10 @@ GROUPS = {
     "plain": (LIB_NAME, ["runtime.cu", "rows.cu", "gemm_simt.cu", "rope_cache.cu", "attention_generic.cu",
                          "attention_decode.cu", "sampling.cu"]),
     "tensor": ("libllm_b200_tensor.so", ["runtime.cu", "gemm_tc.cu", "attention_tc.cu", "attention_decode_mma.cu"]),
+    # host side of the runtime (page pool, step metadata): plain C++, built with g++, needs no CUDA
+    "host": ("libllm_b200_host.so", ["host/page_pool.cpp"]),
 }
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -48,6 +51,7 @@ def sources(group: str = None):
     if group is not None:
         return list(GROUPS[group][1])
     every = sorted(f for f in os.listdir(_HERE) if f.endswith(".cu"))
+    every += sorted("host/" + f for f in os.listdir(os.path.join(_HERE, "host")) if f.endswith(".cpp"))
     listed = {f for _, files in GROUPS.values() for f in files}
     stray = [f for f in every if f not in listed]
     if stray:
@@ -57,6 +61,13 @@ def sources(group: str = None):
 
 def _headers():
     return sorted(f for f in os.listdir(_HERE) if f.endswith((".cuh", ".h")))
+
+
+def _find_cxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++")):
+        if cand and (os.path.isfile(cand) or shutil.which(cand)):
+            return shutil.which(cand) or cand
+    raise KernelBuildError("no C++ compiler found (looked at $CXX, g++ and c++ on PATH)")
 
 
 def _find_nvcc() -> str:
@@ -69,7 +80,7 @@ def _find_nvcc() -> str:
 def _digest(group: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    for name in sources(group) + _headers():
+    for name in sources(group) + (_headers() if group != "host" else []):
         h.update(name.encode())
         with open(os.path.join(_HERE, name), "rb") as f:
             h.update(f.read())
@@ -120,6 +131,8 @@ def build(force: bool = False, verbose: bool = True, group: str = None) -> str:
         with ThreadPoolExecutor(max_workers=len(GROUPS)) as pool:      # the libraries side by side
             paths = list(pool.map(lambda g: build(force, verbose, g), GROUPS))
         return paths[0]
+    if group == "host":
+        return _build_host(force, verbose)
     bdir = _build_dir()
     lib = os.path.join(bdir, GROUPS[group][0])
     stamp = os.path.join(bdir, f"{group}.sha256")
@@ -172,6 +185,35 @@ def build(force: bool = False, verbose: bool = True, group: str = None) -> str:
     return lib
 
 
+def _build_host(force: bool, verbose: bool) -> str:
+    """The host library: C++ files compiled and linked by g++ in one go (a second or two)."""
+    bdir = _build_dir()
+    name, srcs = GROUPS["host"]
+    lib = os.path.join(bdir, name)
+    stamp = os.path.join(bdir, "host.sha256")
+    h = hashlib.sha256(" ".join(CXX_FLAGS).encode())
+    for f in srcs:
+        with open(os.path.join(_HERE, f), "rb") as fh:
+            h.update(f.encode() + fh.read())
+    digest = h.hexdigest()
+    if not force and os.path.isfile(lib) and os.path.isfile(stamp):
+        with open(stamp) as f:
+            if f.read().strip() == digest:
+                return lib
+    t0 = time.time()
+    tmp = lib + f".tmp{os.getpid()}"
+    cmd = [_find_cxx(), *CXX_FLAGS, "-shared", "-o", tmp, *[os.path.join(_HERE, f) for f in srcs]]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise KernelBuildError(f"{cmd[0]} failed on the host library:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp, lib)
+    with open(stamp, "w") as f:
+        f.write(digest)
+    if verbose:
+        _say(f"host library ready after {time.time() - t0:.0f} s")
+    return lib
+
+
 _LIBS = {}
 _LOCK = threading.Lock()
 
@@ -189,9 +231,15 @@ def load(group: str = "plain") -> ctypes.CDLL:
                 lib = ctypes.CDLL(path)
             except OSError as e:
                 raise KernelBuildError(f"cannot load {path}: {e}") from e
-            lib.llmk_last_error.restype = ctypes.c_char_p
+            if group != "host":
+                lib.llmk_last_error.restype = ctypes.c_char_p
             _LIBS[group] = lib
         return _LIBS[group]
+
+
+def load_host() -> ctypes.CDLL:
+    """The host library (page pool, step metadata); needs a C++ compiler, no GPU."""
+    return load("host")
 
 
 def load_tensor() -> ctypes.CDLL:

@@ -1,0 +1,300 @@
+// Host side of the cache, native: pages, block tables and state slots of the live requests,
+// and the routine that writes a step's metadata into the pinned buffer that is copied to the
+// device.  Plain C++17 with a C interface (built with g++, loaded with ctypes); no CUDA here.
+//
+// Like the reference's KV_Pool (kv/KV_pool.h:13-102) the pool keeps, per request slot, the
+// physical pages that hold its tokens, hands pages out from a LIFO free list when a request
+// grows (KV_Pool::append, :40-52) and takes them back when it ends (:55-60).  Unlike it, the
+// pool is split into groups: layers whose needs differ (every past key, or a window of them)
+// have pages and tables of their own, and a window group gives a page back as soon as every
+// later token's window has passed it.  The page size is a parameter, not the constant 16 of
+// kv/KV_Layout.h:2, and contracts are checked, not asserted.  Requests are known here by their
+// slot (the row id that the reference uses to index its tables, kv/KV_pool.h:31-37), which is
+// also the index of a request's fixed-size state.
+#include <algorithm>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <vector>
+
+#define LLMH_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+enum : int { KIND_FULL = 0, KIND_WINDOW = 1 };
+enum : int { ERR_CONTRACT = -1, ERR_OUT_OF_PAGES = -2 };
+
+struct Group {
+  int kind, page_size, num_pages, window, width;     // width: table entries per request
+  std::vector<int> free;                             // LIFO: back() is handed out next
+  std::vector<int> table;                            // [max_requests][width], -1 = given back / not held
+  std::vector<int> n_pages, first_live;              // per slot: logical pages in the table, first one still held
+
+  int pages_for(int length) const { return (length + page_size - 1) / page_size; }
+  // logical pages below this index can no longer be seen by a token at next_pos or later
+  int dead_before(int next_pos) const {
+    if (kind != KIND_WINDOW) return 0;
+    const int lowest_key = next_pos - window + 1;
+    return lowest_key <= 0 ? 0 : lowest_key / page_size;
+  }
+};
+
+struct Pool {
+  std::vector<Group> groups;
+  int max_requests = 0, max_seq_len = 0;
+  std::vector<int> free_slots;                       // LIFO
+  std::vector<int> len;                              // per slot; -1 = not live
+  std::vector<int> fresh;                            // admitted since the last take: state to be zeroed
+  char error[512] = "";
+
+  int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(error, sizeof(error), fmt, ap);
+    va_end(ap);
+    return code;
+  }
+  bool live(int slot) const { return slot >= 0 && slot < max_requests && len[slot] >= 0; }
+
+  // per group, the pages that growing by n_new takes from the free list, net of the window
+  // pages that the same call gives back first
+  void pages_needed(int slot, int cur, int n_new, int* out) const {
+    for (size_t g = 0; g < groups.size(); ++g) {
+      const Group& grp = groups[g];
+      const int have_hi = grp.pages_for(cur), need_hi = grp.pages_for(cur + n_new);
+      int give_back = 0;
+      if (grp.kind == KIND_WINDOW) {
+        const int first = slot >= 0 ? grp.first_live[slot] : 0;
+        const int dead = std::min(grp.dead_before(cur), have_hi);
+        give_back = std::max(0, dead - first);
+      }
+      out[g] = need_hi - have_hi - give_back;
+    }
+  }
+};
+
+}  // namespace
+
+LLMH_API void* llmh_pool_create(int n_groups, const int* kinds, const int* page_sizes, const int* num_pages,
+                                const int* windows, int max_requests, int max_seq_len) {
+  if (n_groups < 0 || max_requests <= 0 || max_seq_len <= 0) return nullptr;
+  Pool* p = new Pool();
+  p->max_requests = max_requests;
+  p->max_seq_len = max_seq_len;
+  for (int g = 0; g < n_groups; ++g) {
+    if (page_sizes[g] <= 0 || num_pages[g] < 0 || (kinds[g] != KIND_FULL && kinds[g] != KIND_WINDOW) ||
+        (kinds[g] == KIND_WINDOW && windows[g] <= 0)) {
+      delete p;
+      return nullptr;
+    }
+    Group grp;
+    grp.kind = kinds[g];
+    grp.page_size = page_sizes[g];
+    grp.num_pages = num_pages[g];
+    grp.window = windows[g];
+    grp.width = grp.pages_for(max_seq_len);
+    grp.free.resize(num_pages[g]);
+    for (int i = 0; i < num_pages[g]; ++i) grp.free[i] = num_pages[g] - 1 - i;      // page 0 is handed out first
+    grp.table.assign((size_t)max_requests * grp.width, -1);
+    grp.n_pages.assign(max_requests, 0);
+    grp.first_live.assign(max_requests, 0);
+    p->groups.push_back(std::move(grp));
+  }
+  p->free_slots.resize(max_requests);
+  for (int i = 0; i < max_requests; ++i) p->free_slots[i] = max_requests - 1 - i;
+  p->len.assign(max_requests, -1);
+  return p;
+}
+
+LLMH_API void llmh_pool_destroy(void* h) { delete static_cast<Pool*>(h); }
+LLMH_API const char* llmh_pool_error(void* h) { return static_cast<Pool*>(h)->error; }
+LLMH_API int llmh_pool_table_width(void* h, int g) { return static_cast<Pool*>(h)->groups[g].width; }
+LLMH_API int llmh_pool_free_pages(void* h, int g) { return (int)static_cast<Pool*>(h)->groups[g].free.size(); }
+LLMH_API int llmh_pool_free_slots(void* h) { return (int)static_cast<Pool*>(h)->free_slots.size(); }
+LLMH_API int llmh_pool_length(void* h, int slot) {
+  Pool* p = static_cast<Pool*>(h);
+  return p->live(slot) ? p->len[slot] : p->fail(ERR_CONTRACT, "slot %d is not live", slot);
+}
+
+// slot -1: a request not yet admitted; length -1: the slot's current length
+LLMH_API int llmh_pool_pages_needed(void* h, int slot, int length, int n_new, int* out) {
+  Pool* p = static_cast<Pool*>(h);
+  if (slot >= 0 && !p->live(slot)) return p->fail(ERR_CONTRACT, "slot %d is not live", slot);
+  const int cur = length >= 0 ? length : (slot >= 0 ? p->len[slot] : 0);
+  p->pages_needed(slot, cur, n_new, out);
+  return 0;
+}
+
+// A new request takes a state slot.
+LLMH_API int llmh_pool_admit(void* h) {
+  Pool* p = static_cast<Pool*>(h);
+  if (p->free_slots.empty()) return p->fail(ERR_CONTRACT, "no request slot free (%d live)", p->max_requests);
+  const int slot = p->free_slots.back();
+  p->free_slots.pop_back();
+  p->len[slot] = 0;
+  for (Group& grp : p->groups) {
+    grp.n_pages[slot] = 0;
+    grp.first_live[slot] = 0;
+  }
+  p->fresh.push_back(slot);
+  return slot;
+}
+
+LLMH_API int llmh_pool_take_fresh(void* h, int* out, int capacity) {
+  Pool* p = static_cast<Pool*>(h);
+  const int n = std::min((int)p->fresh.size(), capacity);
+  std::copy(p->fresh.begin(), p->fresh.begin() + n, out);
+  p->fresh.clear();
+  return n;
+}
+
+// The request is about to write n_new tokens: give back window pages that are out of sight,
+// take the pages that the new tokens need, return the position of the first new token.
+LLMH_API int llmh_pool_extend(void* h, int slot, int n_new) {
+  Pool* p = static_cast<Pool*>(h);
+  if (!p->live(slot)) return p->fail(ERR_CONTRACT, "slot %d is not live", slot);
+  if (n_new <= 0) return p->fail(ERR_CONTRACT, "extend needs at least one token");
+  const int cur = p->len[slot];
+  if (cur + n_new > p->max_seq_len)
+    return p->fail(ERR_CONTRACT, "slot %d: %d+%d tokens exceed max_seq_len %d", slot, cur, n_new, p->max_seq_len);
+  int needs[64];
+  if (p->groups.size() > 64) return p->fail(ERR_CONTRACT, "too many cache groups");
+  p->pages_needed(slot, cur, n_new, needs);
+  for (size_t g = 0; g < p->groups.size(); ++g)
+    if (needs[g] > (int)p->groups[g].free.size())
+      return p->fail(ERR_OUT_OF_PAGES, "group %d: slot %d needs %d pages, %d free", (int)g, slot, needs[g], (int)p->groups[g].free.size());
+  for (Group& grp : p->groups) {
+    int* row = grp.table.data() + (size_t)slot * grp.width;
+    if (grp.kind == KIND_WINDOW) {
+      const int dead = std::min(grp.dead_before(cur), grp.n_pages[slot]);
+      for (int i = grp.first_live[slot]; i < dead; ++i) {
+        grp.free.push_back(row[i]);
+        row[i] = -1;
+      }
+      grp.first_live[slot] = std::max(grp.first_live[slot], dead);
+    }
+    const int want = grp.pages_for(cur + n_new);
+    for (int i = grp.n_pages[slot]; i < want; ++i) {
+      row[i] = grp.free.back();
+      grp.free.pop_back();
+    }
+    grp.n_pages[slot] = want;
+  }
+  p->len[slot] = cur + n_new;
+  return cur;
+}
+
+// The request ended: all its pages and its slot go back.
+LLMH_API int llmh_pool_release(void* h, int slot) {
+  Pool* p = static_cast<Pool*>(h);
+  if (!p->live(slot)) return p->fail(ERR_CONTRACT, "slot %d is not live (released twice?)", slot);
+  for (Group& grp : p->groups) {
+    int* row = grp.table.data() + (size_t)slot * grp.width;
+    for (int i = grp.first_live[slot]; i < grp.n_pages[slot]; ++i) grp.free.push_back(row[i]);
+    std::fill(row, row + grp.n_pages[slot], -1);
+    grp.n_pages[slot] = 0;
+    grp.first_live[slot] = 0;
+  }
+  p->free_slots.push_back(slot);
+  p->len[slot] = -1;
+  return 0;
+}
+
+// The slot's table row in group g (width entries; -1 where no page is held), the number of
+// logical pages in it and the first one still held.
+LLMH_API const int* llmh_pool_table(void* h, int g, int slot, int* n_pages, int* first_live) {
+  Pool* p = static_cast<Pool*>(h);
+  const Group& grp = p->groups[g];
+  *n_pages = grp.n_pages[slot];
+  *first_live = grp.first_live[slot];
+  return grp.table.data() + (size_t)slot * grp.width;
+}
+
+// No page lost, held twice or free twice; no slot lost or shared; tables match lengths.
+LLMH_API int llmh_pool_check(void* h) {
+  Pool* p = static_cast<Pool*>(h);
+  for (size_t g = 0; g < p->groups.size(); ++g) {
+    const Group& grp = p->groups[g];
+    std::vector<int> seen(grp.num_pages, 0);
+    for (int page : grp.free) {
+      if (page < 0 || page >= grp.num_pages) return p->fail(ERR_CONTRACT, "group %d: page %d on the free list", (int)g, page);
+      ++seen[page];
+    }
+    for (int slot = 0; slot < p->max_requests; ++slot) {
+      if (p->len[slot] < 0) continue;
+      if (grp.n_pages[slot] != grp.pages_for(p->len[slot]))
+        return p->fail(ERR_CONTRACT, "group %d: table of slot %d does not match its length", (int)g, slot);
+      const int* row = grp.table.data() + (size_t)slot * grp.width;
+      for (int i = grp.first_live[slot]; i < grp.n_pages[slot]; ++i) {
+        if (row[i] < 0 || row[i] >= grp.num_pages)
+          return p->fail(ERR_CONTRACT, "group %d: a live table entry is marked as given back", (int)g);
+        ++seen[row[i]];
+      }
+    }
+    for (int page = 0; page < grp.num_pages; ++page) {
+      if (seen[page] > 1) return p->fail(ERR_CONTRACT, "group %d: a page is held twice or free twice (page %d)", (int)g, page);
+      if (seen[page] == 0) return p->fail(ERR_CONTRACT, "group %d: pages lost (page %d)", (int)g, page);
+    }
+  }
+  std::vector<int> slots(p->max_requests, 0);
+  for (int s : p->free_slots) ++slots[s];
+  for (int s = 0; s < p->max_requests; ++s)
+    if ((p->len[s] >= 0) + slots[s] != 1) return p->fail(ERR_CONTRACT, "a request slot is lost or shared (slot %d)", s);
+  return 0;
+}
+
+// ---- a step's metadata ---------------------------------------------------------------------
+// Offsets (in int32 words) of the arrays inside the metadata block; block_table and slot_map
+// have one entry per cache group.
+struct StepLayout {
+  int token_ids, positions, token_entry, cu_tokens, kv_lens, state_slots, logit_rows, feed_dst, feed_src;
+  int n_groups;
+  int block_table[16], slot_map[16];
+};
+
+// Entries b = 0..B-1: slot, number of new tokens, position of the first (what extend returned);
+// tokens: all entries' token ids back to back (a fed entry's token is a placeholder);
+// want_counts/wants: per entry the wanted places among its tokens; feeds: per entry the row of
+// the feed source or -1.  Writes the block (int32) and returns the number of fed entries, or a
+// negative code.
+LLMH_API int llmh_prepare_step(void* h, const StepLayout* lay, int32_t* block, int B, const int* slots,
+                               const int* n_tokens, const int* starts, const int* tokens, const int* want_counts,
+                               const int* wants, const int* feeds) {
+  Pool* p = static_cast<Pool*>(h);
+  if (lay->n_groups != (int)p->groups.size() || lay->n_groups > 16) return p->fail(ERR_CONTRACT, "layout and pool disagree on the groups");
+  int t = 0, r = 0, w_at = 0, n_feed = 0;
+  block[lay->cu_tokens] = 0;
+  for (int b = 0; b < B; ++b) {
+    const int slot = slots[b], n = n_tokens[b], start = starts[b];
+    if (!p->live(slot) || p->len[slot] != start + n) return p->fail(ERR_CONTRACT, "entry %d: slot %d does not hold %d tokens", b, slot, start + n);
+    for (int i = 0; i < n; ++i) {
+      block[lay->token_ids + t + i] = tokens[t + i];
+      block[lay->positions + t + i] = start + i;
+      block[lay->token_entry + t + i] = b;
+    }
+    for (int g = 0; g < lay->n_groups; ++g) {
+      const Group& grp = p->groups[g];
+      const int* row = grp.table.data() + (size_t)slot * grp.width;
+      int32_t* bt = block + lay->block_table[g] + (size_t)b * grp.width;
+      std::copy(row, row + grp.width, bt);
+      int32_t* sm = block + lay->slot_map[g] + t;
+      for (int i = 0; i < n; ++i) {
+        const int pos = start + i;
+        sm[i] = row[pos / grp.page_size] * grp.page_size + pos % grp.page_size;
+      }
+    }
+    for (int i = 0; i < want_counts[b]; ++i) block[lay->logit_rows + r++] = t + wants[w_at + i];
+    w_at += want_counts[b];
+    if (feeds[b] >= 0) {
+      block[lay->feed_dst + n_feed] = t;
+      block[lay->feed_src + n_feed] = feeds[b];
+      ++n_feed;
+    }
+    block[lay->kv_lens + b] = start + n;
+    block[lay->state_slots + b] = slot;
+    t += n;
+    block[lay->cu_tokens + b + 1] = t;
+  }
+  return n_feed;
+}

@@ -13,6 +13,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
+import ctypes
+
 import numpy as np
 import torch
 
@@ -66,6 +68,24 @@ class _MetaLayout:
         self.slot_map = [take(max_tokens) for _ in table_widths]
         self.block_table = [take(max_entries * w) for w in table_widths]
         self.total = off
+
+
+class _NativeLayout(ctypes.Structure):
+    """The layout as the native step preparation takes it (StepLayout in csrc/host/page_pool.cpp)."""
+    _fields_ = [(n, ctypes.c_int) for n in ("token_ids", "positions", "token_entry", "cu_tokens", "kv_lens", "state_slots",
+                                            "logit_rows", "feed_dst", "feed_src", "n_groups")] + \
+               [("block_table", ctypes.c_int * 16), ("slot_map", ctypes.c_int * 16)]
+
+    @classmethod
+    def of(cls, lay: "_MetaLayout") -> "_NativeLayout":
+        if len(lay.block_table) > 16:
+            raise ValueError("at most 16 cache groups")
+        out = cls(lay.token_ids, lay.positions, lay.token_entry, lay.cu_tokens, lay.kv_lens, lay.state_slots,
+                  lay.logit_rows, lay.feed_dst, lay.feed_src, len(lay.block_table))
+        for g, (bt, sm) in enumerate(zip(lay.block_table, lay.slot_map)):
+            out.block_table[g] = bt
+            out.slot_map[g] = sm
+        return out
 
 
 class Engine:
@@ -165,8 +185,7 @@ class Engine:
         widths = [self.cache.table_width(g) for g in range(self.cache.num_groups)]
         self.layout = lay = _MetaLayout(self.max_tokens, self.max_entries, self.max_rows, widths)
         self._host_ring = [torch.zeros(lay.total, dtype=torch.int32).pin_memory() for _ in range(4)]
-        # host copy of every request slot's block table, per group, kept up to date as pages are taken
-        self._table_mirror = [np.zeros((self.max_entries, w), dtype=np.int32) for w in widths]
+        self._native_layout = _NativeLayout.of(lay)
         self._host_events = [None] * len(self._host_ring)
         self._ring_at = 0
         self.meta = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
@@ -293,60 +312,31 @@ class Engine:
 
         lay = self.layout
         host_t = self._next_host_buffer()
-        host = host_t.numpy()
         B = len(entries)
-        ns = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=B)
-        starts = np.empty(B, dtype=np.int64)
-        slots = np.empty(B, dtype=np.int64)
-        G = cache.num_groups
+        ns = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=B)
+        starts = np.empty(B, dtype=np.int32)
+        slots = np.empty(B, dtype=np.int32)
         for b, e in enumerate(entries):
             rid = e.request_id
             if not cache.is_live(rid):
                 cache.admit(rid)
-            start = cache.extend(rid, int(ns[b]))
-            slot = cache.slot(rid)
-            starts[b], slots[b] = start, slot
-            for g in range(G):                      # pages taken by this step go into the host mirror of the tables
-                table = cache.table(g, rid)
-                first_new = start // self.page_size
-                if len(table) > first_new:
-                    self._table_mirror[g][slot, first_new:len(table)] = table[first_new:]
-        cu = np.zeros(B + 1, dtype=np.int64)
-        np.cumsum(ns, out=cu[1:])
-        T = int(cu[B])
-        if T == B:                                  # one token each: no repeats needed
-            entry_of = np.arange(B, dtype=np.int64)
-            pos = starts
-            host[lay.token_ids: lay.token_ids + T] = token_arrays
-        else:
-            entry_of = np.repeat(np.arange(B, dtype=np.int64), ns)
-            pos = starts[entry_of] + (np.arange(T, dtype=np.int64) - cu[entry_of])
-            host[lay.token_ids: lay.token_ids + T] = np.concatenate([np.atleast_1d(a) for a in token_arrays])
-        host[lay.positions: lay.positions + T] = pos
-        host[lay.token_entry: lay.token_entry + T] = entry_of
-        host[lay.cu_tokens: lay.cu_tokens + B + 1] = cu
-        host[lay.kv_lens: lay.kv_lens + B] = starts + ns
-        host[lay.state_slots: lay.state_slots + B] = slots
-        ps = self.page_size
-        for g in range(G):
-            w = cache.table_width(g)
-            mirror = self._table_mirror[g]
-            host[lay.block_table[g]: lay.block_table[g] + B * w].reshape(B, w)[:] = mirror[slots]
-            host[lay.slot_map[g]: lay.slot_map[g] + T] = mirror[slots[entry_of], pos // ps] * ps + pos % ps
-        if n_rows:
-            r0 = 0
-            for b, e in enumerate(entries):
-                for w_ in e.want:
-                    host[lay.logit_rows + r0] = cu[b] + w_
-                    r0 += 1
-        n_feed = 0
-        if feed_source is not None:
-            for b, e in enumerate(entries):
-                if e.feed is not None:
-                    host[lay.feed_dst + n_feed] = cu[b]
-                    host[lay.feed_src + n_feed] = e.feed
-                    n_feed += 1
-        entry_tokens, entry_start, entry_slots = ns.astype(np.int32), starts.astype(np.int32), slots.astype(np.int32)
+            starts[b] = cache.extend(rid, int(ns[b]))
+            slots[b] = cache.slot(rid)
+        T = n_tokens
+        tokens = (np.asarray(token_arrays, dtype=np.int32) if T == B
+                  else np.concatenate([np.atleast_1d(a) for a in token_arrays]).astype(np.int32, copy=False))
+        want_counts = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=B)
+        wants = np.fromiter((w for e in entries for w in e.want), dtype=np.int32, count=n_rows)
+        feeds = np.fromiter((-1 if (e.feed is None or feed_source is None) else e.feed for e in entries), dtype=np.int32, count=B)
+        # the native routine writes tokens, positions, block tables, slot maps, wanted rows and the
+        # rest of the step's metadata into the pinned block, from the pool's own tables
+        lib, pool = cache.native
+        ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+        n_feed = lib.llmh_prepare_step(pool, ctypes.byref(self._native_layout), ctypes.c_void_p(host_t.data_ptr()), B,
+                                       ptr(slots), ptr(ns), ptr(starts), ptr(tokens), ptr(want_counts), ptr(wants), ptr(feeds))
+        if n_feed < 0:
+            raise StepError(lib.llmh_pool_error(pool).decode("utf-8", "replace"))
+        entry_tokens, entry_start, entry_slots = ns, starts, slots
         fresh = cache.take_fresh_slots()
         if fresh:
             self.state_storage.zero_slots(fresh)
