@@ -5,8 +5,8 @@
 // inside of a range.  The query heads of the kv group are the rows of an m16n8k16 MMA (up to 16
 // per pass): one instruction scores 8 keys for all of them, so the arithmetic per key no longer
 // grows with the group size.  Each of the four warps works alone on tiles of 32 keys, without
-// block-wide barriers: keys and values are staged per warp through two stages of shared memory
-// with cp.async (the next tile is in flight while one is computed) and read back with ldmatrix
+// block-wide barriers: keys and values are staged per warp through one to three stages of shared
+// memory with cp.async (with several, the next tiles are in flight while one is computed) and read back with ldmatrix
 // (values transposed); scores, maxima, sums and the output are float32, P is rounded to
 // bfloat16 for the second MMA as in the prompt kernel.  A single decoded token has no use for
 // the 128-row tcgen05 MMA; this is the tensor path that fits 8 to 16 rows.

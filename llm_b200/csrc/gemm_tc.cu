@@ -2,7 +2,8 @@
 // accumulation in tensor memory.
 //
 // Both operands are K-major, as activations and checkpoint weights ([out, in]) already
-// are, so nothing is transposed.  One CTA computes one tile: a producer thread moves
+// are, so nothing is transposed.  One CTA computes one tile (or, in the persistent variant for
+// many rows further down, walks over tiles): a producer thread moves
 // [rows x 64] boxes of both operands into a ring of 128-byte-swizzled stages with TMA,
 // one thread issues tcgen05.mma (M = 128, N = BNQ, K = 16, four per stage) and frees each
 // stage with tcgen05.commit, four warps read the accumulator back with tcgen05.ld and
