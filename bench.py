@@ -231,7 +231,7 @@ def main() -> int:
 
     # ---- end to end: the same decode through LLM.generate, host tokens in and out ----
     prompts = [prompt(PROMPT_LEN) for _ in range(args.batch)]
-    llm.generate(prompts[:1], max_new_tokens=4)                      # warm the path
+    llm.generate(prompts, max_new_tokens=args.steps + 1)             # warm-up: the same shapes, so that their graphs exist
     gen = llm.generate(prompts, max_new_tokens=args.steps + 1)
     st = llm.last_stats
     e2e_value = st["decode_tokens"] / st["decode_seconds"] if st["decode_seconds"] > 0 else None
