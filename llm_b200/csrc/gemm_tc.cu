@@ -354,6 +354,34 @@ enum : int { ERR_P_PRODUCER = 4, ERR_P_MMA = 5, ERR_P_EPILOGUE = 6 };
 // silu(gate) * up in float32, as the stand-alone kernel computes it
 __device__ __forceinline__ float silu_times(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
+// 32 values of one row of C, columns q .. q + 32 (those below q_limit), as 16-byte stores where
+// the row allows it.
+template <typename TOut>
+__device__ __forceinline__ void store_row32(TOut* row, const float (&v)[32], int q, int q_limit) {
+  const bool vec_ok = (q + 32 <= q_limit) && ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
+  if (vec_ok) {
+    if (sizeof(TOut) == 2) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 u;
+        __nv_bfloat162 b0 = __floats2bfloat162_rn(v[j], v[j + 1]), b1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+        __nv_bfloat162 b2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), b3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+        u.x = *reinterpret_cast<uint32_t*>(&b0); u.y = *reinterpret_cast<uint32_t*>(&b1);
+        u.z = *reinterpret_cast<uint32_t*>(&b2); u.w = *reinterpret_cast<uint32_t*>(&b3);
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(row) + j) = u;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(row) + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (q + j < q_limit) store_one(row + j, v[j]);
+  }
+}
+
 template <typename TOut, bool SWIGLU>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
@@ -491,29 +519,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
         if (p >= M) continue;
         const int q = q0 + c;
         const int q_limit = SWIGLU ? inter : N;
-        TOut* row = C + (long long)p * ldc + q;
-        const bool vec_ok = (q + 32 <= q_limit) && ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
-        if (vec_ok) {
-          if (sizeof(TOut) == 2) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 u;
-              __nv_bfloat162 b0 = __floats2bfloat162_rn(v[j], v[j + 1]), b1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-              __nv_bfloat162 b2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), b3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-              u.x = *reinterpret_cast<uint32_t*>(&b0); u.y = *reinterpret_cast<uint32_t*>(&b1);
-              u.z = *reinterpret_cast<uint32_t*>(&b2); u.w = *reinterpret_cast<uint32_t*>(&b3);
-              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(row) + j) = u;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<float4*>(reinterpret_cast<float*>(row) + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (q + j < q_limit) store_one(row + j, v[j]);
-        }
+        store_row32(C + (long long)p * ldc + q, v, q, q_limit);
       }
       fence_before_sync();
       __syncwarp();
@@ -527,6 +533,187 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
   if (warp == 1) {
     fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- persistent variant on pairs of CTAs ---------------------------------------------------
+// Two CTAs on neighbouring SMs (a cluster of two) work on one tile of 256 rows x tile_q columns
+// with MMAs of cta_group::2: each CTA stages its 128 rows of A and its half of the tile's rows of
+// W, the first CTA's MMA thread issues for both, and each CTA's tensor memory holds the
+// accumulator of its own 128 rows.  A k-block then costs each SM 32 KB of loads for 128 x 256 x 64
+// products where the single-CTA kernel above needs 48 KB, which is what bounds that kernel; the
+// ring has six stages instead of four.  Everything else (walk over the tiles, two accumulators,
+// the epilogue, SWIGLU) is as above; with SWIGLU the first CTA stages the 128 gate rows and the
+// second the 128 up rows.
+//
+// Barriers: the loads of both CTAs count on the first CTA's full barrier; tcgen05.commit arrives
+// on the empty barrier (and on acc_full) of both CTAs; the epilogue warps of both CTAs arrive on
+// the first CTA's acc_empty.
+enum : int { ERR_2_PRODUCER = 7, ERR_2_MMA = 8, ERR_2_EPILOGUE = 9 };
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_Q_STAGE_BYTES = 128 * BK * 2;      // up to 128 rows of W per CTA
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * (P_STAGE_BYTES + PAIR_Q_STAGE_BYTES) + 1024 + 256;
+
+template <typename TOut, bool SWIGLU>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                    TOut* __restrict__ C, long long ldc, int M, int N, int K, int tile_q, int* __restrict__ err_flag) {
+  constexpr int STAGES = PAIR_STAGES;
+  constexpr int BNQ = 256;                      // columns of one accumulator
+  constexpr uint32_t TMEM_COLS = 512;
+  const uint32_t IDESC = idesc_bf16_f32(2 * BP, tile_q);
+  const int half_q = tile_q / 2;                // rows of W that each CTA stages
+  const uint32_t stage_tx = 2u * (uint32_t)(P_STAGE_BYTES + half_q * BK * 2);      // both CTAs' boxes
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem_p = smem;
+  uint8_t* smem_q = smem + STAGES * P_STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * (P_STAGE_BYTES + PAIR_Q_STAGE_BYTES));
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;       // [2] MMA -> epilogue, in both CTAs
+  uint64_t* acc_empty = acc_full + 2;            // [2] epilogue -> MMA: the first CTA's, eight warps arrive
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int inter = N / 2;
+  const int m_tiles = (M + 2 * BP - 1) / (2 * BP), n_tiles = SWIGLU ? (inter + 127) / 128 : (N + tile_q - 1) / tile_q;
+  const int total_tiles = m_tiles * n_tiles;
+  const int nkb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);
+    }
+    fence_mbar_init();
+    prefetch_tensormap(&map_p);
+    prefetch_tensormap(&map_q);
+  }
+  if (warp == 1) tmem_alloc_pair(tmem_slot, TMEM_COLS);
+  fence_before_sync();
+  cluster_sync();                 // both CTAs' barriers are initialised before either is signalled from the other side
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  pdl_launch_dependents();
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- producer (both CTAs) ----
+      pdl_wait();
+      bool ok = true;
+      int it = 0;
+      for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
+        const int p0 = (tile % m_tiles) * (2 * BP) + (int)rank * BP;
+        const int q_tile = (tile / m_tiles) * (SWIGLU ? 128 : tile_q);
+        const int q0 = SWIGLU ? (rank ? inter + q_tile : q_tile) : q_tile + (int)rank * half_q;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1);
+          if (!ok) break;
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], stage_tx);
+          const uint32_t full0 = map_to_cta(smem_u32(&full_bar[s]), 0);
+          tma_load_2d_pair(smem_q + s * PAIR_Q_STAGE_BYTES, &map_q, kb * BK, q0, full0);
+          tma_load_2d_pair(smem_p + s * P_STAGE_BYTES, &map_p, kb * BK, p0, full0);
+        }
+      }
+      if (!ok) {
+        atomicExch(err_flag, ERR_2_PRODUCER);
+        // loads in flight must land before the CTA may go: the first CTA can wait for them on its
+        // barriers, the second one lets their time pass
+        if (rank == 0) {
+          for (int i = max(0, it - STAGES); i < it; ++i) mbar_wait(&full_bar[i % STAGES], (i / STAGES) & 1);
+        } else {
+          const long long t0 = clock64();
+          while (clock64() - t0 < 4000000ll) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // ---- MMA issuer (the first CTA's, for both) ----
+      bool ok = true;
+      int it = 0, n = 0;
+      for (int tile = pair; tile < total_tiles && ok; tile += pairs, ++n) {
+        const int buf = n & 1;
+        ok = mbar_wait(&acc_empty[buf], ((n >> 1) & 1) ^ 1);   // both epilogues have drained this accumulator
+        if (!ok) break;
+        fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BNQ);
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(&full_bar[s], (it / STAGES) & 1);
+          if (!ok) break;
+          fence_after_sync();
+          const uint64_t desc_p = smem_desc_sw128(smem_u32(smem_p + s * P_STAGE_BYTES));
+          const uint64_t desc_q = smem_desc_sw128(smem_u32(smem_q + s * PAIR_Q_STAGE_BYTES));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) mma_bf16_pair(d_tmem, desc_p + 2 * k, desc_q + 2 * k, IDESC, (kb | k) != 0);
+          mma_commit_pair(&empty_bar[s], 3);
+        }
+        mma_commit_pair(&acc_full[buf], 3);
+      }
+      if (!ok) {
+        atomicExch(err_flag, ERR_2_MMA);
+        mma_commit_pair(&acc_full[0], 3);
+        mma_commit_pair(&acc_full[1], 3);
+      }
+    }
+  } else {
+    // ---- epilogue (both CTAs, each its own 128 rows) ----
+    const int quad = warp & 3;
+    bool ok = true;
+    int n = 0;
+    for (int tile = pair; tile < total_tiles; tile += pairs, ++n) {
+      const int buf = n & 1;
+      const int p0 = (tile % m_tiles) * (2 * BP) + (int)rank * BP, q0 = (tile / m_tiles) * (SWIGLU ? 128 : tile_q);
+      const int p = p0 + quad * 32 + lane;
+      if (ok) ok = mbar_wait(&acc_full[buf], (n >> 1) & 1);
+      fence_after_sync();
+#pragma unroll 1
+      for (int c = 0; c < (SWIGLU ? 128 : tile_q); c += 32) {
+        float v[32];
+        if (ok) {
+          uint32_t r[32];
+          tmem_ld_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BNQ + c), r);
+          if (SWIGLU) {
+            uint32_t u[32];
+            tmem_ld_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BNQ + 128 + c), u);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = silu_times(__uint_as_float(r[j]), __uint_as_float(u[j]));
+          } else {
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+        if (p >= M) continue;
+        const int q = q0 + c;
+        store_row32(C + (long long)p * ldc + q, v, q, SWIGLU ? inter : N);
+      }
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+    }
+    if (!ok && lane == 0) atomicExch(err_flag, ERR_2_EPILOGUE);
+  }
+
+  // Neither CTA may go while the other may still read its shared memory or signal its barriers.
+  fence_before_sync();
+  cluster_sync();
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
 }
 
@@ -622,6 +809,58 @@ int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, void* C, lon
   LLMK_LAUNCH_CHECK("gemm_tc_persistent");
 }
 
+// The pairs that can run at once (one CTA per SM, two neighbouring SMs per pair), asked once.
+template <typename Kernel>
+int max_pairs(Kernel kern) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * 148);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n < 74 ? n : 74;
+}
+
+template <typename TOut, bool SWIGLU>
+int launch_pair(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long ldc, int M, int N, int K,
+                int tile_q, cudaStream_t stream) {
+  auto kern = gemm_tc_pair_kernel<TOut, SWIGLU>;
+  static int pairs_max = -1;
+  if (pairs_max < 0) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES);
+    if (e != cudaSuccess) return llmk_fail((int)e, "gemm_tc: cannot set %d bytes of shared memory: %s", PAIR_SMEM_BYTES, cudaGetErrorString(e));
+    pairs_max = max_pairs(kern);
+  }
+  if (pairs_max < 1) return llmk_fail(-2, "gemm_tc: no pair of CTAs of the pair kernel fits this device");
+  const int tiles = ((M + 2 * BP - 1) / (2 * BP)) * (SWIGLU ? (N / 2 + 127) / 128 : (N + tile_q - 1) / tile_q);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * (tiles < pairs_max ? tiles : pairs_max));
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = llmk_pdl_enabled() ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, kern, mp, mq, (TOut*)C, ldc, M, N, K, tile_q, g_err_flag);
+  LLMK_LAUNCH_CHECK("gemm_tc_pair");
+}
+
 template <typename TOut>
 int launch_out(bool swap, int bnq, bool cluster, const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long ldc,
                long long split_stride, int M, int N, int K, int splits, int kbps, cudaStream_t s) {
@@ -662,8 +901,9 @@ LLMK_API int llmk_gemm_tc_supported(const void* A, const void* W, int M, int N, 
 // splits > 1 with cluster != 0 (swapped mode, tile up to 64, at most 8 splits): the splits of a
 // tile form a thread-block cluster, sum their results on chip and write C as for splits == 1.
 // cluster == 2 selects the persistent kernel (normal mode, one split): one CTA per SM walks over
-// the tiles with two accumulators in tensor memory.
-// swiglu != 0 (persistent kernel only): W [N = 2I, K] is I gate rows followed by I up rows and C
+// the tiles with two accumulators in tensor memory.  cluster == 3: the same on pairs of CTAs with
+// tiles of 256 rows (cta_group::2).
+// swiglu != 0 (persistent kernels only): W [N = 2I, K] is I gate rows followed by I up rows and C
 // [M, I] (bfloat16) receives silu(gate) * up instead of the product.
 // swap != 0 puts the weights on the 128-row side of the MMA; tile is the other side's width
 // (16, 32, 64 or 128 when swapped; a multiple of 32 up to 256 otherwise).
@@ -672,7 +912,7 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
                           int cluster, int swiglu, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (swiglu) {
-    LLMK_REQUIRE(cluster == 2 && !swap && splits == 1 && N % 2 == 0 && (N / 2) % 8 == 0,
+    LLMK_REQUIRE((cluster == 2 || cluster == 3) && !swap && splits == 1 && N % 2 == 0 && (N / 2) % 8 == 0,
                  "gemm_tc: silu(gate) * up in the epilogue needs the persistent kernel and an even N with N/2 a multiple of 8, got N=%d", N);
     tile = 256;       // 128 gate rows and their 128 up rows
   }
@@ -694,7 +934,18 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
   const long long ldp = swap ? ldw : lda, ldq = swap ? lda : ldw;
   const int p_rows = swap ? N : M, q_rows = swap ? M : N;
   if ((rc = get_map(&mp, P, p_rows, K, ldp, BP))) return rc;
-  if ((rc = get_map(&mq, Q, q_rows, K, ldq, swiglu ? 128 : tile))) return rc;
+  if ((rc = get_map(&mq, Q, q_rows, K, ldq, swiglu ? 128 : cluster == 3 ? tile / 2 : tile))) return rc;
+  if (cluster == 3) {       // persistent kernel on pairs of CTAs: normal mode, no split
+    LLMK_REQUIRE(!swap && splits == 1 && tile % 32 == 0 && tile >= 32 && tile <= 256,
+                 "gemm_tc: the pair kernel takes the normal mode, one split and a tile of 32..256 in steps of 32");
+    if (swiglu) {
+      if (out_dtype == LLMK_BF16) return launch_pair<__nv_bfloat16, true>(mp, mq, C, ldc, M, N, K, tile, stream);
+      return llmk_fail(-1, "gemm_tc: silu(gate) * up is written as bfloat16 only");
+    }
+    if (out_dtype == LLMK_F32) return launch_pair<float, false>(mp, mq, C, ldc, M, N, K, tile, stream);
+    if (out_dtype == LLMK_BF16) return launch_pair<__nv_bfloat16, false>(mp, mq, C, ldc, M, N, K, tile, stream);
+    return llmk_fail(-1, "gemm_tc: unsupported output kind %d", out_dtype);
+  }
   if (cluster == 2) {       // persistent kernel: normal mode, no split
     LLMK_REQUIRE(!swap && splits == 1 && tile % 32 == 0 && tile >= 32 && tile <= 256,
                  "gemm_tc: the persistent kernel takes the normal mode, one split and a tile of 32..256 in steps of 32");

@@ -426,33 +426,35 @@ def cluster_fits(tile: int, splits: int) -> bool:
 
 
 PERSISTENT_GEMM = True
+PAIR_GEMM = True
 
 
 def plan_gemm(M: int, N: int, K: int, fused_reduce: bool = False):
-    return _plan_gemm(M, N, K, fused_reduce, PERSISTENT_GEMM)
+    return _plan_gemm(M, N, K, fused_reduce, PERSISTENT_GEMM, PAIR_GEMM)
 
 
 @functools.lru_cache(maxsize=4096)
-def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool):
+def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool, pair: bool = False):
     """(swap, tile, splits, k-blocks per split, mode) for the tensor-core product; mode 0 = one
-    CTA per tile, 1 = the splits of a tile sum on chip in a cluster, 2 = persistent CTAs.
+    CTA per tile, 1 = the splits of a tile sum on chip in a cluster, 2 = persistent CTAs, 3 =
+    persistent pairs of CTAs on tiles of 256 rows.
 
     Up to 128 rows the weights take the 128-row side of the MMA and the rows become its N
     (16 to 128); above that the rows take the 128-row side and the tile is 128 or 256 weight
     rows wide.  K (in blocks of 64) is split over CTAs when there are too few tiles to keep
     all SMs streaming; where the shape allows it the splits of a tile form a cluster and sum
     their results in shared memory, else they write float32 partial results for a later sum.
-    The estimate, in microseconds: per CTA a fixed cost plus, per k-block, the larger of its
-    tensor-core time and its share of HBM time; times the number of waves; plus the sum."""
+    The estimate, in microseconds, for more than 128 rows: a fixed cost plus waves of tiles times
+    k-blocks times a k-block's time, fitted to timings of the products of the 1.1B and 7B shapes
+    at 129 to 4,096 rows; plus the sum of the partial results where K is split."""
     kb = _ceil_div(K, 64)
     if M <= 128:
         return _plan_swapped(M, N, kb, fused_reduce)
-    options = [(False, t, _ceil_div(M, 128) * _ceil_div(N, t)) for t in (256, 224, 192, 160, 128)]
     best = None
-    for swap, tile, tiles in options:
-        # us per k-block at one SM's tensor peak; a tile of 128 or less reads as many bytes from
-        # shared memory per MMA as the tensor core consumes and runs at about two thirds of that
-        t_kb = 128 * tile * 64 * 2 / 15.2e6 * (1.5 if tile <= 128 else 1.0)
+    for tile in (256, 224, 192, 160, 128):
+        tiles = _ceil_div(M, 128) * _ceil_div(N, tile)
+        # us per k-block of one CTA: bound by the bytes that it brings into shared memory
+        t_kb = (128 + tile) * 128 / 114e3
         for s in range(1, min(kb, 32) + 1):
             per = _ceil_div(kb, s)
             if _ceil_div(kb, per) != s:
@@ -461,17 +463,26 @@ def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool):
                 break
             mode = 0
             waves = _ceil_div(tiles * s, _SMS)
-            cost = waves * (per * t_kb + 2.5)
+            cost = waves * (per * t_kb + 0.8) + 7.2
             if persistent and s == 1 and tiles > _SMS:
                 # more than one wave of tiles: one CTA per SM walks over them and drains one
-                # accumulator while the next tile's products run, so the fixed cost is paid once
+                # accumulator while the next tile's products run
                 mode = 2
-                cost = waves * per * t_kb + 2.5
+                cost = waves * per * t_kb + 12.3
             if s > 1:
-                traffic = (2 * s + 1) * M * N * 4 / 4e6               # partials written and read back, us
-                cost += traffic + (0.5 if fused_reduce else 3.0)
+                traffic = (2 * s + 1) * M * N * 4 / 3.3e6             # partials written and read back, us
+                cost += traffic + (0.8 if fused_reduce else 3.3)
             if best is None or cost < best[0] - 1e-9:
-                best = (cost, swap, tile, s, per, mode)
+                best = (cost, False, tile, s, per, mode)
+        if pair:
+            # pairs of CTAs on tiles of 256 rows bring a third fewer bytes into shared memory per
+            # product: a k-block takes what its MMAs take (with the gaps measured) or, on narrow
+            # tiles, the latency of the ring
+            t_kb = max(0.31 + 0.0004 * (tile - 128), 1.43 * 256 * tile * 64 * 2 / 2 / 15.2e6)
+            waves = _ceil_div(_ceil_div(M, 256) * _ceil_div(N, tile), _SMS // 2)
+            cost = waves * kb * t_kb + 8.6
+            if cost < best[0] - 1e-9:
+                best = (cost, False, tile, 1, kb, 3)
     return best[1:]
 
 
@@ -581,7 +592,7 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int) 
     _check_t(load_tensor().llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
                                c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
                                c_int(_BF16), c_int(0), c_int(256), c_int(1), c_int(_ceil_div(k, 64)),
-                               c_int(2), c_int(1), _stream()))
+                               c_int(3 if PAIR_GEMM else 2), c_int(1), _stream()))
 
 
 def set_pdl(on: bool) -> None:

@@ -155,27 +155,33 @@ def test_gemm_tensor_core_every_configuration(ops, swap, tile, splits, cluster):
     (300, 520, 5 * 64 + 24, 32, torch.float32),       # 51 tiles, ragged edges on every side
     (2100, 1944, 3 * 64, 96, torch.bfloat16),         # 357 tiles: CTAs take two or three each
     (1300, 2072, 7 * 64 + 8, 256, torch.float32),     # widest tile, more k-blocks than stages
-    (4099, 1160, 64, 160, torch.bfloat16)])           # one k-block per tile: accumulators swap every block
-def test_gemm_tensor_core_persistent(ops, M, N, K, tile, out_dtype):
-    """One CTA per SM walks over the tiles with two accumulators in tensor memory."""
+    (4099, 1160, 64, 160, torch.bfloat16),            # one k-block per tile: accumulators swap every block
+    (129, 2500, 13 * 64, 224, torch.float32)])        # the second 128 rows hold one row only
+@pytest.mark.parametrize("mode", [2, 3])
+def test_gemm_tensor_core_persistent(ops, M, N, K, tile, out_dtype, mode):
+    """One CTA per SM (mode 2), or a pair of CTAs on two SMs with one MMA for both (mode 3), walks
+    over the tiles with two accumulators in tensor memory."""
     torch.manual_seed(8)
     a = torch.randn(M + 1, K, device=DEV).to(torch.bfloat16)
     w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
     out = torch.full((M + 1, N), 3.0, device=DEV, dtype=out_dtype)
     kb = -(-K // 64)
-    ops.gemm_fast(a, w, out, M, plan=(False, tile, 1, kb, 2))
+    ops.gemm_fast(a, w, out, M, plan=(False, tile, 1, kb, mode))
     torch.cuda.synchronize()
     assert ops.gemm_tc_take_error() == 0
     ref = a[:M].double() @ w.double().T
     assert rel_err(out[:M], ref) < (1e-5 if out_dtype == torch.float32 else 1e-2)
     assert float(out[M:].float().min()) == 3.0
+    # row by row, so that a tile that landed in another tile's place shows
+    worst = ((out[:M].double() - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)).max()
+    assert float(worst) < (1e-4 if out_dtype == torch.float32 else 3e-2)
     # a far-off element: one large entry in the last row and column must land exactly there
     a2 = torch.zeros(M, K, device=DEV, dtype=torch.bfloat16)
     w2 = torch.zeros(N, K, device=DEV, dtype=torch.bfloat16)
     a2[M - 1, K - 1] = 2.0
     w2[N - 1, K - 1] = 4.0
     out2 = torch.full((M, N), 1.0, device=DEV, dtype=out_dtype)
-    ops.gemm_fast(a2, w2, out2, M, plan=(False, tile, 1, kb, 2))
+    ops.gemm_fast(a2, w2, out2, M, plan=(False, tile, 1, kb, mode))
     assert float(out2[M - 1, N - 1]) == 8.0 and float(out2.float().abs().sum()) == 8.0
 
 
@@ -184,8 +190,11 @@ def test_gemm_tensor_core_persistent(ops, M, N, K, tile, out_dtype):
     (2100, 976, 3 * 64),            # 136 tiles
     (1300, 1048, 7 * 64 + 8),       # I no multiple of 16; more k-blocks than stages
     (2048, 5632, 256)])             # 704 tiles: CTAs take four or five each
-def test_gemm_tensor_core_with_silu_epilogue(ops, M, I, K):
-    """silu(gate) * up written by the product's epilogue: a tile takes 128 gate rows and their up rows."""
+@pytest.mark.parametrize("pair", [False, True])
+def test_gemm_tensor_core_with_silu_epilogue(ops, M, I, K, pair, monkeypatch):
+    """silu(gate) * up written by the product's epilogue: a tile takes 128 gate rows and their up
+    rows; by one CTA, or by a pair of which one stages the gate rows and the other the up rows."""
+    monkeypatch.setattr(ops, "PAIR_GEMM", pair)
     torch.manual_seed(9)
     a = torch.randn(M + 1, K, device=DEV).to(torch.bfloat16)
     gate = (torch.randn(I, K, device=DEV) / math.sqrt(K) * 3).to(torch.bfloat16)
