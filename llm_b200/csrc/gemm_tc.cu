@@ -550,14 +550,41 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
 // on the empty barrier (and on acc_full) of both CTAs; the epilogue warps of both CTAs arrive on
 // the first CTA's acc_empty.
 enum : int { ERR_2_PRODUCER = 7, ERR_2_MMA = 8, ERR_2_EPILOGUE = 9 };
+
+struct RopeStore;
+template <typename TOut>
+__device__ __forceinline__ void rope_store_epilogue(uint32_t t_row, bool ok, int p, bool row_valid, int q0, int tile_q,
+                                                    int N, TOut* __restrict__ C, long long ldc, const RopeStore& rs);
 constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_Q_STAGE_BYTES = 128 * BK * 2;      // up to 128 rows of W per CTA
 constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * (P_STAGE_BYTES + PAIR_Q_STAGE_BYTES) + 1024 + 256;
 
-template <typename TOut, bool SWIGLU>
+// What the epilogue EPI_ROPE needs besides the product: W's rows are query heads, then key
+// heads, then value heads (n_kv of each; none if n_kv == 0); row t of the product belongs to
+// position positions[t] and its key and value go to place slot_map[t] of the pages
+// [page][kv head][token in page][head_dim].  Tables [position][head_dim / 2], or null for no rotation.
+struct RopeStore {
+  const float* cos_table;
+  const float* sin_table;
+  const int* positions;
+  const int* slot_map;
+  __nv_bfloat16* k_pages;
+  __nv_bfloat16* v_pages;
+  int n_heads, n_kv, head_dim, page_size;
+};
+enum : int { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ROPE = 2 };
+
+// EPI_ROPE: the product is a QKV projection whose tiles are whole heads (tile_q a multiple of
+// head_dim, 64 or 128).  The epilogue rotates the query and key heads of its row by the row's
+// position (rotate-half, float32, on the float32 accumulator), writes the queries to C
+// [M, n_heads * head_dim] and stores keys and values in the pages, so the product itself never
+// reaches memory and no rotate-and-store kernel runs.
+template <typename TOut, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
-                    TOut* __restrict__ C, long long ldc, int M, int N, int K, int tile_q, int* __restrict__ err_flag) {
+                    TOut* __restrict__ C, long long ldc, int M, int N, int K, int tile_q, RopeStore rs,
+                    int* __restrict__ err_flag) {
+  constexpr bool SWIGLU = EPI == EPI_SWIGLU;
   constexpr int STAGES = PAIR_STAGES;
   constexpr int BNQ = 256;                      // columns of one accumulator
   constexpr uint32_t TMEM_COLS = 512;
@@ -676,30 +703,35 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       const int p = p0 + quad * 32 + lane;
       if (ok) ok = mbar_wait(&acc_full[buf], (n >> 1) & 1);
       fence_after_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BNQ);
+      if constexpr (EPI == EPI_ROPE) {
+        rope_store_epilogue(t_row, ok, p, p < M, q0, tile_q, N, C, ldc, rs);
+      } else {
 #pragma unroll 1
-      for (int c = 0; c < (SWIGLU ? 128 : tile_q); c += 32) {
-        float v[32];
-        if (ok) {
-          uint32_t r[32];
-          tmem_ld_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BNQ + c), r);
-          if (SWIGLU) {
-            uint32_t u[32];
-            tmem_ld_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BNQ + 128 + c), u);
-            tmem_ld_wait();
+        for (int c = 0; c < (SWIGLU ? 128 : tile_q); c += 32) {
+          float v[32];
+          if (ok) {
+            uint32_t r[32];
+            tmem_ld_x32(t_row + (uint32_t)c, r);
+            if (SWIGLU) {
+              uint32_t u[32];
+              tmem_ld_x32(t_row + (uint32_t)(128 + c), u);
+              tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = silu_times(__uint_as_float(r[j]), __uint_as_float(u[j]));
+              for (int j = 0; j < 32; ++j) v[j] = silu_times(__uint_as_float(r[j]), __uint_as_float(u[j]));
+            } else {
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            }
           } else {
-            tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
           }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          if (p >= M) continue;
+          const int q = q0 + c;
+          store_row32(C + (long long)p * ldc + q, v, q, SWIGLU ? inter : N);
         }
-        if (p >= M) continue;
-        const int q = q0 + c;
-        store_row32(C + (long long)p * ldc + q, v, q, SWIGLU ? inter : N);
       }
       fence_before_sync();
       __syncwarp();
@@ -714,6 +746,70 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   if (warp == 1) {
     fence_after_sync();
     tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+// The epilogue of a QKV projection (see RopeStore): this thread holds row p of the tile, whose
+// accumulator row starts at t_row in tensor memory; the tile's columns q0 .. q0 + tile_q are whole
+// heads.  Every lane runs the tensor-memory loads (they are warp-wide); only valid rows store.
+template <typename TOut>
+__device__ __forceinline__ void rope_store_epilogue(uint32_t t_row, bool ok, int p, bool row_valid, int q0, int tile_q,
+                                                    int N, TOut* __restrict__ C, long long ldc, const RopeStore& rs) {
+  const int hd = rs.head_dim, half = hd / 2;
+  int pos = 0, slot = 0;
+  if (row_valid) {
+    pos = rs.positions[p];
+    if (rs.n_kv) slot = rs.slot_map[p];
+  }
+  const int page = slot / rs.page_size, off = slot % rs.page_size;
+  const float* cs = rs.cos_table ? rs.cos_table + (size_t)pos * half : nullptr;
+  const float* sn = rs.cos_table ? rs.sin_table + (size_t)pos * half : nullptr;
+#pragma unroll 1
+  for (int hc = 0; hc < tile_q && q0 + hc < N; hc += hd) {
+    const int head = (q0 + hc) / hd;
+    const bool is_q = head < rs.n_heads, is_k = !is_q && head < rs.n_heads + rs.n_kv;
+    TOut* dst;
+    if (is_q) {
+      dst = C + (long long)p * ldc + (long long)head * hd;
+    } else {
+      const int g = head - rs.n_heads - (is_k ? 0 : rs.n_kv);
+      __nv_bfloat16* pages = is_k ? rs.k_pages : rs.v_pages;
+      dst = reinterpret_cast<TOut*>(pages + (((size_t)page * rs.n_kv + g) * rs.page_size + off) * hd);
+    }
+    const bool rotate = (is_q || is_k) && cs != nullptr;
+#pragma unroll 1
+    for (int i = 0; i < half; i += 32) {
+      // 32 columns of the first half of the head and their partners in the second half
+      float a[32], b[32];
+      if (ok) {
+        uint32_t ra[32], rb[32];
+        tmem_ld_x32(t_row + (uint32_t)(hc + i), ra);
+        tmem_ld_x32(t_row + (uint32_t)(hc + half + i), rb);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { a[j] = __uint_as_float(ra[j]); b[j] = __uint_as_float(rb[j]); }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { a[j] = 0.f; b[j] = 0.f; }
+      }
+      if (!row_valid) continue;
+      if (rotate) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 c4 = __ldg(reinterpret_cast<const float4*>(cs + i + j));
+          const float4 s4 = __ldg(reinterpret_cast<const float4*>(sn + i + j));
+          const float c[4] = {c4.x, c4.y, c4.z, c4.w}, s[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float x = a[j + k], y = b[j + k];
+            a[j + k] = x * c[k] - y * s[k];
+            b[j + k] = x * s[k] + y * c[k];
+          }
+        }
+      }
+      store_row32(dst + i, a, 0, 32);
+      store_row32(dst + half + i, b, 0, 32);
+    }
   }
 }
 
@@ -831,10 +927,11 @@ int max_pairs(Kernel kern) {
   return n < 74 ? n : 74;
 }
 
-template <typename TOut, bool SWIGLU>
+template <typename TOut, int EPI>
 int launch_pair(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long ldc, int M, int N, int K,
-                int tile_q, cudaStream_t stream) {
-  auto kern = gemm_tc_pair_kernel<TOut, SWIGLU>;
+                int tile_q, const RopeStore& rs, cudaStream_t stream) {
+  constexpr bool SWIGLU = EPI == EPI_SWIGLU;
+  auto kern = gemm_tc_pair_kernel<TOut, EPI>;
   static int pairs_max = -1;
   if (pairs_max < 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES);
@@ -857,7 +954,7 @@ int launch_pair(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = llmk_pdl_enabled() ? 2 : 1;
-  cudaLaunchKernelEx(&cfg, kern, mp, mq, (TOut*)C, ldc, M, N, K, tile_q, g_err_flag);
+  cudaLaunchKernelEx(&cfg, kern, mp, mq, (TOut*)C, ldc, M, N, K, tile_q, rs, g_err_flag);
   LLMK_LAUNCH_CHECK("gemm_tc_pair");
 }
 
@@ -939,11 +1036,11 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
     LLMK_REQUIRE(!swap && splits == 1 && tile % 32 == 0 && tile >= 32 && tile <= 256,
                  "gemm_tc: the pair kernel takes the normal mode, one split and a tile of 32..256 in steps of 32");
     if (swiglu) {
-      if (out_dtype == LLMK_BF16) return launch_pair<__nv_bfloat16, true>(mp, mq, C, ldc, M, N, K, tile, stream);
+      if (out_dtype == LLMK_BF16) return launch_pair<__nv_bfloat16, EPI_SWIGLU>(mp, mq, C, ldc, M, N, K, tile, RopeStore{}, stream);
       return llmk_fail(-1, "gemm_tc: silu(gate) * up is written as bfloat16 only");
     }
-    if (out_dtype == LLMK_F32) return launch_pair<float, false>(mp, mq, C, ldc, M, N, K, tile, stream);
-    if (out_dtype == LLMK_BF16) return launch_pair<__nv_bfloat16, false>(mp, mq, C, ldc, M, N, K, tile, stream);
+    if (out_dtype == LLMK_F32) return launch_pair<float, EPI_PLAIN>(mp, mq, C, ldc, M, N, K, tile, RopeStore{}, stream);
+    if (out_dtype == LLMK_BF16) return launch_pair<__nv_bfloat16, EPI_PLAIN>(mp, mq, C, ldc, M, N, K, tile, RopeStore{}, stream);
     return llmk_fail(-1, "gemm_tc: unsupported output kind %d", out_dtype);
   }
   if (cluster == 2) {       // persistent kernel: normal mode, no split
@@ -961,6 +1058,48 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
   if (out_dtype == LLMK_F32) return launch_out<float>(swap != 0, tile, cluster != 0, mp, mq, C, ldc, split_stride, M, N, K, splits, kblocks_per_split, stream);
   if (out_dtype == LLMK_BF16) return launch_out<__nv_bfloat16>(swap != 0, tile, cluster != 0, mp, mq, C, ldc, split_stride, M, N, K, splits, kblocks_per_split, stream);
   return llmk_fail(-1, "gemm_tc: unsupported output kind %d", out_dtype);
+}
+
+// Whether llmk_gemm_tc_qkv_rope takes these sizes and pointers.
+LLMK_API int llmk_gemm_tc_qkv_rope_supported(const void* A, const void* W, int M, int N, int K, long long lda,
+                                             long long ldw, const void* q_out, long long ldq, const float* cos_table,
+                                             const float* sin_table, const void* k_pages, const void* v_pages,
+                                             int n_heads, int n_kv, int head_dim) {
+  if (!llmk_gemm_tc_supported(A, W, M, N, K, lda, ldw)) return 0;
+  if (head_dim != 64 && head_dim != 128) return 0;
+  if (n_heads < 1 || n_kv < 0 || (long long)(n_heads + 2 * n_kv) * head_dim != N) return 0;
+  if ((uintptr_t)q_out % 16 || ldq % 8 || ldq < (long long)n_heads * head_dim) return 0;
+  if ((cos_table != nullptr) != (sin_table != nullptr) || (uintptr_t)cos_table % 16 || (uintptr_t)sin_table % 16) return 0;
+  if (n_kv && (!k_pages || !v_pages || (uintptr_t)k_pages % 16 || (uintptr_t)v_pages % 16)) return 0;
+  return 1;
+}
+
+// The QKV projection of a prompt portion with rotation and cache store in its epilogue (the pair
+// kernel): A [M, K] and W [(n_heads + 2 n_kv) * head_dim, K] bfloat16; rotated queries go to
+// q_out [M, ldq] (bfloat16), rotated keys and plain values to place slot_map[t] of the pages
+// [page][n_kv][page_size][head_dim]; positions[t] selects the row of the tables
+// [position][head_dim / 2] (null tables: no rotation).  n_kv == 0: W holds query heads only and
+// nothing is stored.  tile: columns per tile, a multiple of head_dim up to 256.
+LLMK_API int llmk_gemm_tc_qkv_rope(const void* A, const void* W, void* q_out, int M, int N, int K, long long lda,
+                                   long long ldw, long long ldq, int tile, const float* cos_table,
+                                   const float* sin_table, const int* positions, const int* slot_map, void* k_pages,
+                                   void* v_pages, int n_heads, int n_kv, int head_dim, int page_size,
+                                   cudaStream_t stream) {
+  if (M == 0) return 0;
+  LLMK_REQUIRE(llmk_gemm_tc_qkv_rope_supported(A, W, M, N, K, lda, ldw, q_out, ldq, cos_table, sin_table, k_pages, v_pages,
+                                               n_heads, n_kv, head_dim),
+               "gemm_tc_qkv_rope: needs bfloat16 rows of 16-byte multiples, a head size of 64 or 128 (got %d) and N = (%d + 2 * %d) heads",
+               head_dim, n_heads, n_kv);
+  LLMK_REQUIRE(tile >= head_dim && tile <= 256 && tile % head_dim == 0, "gemm_tc_qkv_rope: tile %d must be a multiple of the head size %d up to 256", tile, head_dim);
+  LLMK_REQUIRE(positions && (n_kv == 0 || (slot_map && page_size > 0)), "gemm_tc_qkv_rope: positions, slot map and page size are needed");
+  int rc = ensure_err_flag();
+  if (rc) return rc;
+  CUtensorMap mp, mq;
+  if ((rc = get_map(&mp, A, M, K, lda, BP))) return rc;
+  if ((rc = get_map(&mq, W, N, K, ldw, tile / 2))) return rc;
+  RopeStore rs{cos_table, sin_table, positions, slot_map, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages,
+               n_heads, n_kv, head_dim, page_size > 0 ? page_size : 1};
+  return launch_pair<__nv_bfloat16, EPI_ROPE>(mp, mq, q_out, ldq, M, N, K, tile, rs, stream);
 }
 
 // Reads and clears the error word that a kernel sets when one of its waits gave up

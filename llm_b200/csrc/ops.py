@@ -595,6 +595,61 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int) 
                                c_int(3 if PAIR_GEMM else 2), c_int(1), _stream()))
 
 
+FUSE_PROMPT_ROPE = True
+
+
+def _qkv_rope_tile(rows: int, n: int, k: int, head_dim: int) -> int:
+    """The tile width (whole heads, up to 256 columns) with the fewest rounds of pair tiles, by
+    the pair kernel's terms of plan_gemm."""
+    best = None
+    for tile in range(head_dim, 257, head_dim):
+        t_kb = max(0.31 + 0.0004 * (tile - 128), 1.43 * 256 * tile * 64 * 2 / 2 / 15.2e6)
+        cost = _ceil_div(_ceil_div(rows, 256) * _ceil_div(n, tile), _SMS // 2) * t_kb
+        if best is None or cost < best[0] - 1e-9:
+            best = (cost, tile)
+    return best[1]
+
+
+def qkv_rope_store(x: torch.Tensor, w: torch.Tensor, q_out, rows: int, cos, sin, positions: torch.Tensor,
+                   slot_map: torch.Tensor, k_pages, v_pages, n_heads: int, n_kv: int, head_dim: int):
+    """The QKV projection of a prompt portion with rotation and cache store in its epilogue:
+    x[:rows] @ w.T for w = [q heads; k heads; v heads] (n_kv of each; 0: query heads only), the
+    query and key heads rotated by the tables at positions[t], queries written to q_out() [rows,
+    n_heads * head_dim], keys and values to place slot_map[t] of the pages.  Returns the tensor
+    of the queries; or None, having done nothing, where the kernel does not apply (float32, up to
+    128 rows, whose product splits K instead, a head size other than 64 or 128): the caller then
+    runs the product and rope_kv_write."""
+    if (not FUSE_PROMPT_ROPE or not PAIR_GEMM or rows <= 128 or x.dtype != torch.bfloat16
+            or w.dtype != torch.bfloat16 or head_dim not in (64, 128)):
+        return None
+    n, k = w.shape
+    if n != (n_heads + 2 * n_kv) * head_dim:
+        return None
+    if cos is not None and (cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.shape[1] != head_dim // 2
+                            or not cos.is_contiguous() or not sin.is_contiguous()):
+        return None
+    if n_kv and not (k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == torch.bfloat16
+                     and k_pages.shape[1] == n_kv and k_pages.shape[3] == head_dim):
+        return None
+    lib = load_tensor()
+    q = q_out()
+    _rows_contig(x, "x"); _rows_contig(w, "w"); _rows_contig(q, "q_out")
+    assert q.dtype == torch.bfloat16 and positions.dtype == torch.int32 and slot_map.dtype == torch.int32
+    args = (_ptr(x), _ptr(w), c_int(rows), c_int(n), c_int(k), c_longlong(x.stride(0)), c_longlong(w.stride(0)))
+    if not lib.llmk_gemm_tc_qkv_rope_supported(*args, _ptr(q), c_longlong(q.stride(0)), _ptr(cos), _ptr(sin),
+                                               _ptr(k_pages) if n_kv else c_void_p(0),
+                                               _ptr(v_pages) if n_kv else c_void_p(0), c_int(n_heads), c_int(n_kv),
+                                               c_int(head_dim)):
+        return None
+    _check_t(lib.llmk_gemm_tc_qkv_rope(_ptr(x), _ptr(w), _ptr(q), c_int(rows), c_int(n), c_int(k),
+                                       c_longlong(x.stride(0)), c_longlong(w.stride(0)), c_longlong(q.stride(0)),
+                                       c_int(_qkv_rope_tile(rows, n, k, head_dim)), _ptr(cos), _ptr(sin),
+                                       _ptr(positions), _ptr(slot_map), _ptr(k_pages) if n_kv else c_void_p(0),
+                                       _ptr(v_pages) if n_kv else c_void_p(0), c_int(n_heads), c_int(n_kv),
+                                       c_int(head_dim), c_int(k_pages.shape[2] if n_kv else 1), _stream()))
+    return q
+
+
 def set_pdl(on: bool) -> None:
     """Programmatic dependent launch between the kernels of a step (on by default); set in both
     kernel libraries."""

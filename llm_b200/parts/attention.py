@@ -67,12 +67,20 @@ class PagedAttention(Part):
         T = ctx.n_tokens
         ws = ctx.workspace
         width = self.q_size + 2 * self.kv_size
-        qkv = linear(x, self.w_qkv, ws.get("qkv", T, width, self.dtype), T, allow_partial=FUSE_PARTIALS)
         cos = sin = None
         if self.position is not None:
             cos, sin = self.position.tables()
         k_pages, v_pages = view.k_pages, view.v_pages
         attn = ws.get("attn_out", T, self.q_size, self.dtype)
+        # many rows: one kernel projects, rotates and stores; then the attention over the pages
+        q = ops.qkv_rope_store(x, self.w_qkv, lambda: ws.get("q_rot", T, self.q_size, self.dtype), T, cos, sin,
+                               ctx.positions, view.group.slot_map, k_pages, v_pages, self.num_heads,
+                               0 if self.shares_cache else k_pages.shape[1], self.head_dim)
+        if q is not None:
+            ops.paged_attention(attn, q, k_pages, v_pages, view.group, ctx, self.num_heads, k_pages.shape[1],
+                                self.head_dim, self.window or 0, self.scale)
+            return linear(attn, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
+        qkv = linear(x, self.w_qkv, ws.get("qkv", T, width, self.dtype), T, allow_partial=FUSE_PARTIALS)
         ops.rope_store_attend(attn, qkv, cos, sin, k_pages, v_pages, view.group, ctx, self.num_heads,
                               k_pages.shape[1], self.head_dim, self.window or 0, self.scale,
                               write_kv=not self.shares_cache,

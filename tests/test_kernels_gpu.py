@@ -680,3 +680,67 @@ def test_tensor_core_attention_refuses_other_sizes(ops):
     assert not ops.attention_tc_supported(torch.bfloat16, 4, 2, 64, 8)
     assert not ops.attention_tc_supported(torch.float32, 4, 2, 64, 16)
     assert not ops.attention_tc_supported(torch.bfloat16, 256, 1, 64, 16)
+
+
+@pytest.mark.parametrize("M,NH,NKV,HS,K,page", [
+    (300, 5, 1, 64, 5 * 64 + 24, 16),     # 7 heads: the last tile is one head wide; a ragged last row tile
+    (1111, 12, 4, 64, 3 * 64, 8),         # 20 heads; several tiles per pair
+    (400, 3, 3, 128, 2 * 64 + 8, 16),     # head size 128: two 32-column pieces per half
+    (260, 6, 0, 64, 64, 16)])             # query heads only (a layer that reads another layer's pages)
+def test_qkv_projection_with_rotation_and_store_in_its_epilogue(ops, M, NH, NKV, HS, K, page):
+    """The pair kernel's QKV epilogue against product, rotation and store written out in float32:
+    positions and places are scattered, so a row that took another row's angle or page shows."""
+    torch.manual_seed(12)
+    N = (NH + 2 * NKV) * HS
+    a = torch.randn(M + 1, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    max_pos = 2 * M
+    inv = 1.0 / (10000.0 ** (torch.arange(0, HS, 2, dtype=torch.float64) / HS))
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv[None, :]
+    cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
+    g = torch.Generator().manual_seed(3)
+    pos = torch.randperm(max_pos, generator=g)[:M].to(torch.int32)
+    n_pages = -(-M // page) + 3
+    slot = torch.randperm(n_pages * page, generator=g)[:M].to(torch.int32)
+    kp = torch.full((n_pages, max(NKV, 1), page, HS), 7.0, device=DEV, dtype=torch.bfloat16)
+    vp = torch.full((n_pages, max(NKV, 1), page, HS), 7.0, device=DEV, dtype=torch.bfloat16)
+    q_buf = torch.full((M + 1, NH * HS), 3.0, device=DEV, dtype=torch.bfloat16)
+    q = ops.qkv_rope_store(a, w, lambda: q_buf, M, cos, sin, pos.to(DEV), slot.to(DEV), kp if NKV else None,
+                           vp if NKV else None, NH, NKV, HS)
+    torch.cuda.synchronize()
+    assert q is q_buf and ops.gemm_tc_take_error() == 0
+    ref = (a[:M].double() @ w.double().T).cpu()
+
+    def rotate(x):          # [M, heads, HS]
+        c, s = ang[pos.long()].cos()[:, None, :], ang[pos.long()].sin()[:, None, :]
+        x1, x2 = x[..., :HS // 2], x[..., HS // 2:]
+        return torch.cat([x1 * c - x2 * s, x1 * s + x2 * c], dim=-1)
+
+    q_ref = rotate(ref[:, :NH * HS].view(M, NH, HS)).reshape(M, NH * HS)
+    assert rel_err(q[:M], q_ref) < 1e-2
+    assert float(q_buf[M].float().min()) == 3.0 and float(q_buf[M].float().max()) == 3.0
+    if NKV:
+        k_ref = rotate(ref[:, NH * HS:(NH + NKV) * HS].view(M, NKV, HS))
+        v_ref = ref[:, (NH + NKV) * HS:].view(M, NKV, HS)
+        pg, off = (slot // page).long(), (slot % page).long()
+        assert rel_err(kp.cpu()[pg, :, off], k_ref) < 1e-2
+        assert rel_err(vp.cpu()[pg, :, off], v_ref) < 1e-2
+        untouched = torch.ones(n_pages, page, dtype=torch.bool)
+        untouched[pg, off] = False
+        assert bool((kp.cpu().float().permute(0, 2, 1, 3)[untouched] == 7.0).all())
+        assert bool((vp.cpu().float().permute(0, 2, 1, 3)[untouched] == 7.0).all())
+    # without tables nothing is rotated
+    q2 = ops.qkv_rope_store(a, w, lambda: q_buf, M, None, None, pos.to(DEV), slot.to(DEV), kp if NKV else None,
+                            vp if NKV else None, NH, NKV, HS)
+    assert rel_err(q2[:M], ref[:, :NH * HS]) < 1e-2
+
+
+def test_qkv_epilogue_is_not_offered_for_few_rows_float32_or_other_head_sizes(ops):
+    a = torch.zeros(300, 64, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(4 * 64, 64, device=DEV, dtype=torch.bfloat16)
+    pos = torch.zeros(300, dtype=torch.int32, device=DEV)
+    buf = lambda: torch.zeros(300, 4 * 64, device=DEV, dtype=torch.bfloat16)
+    assert ops.qkv_rope_store(a, w, buf, 128, None, None, pos, pos, None, None, 4, 0, 64) is None
+    assert ops.qkv_rope_store(a.float(), w.float(), buf, 300, None, None, pos, pos, None, None, 4, 0, 64) is None
+    assert ops.qkv_rope_store(a, w, buf, 300, None, None, pos, pos, None, None, 8, 0, 32) is None
+    assert ops.qkv_rope_store(a, w, buf, 300, None, None, pos, pos, None, None, 4, 0, 64) is not None
