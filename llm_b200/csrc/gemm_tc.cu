@@ -633,20 +633,32 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   if (warp == 0) {
     if (lane == 0) {
       // ---- producer (both CTAs) ----
+      // The weights do not depend on the kernel before: those of the first pass over the ring
+      // are requested before waiting for it, the activations after.
+      const int early = pair < total_tiles ? min(nkb, STAGES) : 0;
+      auto weight_row = [&](int tile) {
+        const int q_tile = (tile / m_tiles) * (SWIGLU ? 128 : tile_q);
+        return SWIGLU ? (rank ? inter + q_tile : q_tile) : q_tile + (int)rank * half_q;
+      };
+      for (int i = 0; i < early; ++i) {
+        if (rank == 0) mbar_arrive_expect_tx(&full_bar[i], stage_tx);
+        tma_load_2d_pair(smem_q + i * PAIR_Q_STAGE_BYTES, &map_q, i * BK, weight_row(pair), map_to_cta(smem_u32(&full_bar[i]), 0));
+      }
       pdl_wait();
       bool ok = true;
       int it = 0;
       for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
         const int p0 = (tile % m_tiles) * (2 * BP) + (int)rank * BP;
-        const int q_tile = (tile / m_tiles) * (SWIGLU ? 128 : tile_q);
-        const int q0 = SWIGLU ? (rank ? inter + q_tile : q_tile) : q_tile + (int)rank * half_q;
+        const int q0 = weight_row(tile);
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % STAGES;
-          ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1);
-          if (!ok) break;
-          if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], stage_tx);
           const uint32_t full0 = map_to_cta(smem_u32(&full_bar[s]), 0);
-          tma_load_2d_pair(smem_q + s * PAIR_Q_STAGE_BYTES, &map_q, kb * BK, q0, full0);
+          if (it >= early) {
+            ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1);
+            if (!ok) break;
+            if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], stage_tx);
+            tma_load_2d_pair(smem_q + s * PAIR_Q_STAGE_BYTES, &map_q, kb * BK, q0, full0);
+          }
           tma_load_2d_pair(smem_p + s * P_STAGE_BYTES, &map_p, kb * BK, p0, full0);
         }
       }

@@ -416,15 +416,6 @@ def _ceil_div(a: int, b: int) -> int:
     return -(-a // b)
 
 
-_RING_BYTES = {16: 6 * (16384 + 2048), 32: 5 * (16384 + 4096), 64: 4 * (16384 + 8192)}
-
-
-def cluster_fits(tile: int, splits: int) -> bool:
-    """Whether the splits of a tile can sum their results on chip: swapped tiles up to 64 rows,
-    at most 8 CTAs in a cluster, and the partial rows must fit the first CTA's stage ring."""
-    return tile in _RING_BYTES and 2 <= splits <= 8 and (splits - 1) * tile * 128 * 4 <= _RING_BYTES[tile]
-
-
 PERSISTENT_GEMM = True
 PAIR_GEMM = True
 
