@@ -2,8 +2,8 @@
 // accumulation in tensor memory.
 //
 // Both operands are K-major, as activations and checkpoint weights ([out, in]) already
-// are, so nothing is transposed.  One CTA computes one tile (or, in the persistent variant for
-// many rows further down, walks over tiles): a producer thread moves
+// are, so nothing is transposed.  One CTA computes one tile (or, in the persistent variants for
+// many rows further down, one CTA or a pair of CTAs walks over tiles): a producer thread moves
 // [rows x 64] boxes of both operands into a ring of 128-byte-swizzled stages with TMA,
 // one thread issues tcgen05.mma (M = 128, N = BNQ, K = 16, four per stage) and frees each
 // stage with tcgen05.commit, four warps read the accumulator back with tcgen05.ld and
@@ -75,8 +75,6 @@ constexpr int THREADS = 192;       // warp 0: TMA, warp 1: MMA + tensor memory, 
 constexpr int P_STAGE_BYTES = BP * BK * 2;
 
 __host__ __device__ constexpr int q_stage_bytes(int bnq) { return bnq * BK * 2; }
-// Narrow tiles keep the ring at six stages so that two CTAs fit on an SM: the CTAs of the next
-// product can then stage their weights while this one drains.
 // Stages of the ring.  In the swapped mode (few rows, bound by the weights' way from memory) two
 // CTAs share an SM, so that twice as many CTAs stream weights at a time: their rings are sized to
 // about 100 KB each.  In the normal mode one CTA has the SM.
@@ -1115,7 +1113,8 @@ LLMK_API int llmk_gemm_tc_qkv_rope(const void* A, const void* W, void* q_out, in
 }
 
 // Reads and clears the error word that a kernel sets when one of its waits gave up
-// (1 = producer, 2 = MMA issuer, 3 = epilogue).  Synchronises the device.
+// (1 = producer, 2 = MMA issuer, 3 = epilogue of the one-tile kernel; 4 to 6 the same of the
+// persistent kernel, 7 to 9 of the pair kernel).  Synchronises the device.
 LLMK_API int llmk_gemm_tc_take_error() {
   if (!g_err_flag) return 0;
   int v = 0;
