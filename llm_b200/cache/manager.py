@@ -55,10 +55,16 @@ _KINDS = {"full": 0, "window": 1}
 _OUT_OF_PAGES = -2
 
 
+_NAMED_KEYS = 1 << 62       # keys of ids that are not integers start here
+
+
 class CacheManager:
     """Requests by their caller's ids on top of the native page pool (csrc/host/page_pool.cpp),
-    which knows them by slot.  The pool does the bookkeeping (pages, tables, window give-back,
-    slots, invariants); this class maps ids to slots and turns its error codes into exceptions."""
+    which does the bookkeeping (pages, tables, window give-back, slots, the live requests and
+    their slots, invariants) and knows a request by a 64-bit key: an integer id is its own key,
+    any other hashable id gets one here.  This class turns the pool's error codes into
+    exceptions.  The native scheduler works on the same pool, so a request that it releases is
+    gone here too."""
 
     def __init__(self, groups: List[GroupSpec], max_requests: int, max_seq_len: int):
         if max_requests <= 0 or max_seq_len <= 0:
@@ -79,7 +85,12 @@ class CacheManager:
         self._pool = ctypes.c_void_p(self._pool)
         self.max_requests = max_requests
         self.max_seq_len = max_seq_len
-        self._slot: Dict[Hashable, int] = {}
+        lib.llmh_pool_admit.argtypes = [ctypes.c_void_p, ctypes.c_longlong]
+        lib.llmh_pool_slot.argtypes = [ctypes.c_void_p, ctypes.c_longlong]
+        self._named: Dict[Hashable, int] = {}          # ids that are not integers -> keys
+        self._names: Dict[int, Hashable] = {}
+        self._next_named = 0
+        self._keys = (ctypes.c_longlong * max_requests)()
         self._needs = (ctypes.c_int * max(n, 1))()
         self._fresh = (ctypes.c_int * max_requests)()
 
@@ -114,36 +125,58 @@ class CacheManager:
     def num_free_slots(self) -> int:
         return self._lib.llmh_pool_free_slots(self._pool)
 
+    def key(self, req: Hashable, create: bool = False):
+        """The 64-bit key under which the pool knows the request; None for an id that is not an
+        integer and has no key yet (unless create)."""
+        if isinstance(req, int) and not isinstance(req, bool):
+            if not -_NAMED_KEYS <= req < _NAMED_KEYS:
+                raise CacheError(f"request id {req} is out of range")
+            return req
+        k = self._named.get(req)
+        if k is None and create:
+            k = self._named[req] = _NAMED_KEYS + self._next_named
+            self._next_named += 1
+            self._names[k] = req
+        return k
+
+    def _slot_or_none(self, req: Hashable) -> int:
+        k = self.key(req)
+        return -1 if k is None else self._lib.llmh_pool_slot(self._pool, k)
+
     def is_live(self, req: Hashable) -> bool:
-        return req in self._slot
+        return self._slot_or_none(req) >= 0
 
     def live_requests(self):
-        return list(self._slot)
+        n = self._lib.llmh_pool_live_keys(self._pool, self._keys, self.max_requests)
+        return [self._names.get(k, k) for k in self._keys[:n]]
 
     def length(self, req: Hashable) -> int:
-        return self._lib.llmh_pool_length(self._pool, self._slot[req])
+        return self._lib.llmh_pool_length(self._pool, self.slot(req))
 
     def slot(self, req: Hashable) -> int:
-        return self._slot[req]
+        slot = self._slot_or_none(req)
+        if slot < 0:
+            raise CacheError(f"request {req!r} is not live")
+        return slot
 
     def table(self, g: int, req: Hashable) -> List[int]:
         """The request's logical pages in group g (-1 = given back)."""
         n, first = ctypes.c_int(), ctypes.c_int()
-        row = self._lib.llmh_pool_table(self._pool, g, self._slot[req], ctypes.byref(n), ctypes.byref(first))
+        row = self._lib.llmh_pool_table(self._pool, g, self.slot(req), ctypes.byref(n), ctypes.byref(first))
         return [row[i] for i in range(n.value)]
 
     def pages_needed(self, req: Optional[Hashable], n_new: int, length: Optional[int] = None) -> List[int]:
         """Per group, the pages that growing by n_new tokens takes from the free list, net of
         the window pages that the same call gives back first.  req None = a request not yet
         admitted (length 0 unless given)."""
-        slot = self._slot.get(req, -1) if req is not None else -1
+        slot = self._slot_or_none(req) if req is not None else -1
         rc = self._lib.llmh_pool_pages_needed(self._pool, slot, -1 if length is None else length, n_new, self._needs)
         if rc < 0:
             self._fail(rc)
         return list(self._needs[:len(self._specs)])
 
     def can_extend(self, req: Optional[Hashable], n_new: int) -> bool:
-        cur = self.length(req) if req in self._slot else 0
+        cur = self.length(req) if req is not None and self.is_live(req) else 0
         if cur + n_new > self.max_seq_len:
             return False
         return all(need <= self.num_free_pages(g) for g, need in enumerate(self.pages_needed(req, n_new)))
@@ -151,13 +184,26 @@ class CacheManager:
     # ---- life cycle ----
     def admit(self, req: Hashable) -> int:
         """A new request takes a state slot; returns the slot."""
-        if req in self._slot:
-            raise CacheError(f"request {req!r} is already live")
-        slot = self._lib.llmh_pool_admit(self._pool)
+        slot = self._lib.llmh_pool_admit(self._pool, self.key(req, create=True))
         if slot < 0:
             self._fail(slot)
-        self._slot[req] = slot
         return slot
+
+    def begin_step(self, reqs, counts, slots, starts) -> None:
+        """The start of a step, all or nothing: request reqs[b] (admitted here if it is new) grows
+        by counts[b] tokens; slots[b] and starts[b] receive its slot and the position of its first
+        new token.  counts, slots and starts are int32 numpy arrays.  Nothing has moved if it
+        raises: CacheError (no request slot, or max_seq_len) or OutOfPages."""
+        n = len(reqs)
+        keys = (ctypes.c_longlong * max(n, 1))(*[self.key(r, create=True) for r in reqs])
+        bad = ctypes.c_int()
+        ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+        rc = self._lib.llmh_pool_begin_step(self._pool, n, keys, ptr(counts), ptr(slots), ptr(starts), ctypes.byref(bad))
+        if rc < 0:
+            msg = self._lib.llmh_pool_error(self._pool).decode("utf-8", "replace")
+            if rc != _OUT_OF_PAGES and bad.value >= 0:
+                msg = f"request {reqs[bad.value]!r}: {msg}"
+            raise (OutOfPages if rc == _OUT_OF_PAGES else CacheError)(msg)
 
     def take_fresh_slots(self) -> List[int]:
         """Slots admitted since the last call: their state is to be zeroed."""
@@ -168,20 +214,22 @@ class CacheManager:
         """The request is about to write n_new tokens: give back window pages that are out
         of sight, take the pages that the new tokens need, and return the position of the
         first new token (the reference's KV_Pool::append, kv/KV_pool.h:40-52)."""
-        if req not in self._slot:
-            raise CacheError(f"request {req!r} is not live")
-        start = self._lib.llmh_pool_extend(self._pool, self._slot[req], n_new)
+        start = self._lib.llmh_pool_extend(self._pool, self.slot(req), n_new)
         if start < 0:
             self._fail(start)
         return start
 
     def release(self, req: Hashable) -> None:
         """The request ended: all its pages and its slot go back (kv/KV_pool.h:55-60)."""
-        if req not in self._slot:
+        slot = self._slot_or_none(req)
+        if slot < 0:
             raise CacheError(f"request {req!r} is not live (released twice?)")
-        rc = self._lib.llmh_pool_release(self._pool, self._slot.pop(req))
+        rc = self._lib.llmh_pool_release(self._pool, slot)
         if rc < 0:
             self._fail(rc)
+        k = self._named.pop(req, None) if not isinstance(req, int) or isinstance(req, bool) else None
+        if k is not None:
+            del self._names[k]
 
     def physical_slot(self, g: int, req: Hashable, pos: int) -> int:
         """page * page_size + offset of a held position (kv/KV_pool.h:76-79)."""
@@ -198,5 +246,3 @@ class CacheManager:
         rc = self._lib.llmh_pool_check(self._pool)
         if rc < 0:
             self._fail(rc)
-        if sorted(self._slot.values()) != sorted(set(self._slot.values())):
-            raise CacheError("two requests share a slot")

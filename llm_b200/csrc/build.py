@@ -28,8 +28,8 @@ GROUPS = {
     "plain": (LIB_NAME, ["runtime.cu", "rows.cu", "gemm_simt.cu", "rope_cache.cu", "attention_generic.cu",
                          "attention_decode.cu", "sampling.cu"]),
     "tensor": ("libllm_b200_tensor.so", ["runtime.cu", "gemm_tc.cu", "attention_tc.cu", "attention_decode_mma.cu"]),
-    # host side of the runtime (page pool, step metadata): plain C++, built with g++, needs no CUDA
-    "host": ("libllm_b200_host.so", ["host/page_pool.cpp"]),
+    # host side of the runtime (page pool, step metadata, scheduler): plain C++, built with g++, needs no CUDA
+    "host": ("libllm_b200_host.so", ["host/page_pool.cpp", "host/scheduler.cpp"]),
 }
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall"]
 
@@ -192,7 +192,7 @@ def _build_host(force: bool, verbose: bool) -> str:
     lib = os.path.join(bdir, name)
     stamp = os.path.join(bdir, "host.sha256")
     h = hashlib.sha256(" ".join(CXX_FLAGS).encode())
-    for f in srcs:
+    for f in sorted("host/" + n for n in os.listdir(os.path.join(_HERE, "host")) if n.endswith((".cpp", ".h"))):
         with open(os.path.join(_HERE, f), "rb") as fh:
             h.update(f.encode() + fh.read())
     digest = h.hexdigest()

@@ -11,70 +11,9 @@
 // kv/KV_Layout.h:2, and contracts are checked, not asserted.  Requests are known here by their
 // slot (the row id that the reference uses to index its tables, kv/KV_pool.h:31-37), which is
 // also the index of a request's fixed-size state.
-#include <algorithm>
-#include <cstdarg>
-#include <cstdint>
-#include <cstdio>
-#include <string>
-#include <vector>
+#include "page_pool.h"
 
-#define LLMH_API extern "C" __attribute__((visibility("default")))
-
-namespace {
-
-enum : int { KIND_FULL = 0, KIND_WINDOW = 1 };
-enum : int { ERR_CONTRACT = -1, ERR_OUT_OF_PAGES = -2 };
-
-struct Group {
-  int kind, page_size, num_pages, window, width;     // width: table entries per request
-  std::vector<int> free;                             // LIFO: back() is handed out next
-  std::vector<int> table;                            // [max_requests][width], -1 = given back / not held
-  std::vector<int> n_pages, first_live;              // per slot: logical pages in the table, first one still held
-
-  int pages_for(int length) const { return (length + page_size - 1) / page_size; }
-  // logical pages below this index can no longer be seen by a token at next_pos or later
-  int dead_before(int next_pos) const {
-    if (kind != KIND_WINDOW) return 0;
-    const int lowest_key = next_pos - window + 1;
-    return lowest_key <= 0 ? 0 : lowest_key / page_size;
-  }
-};
-
-struct Pool {
-  std::vector<Group> groups;
-  int max_requests = 0, max_seq_len = 0;
-  std::vector<int> free_slots;                       // LIFO
-  std::vector<int> len;                              // per slot; -1 = not live
-  std::vector<int> fresh;                            // admitted since the last take: state to be zeroed
-  char error[512] = "";
-
-  int fail(int code, const char* fmt, ...) {
-    va_list ap;
-    va_start(ap, fmt);
-    vsnprintf(error, sizeof(error), fmt, ap);
-    va_end(ap);
-    return code;
-  }
-  bool live(int slot) const { return slot >= 0 && slot < max_requests && len[slot] >= 0; }
-
-  // per group, the pages that growing by n_new takes from the free list, net of the window
-  // pages that the same call gives back first
-  void pages_needed(int slot, int cur, int n_new, int* out) const {
-    for (size_t g = 0; g < groups.size(); ++g) {
-      const Group& grp = groups[g];
-      const int have_hi = grp.pages_for(cur), need_hi = grp.pages_for(cur + n_new);
-      int give_back = 0;
-      if (grp.kind == KIND_WINDOW) {
-        const int first = slot >= 0 ? grp.first_live[slot] : 0;
-        const int dead = std::min(grp.dead_before(cur), have_hi);
-        give_back = std::max(0, dead - first);
-      }
-      out[g] = need_hi - have_hi - give_back;
-    }
-  }
-};
-
-}  // namespace
+using namespace llmh;
 
 LLMH_API void* llmh_pool_create(int n_groups, const int* kinds, const int* page_sizes, const int* num_pages,
                                 const int* windows, int max_requests, int max_seq_len) {
@@ -104,6 +43,7 @@ LLMH_API void* llmh_pool_create(int n_groups, const int* kinds, const int* page_
   p->free_slots.resize(max_requests);
   for (int i = 0; i < max_requests; ++i) p->free_slots[i] = max_requests - 1 - i;
   p->len.assign(max_requests, -1);
+  p->key.assign(max_requests, 0);
   return p;
 }
 
@@ -126,19 +66,20 @@ LLMH_API int llmh_pool_pages_needed(void* h, int slot, int length, int n_new, in
   return 0;
 }
 
-// A new request takes a state slot.
-LLMH_API int llmh_pool_admit(void* h) {
+// A new request, known to the caller by `key`, takes a state slot; returns the slot.
+LLMH_API int llmh_pool_admit(void* h, long long key) { return static_cast<Pool*>(h)->admit(key); }
+// The slot of a live request, or -1.
+LLMH_API int llmh_pool_slot(void* h, long long key) { return static_cast<Pool*>(h)->slot_of(key); }
+// The keys of the live requests into out (up to capacity); returns their number.
+LLMH_API int llmh_pool_live_keys(void* h, long long* out, int capacity) {
   Pool* p = static_cast<Pool*>(h);
-  if (p->free_slots.empty()) return p->fail(ERR_CONTRACT, "no request slot free (%d live)", p->max_requests);
-  const int slot = p->free_slots.back();
-  p->free_slots.pop_back();
-  p->len[slot] = 0;
-  for (Group& grp : p->groups) {
-    grp.n_pages[slot] = 0;
-    grp.first_live[slot] = 0;
-  }
-  p->fresh.push_back(slot);
-  return slot;
+  int n = 0;
+  for (int slot = 0; slot < p->max_requests; ++slot)
+    if (p->len[slot] >= 0) {
+      if (n < capacity) out[n] = p->key[slot];
+      ++n;
+    }
+  return n;
 }
 
 LLMH_API int llmh_pool_take_fresh(void* h, int* out, int capacity) {
@@ -186,18 +127,47 @@ LLMH_API int llmh_pool_extend(void* h, int slot, int n_new) {
 }
 
 // The request ended: all its pages and its slot go back.
-LLMH_API int llmh_pool_release(void* h, int slot) {
+LLMH_API int llmh_pool_release(void* h, int slot) { return static_cast<Pool*>(h)->release(slot); }
+
+// The start of a step, all or nothing: entries b = 0..B-1 are requests (by key; new ones are
+// admitted) that bring counts[b] tokens each.  First sees that every entry fits (request slots,
+// max_seq_len, pages of every group), before any page moves; then admits and extends.  slots[b]
+// and starts[b] get the request's slot and the position of its first new token.  Returns 0,
+// ERR_CONTRACT (*bad = the entry at fault, or -1) or ERR_OUT_OF_PAGES (*bad = the group).
+LLMH_API int llmh_pool_begin_step(void* h, int B, const long long* keys, const int* counts, int* slots, int* starts,
+                                  int* bad) {
   Pool* p = static_cast<Pool*>(h);
-  if (!p->live(slot)) return p->fail(ERR_CONTRACT, "slot %d is not live (released twice?)", slot);
-  for (Group& grp : p->groups) {
-    int* row = grp.table.data() + (size_t)slot * grp.width;
-    for (int i = grp.first_live[slot]; i < grp.n_pages[slot]; ++i) grp.free.push_back(row[i]);
-    std::fill(row, row + grp.n_pages[slot], -1);
-    grp.n_pages[slot] = 0;
-    grp.first_live[slot] = 0;
+  const int G = (int)p->groups.size();
+  if (G > 64) return p->fail(ERR_CONTRACT, "too many cache groups");
+  int need[64] = {0}, k[64];
+  int fresh = 0;
+  *bad = -1;
+  for (int b = 0; b < B; ++b) {
+    const int slot = p->slot_of(keys[b]);
+    const int cur = slot >= 0 ? p->len[slot] : 0;
+    fresh += slot < 0;
+    if (counts[b] <= 0 || cur + counts[b] > p->max_seq_len) {
+      *bad = b;
+      return p->fail(ERR_CONTRACT, "%d+%d tokens exceed max_seq_len %d", cur, counts[b], p->max_seq_len);
+    }
+    p->pages_needed(slot, cur, counts[b], k);
+    for (int g = 0; g < G; ++g) need[g] += k[g];
   }
-  p->free_slots.push_back(slot);
-  p->len[slot] = -1;
+  if (fresh > (int)p->free_slots.size())
+    return p->fail(ERR_CONTRACT, "%d new requests but only %d request slots free", fresh, (int)p->free_slots.size());
+  for (int g = 0; g < G; ++g)
+    if (need[g] > (int)p->groups[g].free.size()) {
+      *bad = g;
+      return p->fail(ERR_OUT_OF_PAGES, "cache group %d: the step needs %d pages, %d free", g, need[g], (int)p->groups[g].free.size());
+    }
+  for (int b = 0; b < B; ++b) {
+    int slot = p->slot_of(keys[b]);
+    if (slot < 0) slot = p->admit(keys[b]);
+    if (slot < 0) return slot;
+    slots[b] = slot;
+    starts[b] = llmh_pool_extend(h, slot, counts[b]);
+    if (starts[b] < 0) return starts[b];
+  }
   return 0;
 }
 
@@ -241,6 +211,13 @@ LLMH_API int llmh_pool_check(void* h) {
   for (int s : p->free_slots) ++slots[s];
   for (int s = 0; s < p->max_requests; ++s)
     if ((p->len[s] >= 0) + slots[s] != 1) return p->fail(ERR_CONTRACT, "a request slot is lost or shared (slot %d)", s);
+  size_t live = 0;
+  for (int s = 0; s < p->max_requests; ++s)
+    if (p->len[s] >= 0) {
+      ++live;
+      if (p->slot_of(p->key[s]) != s) return p->fail(ERR_CONTRACT, "slot %d and its request's key disagree", s);
+    }
+  if (live != p->slot_of_key.size()) return p->fail(ERR_CONTRACT, "two requests share a slot");
   return 0;
 }
 

@@ -18,7 +18,7 @@ import ctypes
 import numpy as np
 import torch
 
-from ..cache.manager import CacheManager, GroupSpec, OutOfPages
+from ..cache.manager import CacheError, CacheManager, GroupSpec, OutOfPages
 from ..cache.storage import CacheStorage, StateStorage, bytes_per_page
 from ..config.engine_options import EngineOptions
 from ..config.model_config import load_config, parse_config
@@ -293,35 +293,20 @@ class Engine:
             raise StepError(f"{n_rows} wanted rows exceed the limit {self.max_rows}")
 
         cache = self.cache
-        # All-or-nothing: see that every entry fits before any page moves.
-        new_ids = [e.request_id for e in entries if not cache.is_live(e.request_id)]
-        if len(new_ids) > cache.num_free_slots():
-            raise StepError(f"{len(new_ids)} new requests but only {cache.num_free_slots()} request slots free")
-        need = [0] * cache.num_groups
-        for e in entries:
-            live = cache.is_live(e.request_id)
-            cur = cache.length(e.request_id) if live else 0
-            if cur + len(e.tokens) > self.max_seq_len:
-                raise StepError(f"request {e.request_id!r}: {cur}+{len(e.tokens)} tokens exceed max_seq_len "
-                                f"{self.max_seq_len}")
-            for g, k in enumerate(cache.pages_needed(e.request_id if live else None, len(e.tokens))):
-                need[g] += k
-        for g in range(cache.num_groups):
-            if need[g] > cache.num_free_pages(g):
-                raise OutOfPages(f"cache group {g}: the step needs {need[g]} pages, {cache.num_free_pages(g)} free")
-
         lay = self.layout
         host_t = self._next_host_buffer()
         B = len(entries)
         ns = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=B)
         starts = np.empty(B, dtype=np.int32)
         slots = np.empty(B, dtype=np.int32)
-        for b, e in enumerate(entries):
-            rid = e.request_id
-            if not cache.is_live(rid):
-                cache.admit(rid)
-            starts[b] = cache.extend(rid, int(ns[b]))
-            slots[b] = cache.slot(rid)
+        # all or nothing: the pool sees that every entry fits before any page moves, then admits
+        # the new requests and takes the pages
+        try:
+            cache.begin_step([e.request_id for e in entries], ns, slots, starts)
+        except OutOfPages:
+            raise
+        except CacheError as err:
+            raise StepError(str(err)) from None
         T = n_tokens
         tokens = (np.asarray(token_arrays, dtype=np.int32) if T == B
                   else np.concatenate([np.atleast_1d(a) for a in token_arrays]).astype(np.int32, copy=False))

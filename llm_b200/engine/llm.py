@@ -60,9 +60,9 @@ class LLM:
         logits = self.engine.step(entries, feed_source=previous[1].device if feed_rows else None)
         temps, unis = [], []
         for e in rows:
-            r = scheduler.requests[e.request_id]
-            temps.append(r.temperature)
-            unis.append(uniform_for(r.seed, r.id, e.start + len(e.tokens)) if r.temperature > 0 else 0.0)
+            sp = scheduler.sampling_of(e.request_id)
+            temps.append(sp.temperature)
+            unis.append(uniform_for(sp.seed, e.request_id, e.start + len(e.tokens)) if sp.temperature > 0 else 0.0)
         return rows, self.sampler.sample_async(logits, temps, unis)
 
     def inference(self, scheduler: Scheduler, batch: ScheduledBatch) -> Dict[int, int]:

@@ -1,6 +1,10 @@
 """The scheduler: admits requests, cuts prompts into portions under a token budget,
 decodes, finishes and frees.
 
+The scheduler itself is native (csrc/host/scheduler.cpp, C++ behind a C interface on top of the
+native page pool, as the reference's scheduler is C++); this module is its Python face: the
+batch and request types that the entry points work with, and a class that passes calls through.
+
 Rules are those of the reference's Scheduler (runtime/Scheduler.h:81-283) with one
 change: a step is one mixed batch instead of a prefill batch or a decode batch
 (:103-108).  Decoding requests come first, one token each; what is left of
@@ -17,14 +21,13 @@ produced so far as its prompt, to be recomputed (:194,234-246).  A request whose
 prompt plus max_new_tokens can never fit is refused at add_request (:89-91).
 
 The pages themselves are taken inside Engine.step, as the reference takes them in
-Engine::prepare (runtime/Engine.h:57); the scheduler only does the arithmetic, and
-asks the cache manager for it, group by group.
+Engine::prepare (runtime/Engine.h:57); the scheduler only does the arithmetic, group by group.
 """
 from __future__ import annotations
 
-from collections import deque
+import ctypes
 from dataclasses import dataclass, field
-from typing import Deque, Dict, List, Optional
+from typing import Dict, Iterator, List, Optional
 
 from ..cache.manager import CacheManager
 
@@ -41,6 +44,8 @@ class SchedulerConfig:
 
 @dataclass
 class Request:
+    """A request as the scheduler has it at the moment of asking (a copy: it does not follow
+    the scheduler's later steps)."""
     id: int
     token_ids: List[int]
     prompt_len: int
@@ -78,6 +83,39 @@ class ScheduledBatch:
         return sum(len(e.tokens) for e in self.entries)
 
 
+@dataclass
+class _Sampling:
+    temperature: float
+    seed: int
+    ignore_eos: bool
+    max_new_tokens: int
+
+
+class _Requests:
+    """scheduler.requests: the waiting and running requests by id, read from the native side."""
+
+    def __init__(self, sched: "Scheduler"):
+        self._s = sched
+
+    def __contains__(self, rid) -> bool:
+        return rid in self._s._sampling
+
+    def __len__(self) -> int:
+        return self._s.num_requests()
+
+    def __iter__(self) -> Iterator[int]:
+        return iter(list(self._s._sampling))
+
+    def get(self, rid, default=None):
+        return self._s._request(rid) or default
+
+    def __getitem__(self, rid) -> Request:
+        r = self._s._request(rid)
+        if r is None:
+            raise KeyError(rid)
+        return r
+
+
 class Scheduler:
     def __init__(self, cache: CacheManager, cfg: SchedulerConfig):
         if cfg.max_num_seqs > cfg.max_num_batched_tokens:
@@ -85,196 +123,129 @@ class Scheduler:
         if cfg.max_num_seqs > cache.max_requests:
             raise ValueError("max_num_seqs exceeds the cache manager's request slots")
         self.cache, self.cfg = cache, cfg
-        self._next_id = 0
-        self.requests: Dict[int, Request] = {}
-        self.prefill_ready: Deque[int] = deque()
-        self.decode_ready: Deque[int] = deque()
-        self.num_preemptions = 0
+        self._lib, pool = cache.native
+        lib = self._lib
+        lib.llmh_sched_create.restype = ctypes.c_void_p
+        lib.llmh_sched_add.restype = ctypes.c_longlong
+        lib.llmh_sched_num_preemptions.restype = ctypes.c_longlong
+        lib.llmh_sched_batch.restype = ctypes.POINTER(ctypes.c_int)
+        lib.llmh_sched_finished.restype = ctypes.POINTER(ctypes.c_int)
+        lib.llmh_sched_request.restype = ctypes.POINTER(ctypes.c_int)
+        lib.llmh_sched_request.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.POINTER(ctypes.c_int),
+                                           ctypes.POINTER(ctypes.c_int)]
+        eos = cfg.eos_token_id if cfg.eos_token_id is not None else -1
+        h = lib.llmh_sched_create(pool, cfg.max_num_seqs, cfg.max_num_batched_tokens, eos)
+        if not h:
+            raise ValueError("the scheduler refused this configuration")
+        self._h = ctypes.c_void_p(h)
+        n = cfg.max_num_seqs
+        self._ids = (ctypes.c_longlong * n)()
+        self._starts = (ctypes.c_int * n)()
+        self._counts = (ctypes.c_int * n)()
+        self._samples = (ctypes.c_int * n)()
+        self._new = (ctypes.c_int * n)()
+        self._sampling: Dict[int, _Sampling] = {}      # what only the sampler needs, by request id
+        self.requests = _Requests(self)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.llmh_sched_destroy(h)
 
     # ---- admission ----
     def add_request(self, prompt: List[int], max_new_tokens: int, temperature: float = 0.0, seed: int = 0,
                     ignore_eos: bool = False) -> int:
         """Returns the request id, or -1 if the request can never run: empty prompt, longer
         than max_seq_len with its new tokens, or more pages than a whole group holds."""
-        worst = len(prompt) + max_new_tokens
-        if not prompt or max_new_tokens <= 0 or worst > self.cache.max_seq_len:
-            return -1
-        for g, need in enumerate(self.cache.pages_needed(None, worst, length=0)):
-            if need > self.cache.group_spec(g).num_pages:
-                return -1
-        rid = self._next_id
-        self._next_id += 1
-        self.requests[rid] = Request(rid, list(prompt), len(prompt), max_new_tokens, temperature, seed, ignore_eos)
-        self.prefill_ready.append(rid)
+        arr = (ctypes.c_int * max(len(prompt), 1))(*prompt)
+        rid = int(self._lib.llmh_sched_add(self._h, arr, len(prompt), int(max_new_tokens), int(ignore_eos)))
+        if rid >= 0:
+            self._sampling[rid] = _Sampling(temperature, seed, ignore_eos, int(max_new_tokens))
         return rid
 
     def num_requests(self) -> int:
-        return len(self.requests)
+        return self._lib.llmh_sched_num_requests(self._h)
+
+    @property
+    def num_preemptions(self) -> int:
+        return int(self._lib.llmh_sched_num_preemptions(self._h))
+
+    @property
+    def prefill_ready(self) -> List[int]:
+        return self._queue(0)
+
+    @property
+    def decode_ready(self) -> List[int]:
+        return self._queue(1)
+
+    def _queue(self, which: int) -> List[int]:
+        n = self._lib.llmh_sched_queue(self._h, which, self._ids, 0)
+        out = (ctypes.c_longlong * max(n, 1))()
+        self._lib.llmh_sched_queue(self._h, which, out, n)
+        return list(out[:n])
+
+    def _request(self, rid) -> Optional[Request]:
+        n, fields = ctypes.c_int(), (ctypes.c_int * 6)()
+        toks = self._lib.llmh_sched_request(self._h, int(rid), ctypes.byref(n), fields)
+        if not toks:
+            return None
+        sp = self._sampling[rid]
+        return Request(rid, toks[:n.value], fields[0], fields[1], sp.temperature, sp.seed, sp.ignore_eos,
+                       DECODE if fields[2] else PREFILL, fields[3], fields[4], bool(fields[5]))
+
+    def sampling_of(self, rid) -> _Sampling:
+        """temperature, seed and ignore_eos of a waiting or running request."""
+        return self._sampling[rid]
 
     # ---- one step's batch ----
     def schedule(self) -> ScheduledBatch:
         """The next step's batch.  If nothing can run although requests wait, prompts that
         hold pages behind the head of the queue give them back (they are recomputed later),
         which always lets the head run: admission made sure that it fits alone."""
-        batch = self._schedule_once()
-        if batch.empty() and self.requests:
-            head = self.prefill_ready[0] if self.prefill_ready else None
-            freed = False
-            for rid in reversed(self.prefill_ready):
-                if rid != head and self.cache.is_live(rid):
-                    self.cache.release(rid)
-                    self.requests[rid].cached_len = 0
-                    self.requests[rid].num_preemptions += 1
-                    self.num_preemptions += 1
-                    freed = True
-            if freed:
-                batch = self._schedule_once()
-        return batch
-
-    def _schedule_once(self) -> ScheduledBatch:
+        n_tokens = ctypes.c_int()
+        n = self._lib.llmh_sched_schedule(self._h, ctypes.byref(n_tokens))
+        toks = self._lib.llmh_sched_batch(self._h, self._ids, self._starts, self._counts, self._samples)
         batch = ScheduledBatch()
-        cache, cfg = self.cache, self.cfg
-        G = cache.num_groups
-        promised = [0] * G
-
-        def fits(needs, reserve=None) -> bool:
-            return all(cache.num_free_pages(g) - promised[g] >= needs[g] + (reserve[g] if reserve else 0)
-                       for g in range(G))
-
-        # Decoding requests first; preempt from the back while they do not all fit.
-        per_request = {}
-        while self.decode_ready:
-            needs = [0] * G
-            first = list(self.decode_ready)[:cfg.max_num_seqs]
-            for rid in first:
-                k = per_request.get(rid)
-                if k is None:
-                    k = per_request[rid] = cache.pages_needed(rid, 1)
-                for g in range(G):
-                    needs[g] += max(k[g], 0)
-            if fits(needs):
-                break
-            self._preempt_last_decode()
-        for rid in list(self.decode_ready)[:cfg.max_num_seqs]:
-            r = self.requests[rid]
-            self.decode_ready.popleft()
-            k = per_request[rid]
-            for g in range(G):
-                promised[g] += k[g]
-            batch.entries.append(ScheduledEntry(rid, r.cached_len, [r.token_ids[-1]], True))
-        budget = cfg.max_num_batched_tokens - batch.num_tokens
-
-        # Prompt portions in arrival order.
-        while self.prefill_ready and budget > 0 and len(batch.entries) < cfg.max_num_seqs:
-            rid = self.prefill_ready[0]
-            r = self.requests[rid]
-            target = len(r.token_ids)
-            chunk = min(target - r.cached_len, budget)
-            is_final = r.cached_len + chunk == target
-            live = cache.is_live(rid)
-            if not live and cache.num_free_slots() - self._new_in(batch) <= 0:
-                break
-            needs = cache.pages_needed(rid if live else None, chunk, length=r.cached_len)
-            reserve = self._decode_reserve(batch)
-            if is_final:          # this request decodes next and may start on a fresh page
-                for g in range(G):
-                    if target % cache.group_spec(g).page_size == 0:
-                        reserve[g] += 1
-            if not fits(needs, reserve):
-                break
-            for g in range(G):
-                promised[g] += needs[g]
-            batch.entries.append(ScheduledEntry(rid, r.cached_len, r.token_ids[r.cached_len:r.cached_len + chunk],
-                                                is_final))
-            budget -= chunk
-            if is_final:
-                self.prefill_ready.popleft()
-            else:
-                break        # the rest of this prompt comes in the next step; nothing may overtake it
+        at = 0
+        for i in range(n):
+            c = self._counts[i]
+            batch.entries.append(ScheduledEntry(self._ids[i], self._starts[i], toks[at:at + c], bool(self._samples[i])))
+            at += c
         return batch
 
-    def _new_in(self, batch: ScheduledBatch) -> int:
-        return sum(1 for e in batch.entries if not self.cache.is_live(e.request_id))
-
-    def _decode_reserve(self, batch: ScheduledBatch) -> List[int]:
-        """One page per request that, after this step, decodes from a page boundary."""
-        G = self.cache.num_groups
-        reserve = [0] * G
-        in_batch = {e.request_id: e for e in batch.entries}
-        for rid, r in self.requests.items():
-            e = in_batch.get(rid)
-            if e is not None:
-                after = e.start + len(e.tokens)
-                runs_on = e.samples
-            else:
-                after = r.cached_len
-                runs_on = r.phase == DECODE
-            if runs_on and after > 0:
-                for g in range(G):
-                    if after % self.cache.group_spec(g).page_size == 0:
-                        reserve[g] += 1
-        return reserve
-
-    def _preempt_last_decode(self) -> None:
-        rid = self.decode_ready.pop()
-        r = self.requests[rid]
-        if self.cache.is_live(rid):
-            self.cache.release(rid)
-        r.cached_len = 0
-        r.phase = PREFILL
-        r.num_preemptions += 1
-        self.prefill_ready.appendleft(rid)
-        self.num_preemptions += 1
+    def _pack(self, batch: ScheduledBatch) -> int:
+        n = len(batch.entries)
+        if n > len(self._ids):
+            raise ValueError("a batch of more entries than max_num_seqs")
+        for i, e in enumerate(batch.entries):
+            self._ids[i], self._starts[i], self._counts[i], self._samples[i] = e.request_id, e.start, len(e.tokens), e.samples
+        return n
 
     # ---- after the step ----
     def update(self, batch: ScheduledBatch, new_tokens: Dict[int, int]) -> List[Request]:
         """Account for a finished step.  new_tokens maps the id of every entry that samples
         to its next token.  Returns the requests that finished; their pages are free again."""
+        n = self._pack(batch)
+        for i, e in enumerate(batch.entries):
+            self._new[i] = int(new_tokens[e.request_id]) if e.samples and e.request_id in new_tokens else 0
+        k = self._lib.llmh_sched_update(self._h, n, self._ids, self._starts, self._counts, self._samples, self._new)
         done = []
-        for e in batch.entries:
-            r = self.requests.get(e.request_id)
-            if r is None:
-                continue
-            r.cached_len = e.start + len(e.tokens)
-            if not e.samples:
-                continue
-            if r.ended:                      # ran one step too far: that step's token is dropped
-                self._retire(r, done)
-                continue
-            tok = int(new_tokens[e.request_id])
-            r.token_ids.append(tok)
-            if tok != PENDING_TOKEN and self._finished(r, tok):
-                self._retire(r, done)
-            else:
-                r.phase = DECODE
-                self.decode_ready.append(r.id)
+        rid, plen, nt, npre = ctypes.c_longlong(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        for i in range(k):
+            toks = self._lib.llmh_sched_finished(self._h, i, ctypes.byref(rid), ctypes.byref(plen), ctypes.byref(nt),
+                                                 ctypes.byref(npre))
+            sp = self._sampling.pop(rid.value)
+            done.append(Request(rid.value, toks[:nt.value], plen.value, sp.max_new_tokens, sp.temperature, sp.seed,
+                                sp.ignore_eos, DECODE, nt.value, npre.value, True))
         return done
-
-    def _retire(self, r: Request, done: List[Request]) -> None:
-        if self.cache.is_live(r.id):
-            self.cache.release(r.id)
-        del self.requests[r.id]
-        done.append(r)
 
     # ---- one step of lookahead: the next step is launched before this step's tokens are read ----
     def can_look_ahead(self, batch: ScheduledBatch) -> bool:
         """Whether the step after `batch` can be scheduled before the tokens of `batch` are
         known: only decoding requests, nobody waiting to be admitted, nobody at its last token,
         and pages for one more token of each without preempting anyone."""
-        if self.prefill_ready or not batch.entries:
-            return False
-        need = [0] * self.cache.num_groups
-        for e in batch.entries:
-            r = self.requests.get(e.request_id)
-            if r is None or not e.samples or r.ended:
-                return False
-            if len(r.token_ids) - r.prompt_len + 2 > r.max_new_tokens:     # this step's token would be its last
-                return False
-            if self.cache.length(r.id) + 1 > self.cache.max_seq_len:
-                return False
-            for g, k in enumerate(self.cache.pages_needed(r.id, 1)):
-                need[g] += max(k, 0)
-        return all(need[g] <= self.cache.num_free_pages(g) for g in range(self.cache.num_groups))
+        n = self._pack(batch)
+        return bool(self._lib.llmh_sched_can_look_ahead(self._h, n, self._ids, self._samples))
 
     def update_pending(self, batch: ScheduledBatch) -> None:
         """update() for a step whose tokens are not known yet: every request gets a placeholder
@@ -286,22 +257,8 @@ class Scheduler:
         """The tokens of a step that was accounted with update_pending() have arrived.  A request
         that ends with its token is marked: it is already part of the step in flight and retires
         when that step is accounted."""
-        eos = self.cfg.eos_token_id
-        for e in batch.entries:
-            r = self.requests.get(e.request_id)
-            if r is None:
-                continue
-            tok = int(new_tokens[e.request_id])
-            at = len(r.token_ids) - 1
-            while at >= r.prompt_len and r.token_ids[at] != PENDING_TOKEN:
-                at -= 1
-            assert at >= r.prompt_len, "no pending token to resolve"
-            r.token_ids[at] = tok
-            if eos is not None and eos >= 0 and tok == eos and not r.ignore_eos:
-                del r.token_ids[at + 1:]
-                r.ended = True
-
-    def _finished(self, r: Request, tok: int) -> bool:
-        eos = self.cfg.eos_token_id
-        hit_eos = eos is not None and eos >= 0 and tok == eos and not r.ignore_eos
-        return hit_eos or len(r.token_ids) - r.prompt_len >= r.max_new_tokens
+        n = self._pack(batch)
+        for i, e in enumerate(batch.entries):
+            self._new[i] = int(new_tokens[e.request_id])
+        rc = self._lib.llmh_sched_resolve(self._h, n, self._ids, self._new)
+        assert rc == 0, "no pending token to resolve"

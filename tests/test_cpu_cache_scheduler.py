@@ -269,3 +269,24 @@ def test_lookahead_placeholders_resolve_and_late_end():
     run_step(s, c, b4, token=8)
     b5 = s.schedule()                                         # generated 5 of 6: this step's token is the last
     assert not s.can_look_ahead(b5)
+
+
+def test_request_ids_are_integers_or_names_and_the_scheduler_shares_the_pool():
+    """The pool knows requests by a 64-bit key: integers are their own key, other ids get one.
+    What the native scheduler releases is gone for the cache manager too."""
+    c = full_pool(pages=8)
+    c.admit("a"); c.admit(7); c.admit(("x", 1))
+    c.extend("a", 3); c.extend(7, 20); c.extend(("x", 1), 1)
+    assert sorted(map(str, c.live_requests())) == sorted(["a", "7", "('x', 1)"])
+    assert c.length(7) == 20 and c.slot("a") != c.slot(7) and not c.is_live("b") and not c.is_live(8)
+    with pytest.raises(CacheError):
+        c.admit(7)
+    c.release("a"); c.release(7); c.release(("x", 1))
+    c.admit("a")                                          # a name may come back
+    c.release("a")
+    c.check()
+    s = Scheduler(c, SchedulerConfig(4, 64))
+    rid = s.add_request([1, 2, 3], 1)
+    run_step(s, c, s.schedule())                          # finishes with its first token
+    assert not c.is_live(rid) and c.num_free_slots() == 4 and rid not in s.requests
+    c.check()

@@ -145,3 +145,26 @@ def test_recurring_prompt_shapes_replayed_from_graphs_match_plain(models, name, 
     if len(lt) >= 4 * 16 and len(st) > 4:
         assert eng.counters["graph_replays"] > before
     eng.cache.check()
+
+
+def test_a_step_that_cannot_run_is_refused_whole(models):
+    """Too many new requests, a request past max_seq_len, too few pages: the step is refused
+    before any page or slot moves, and the engine goes on as if it had not been asked."""
+    from llm_b200.cache import OutOfPages
+    from llm_b200.engine.engine import StepEntry, StepError
+    d, cfg, page, reqs, ref = models("A", "float32")
+    eng = make_engine(d, "float32", page, num_blocks=4, max_seqs=2)
+    toks = reqs["r2"]                                           # 33 tokens: three pages of 16
+    first = eng.step([StepEntry("x", toks[:20], [19])]).double().cpu().clone()
+    free = eng.cache.num_free_pages(0)
+    with pytest.raises(OutOfPages):                             # "y" needs 3 pages, 2 are free; "x" would have fitted
+        eng.step([StepEntry("x", toks[20:22], [1]), StepEntry("y", toks, [0])])
+    with pytest.raises(StepError):                              # a third request: only two slots
+        eng.step([StepEntry("x", toks[20:22], []), StepEntry("y", [1], []), StepEntry("z", [2], [])])
+    with pytest.raises(StepError):                              # past the longest sequence the engine holds
+        eng.step([StepEntry("x", [1] * (eng.max_seq_len - 19), [])])
+    eng.cache.check()
+    assert eng.cache.num_free_pages(0) == free and eng.cache.length("x") == 20 and not eng.cache.is_live("y")
+    rest = eng.step([StepEntry("x", toks[20:], list(range(13)))]).double().cpu()
+    got = torch.cat([first, rest])
+    assert max_err(got, ref["r2"][19:]) < TOL["float32"]
