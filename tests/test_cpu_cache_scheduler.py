@@ -290,3 +290,57 @@ def test_request_ids_are_integers_or_names_and_the_scheduler_shares_the_pool():
     run_step(s, c, s.schedule())                          # finishes with its first token
     assert not c.is_live(rid) and c.num_free_slots() == 4 and rid not in s.requests
     c.check()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_load_with_lookahead_keeps_tokens_and_pages_straight(seed):
+    """Random requests, steps accounted ahead of their tokens whenever the scheduler allows it:
+    every request finishes with exactly the tokens it was given, in order, no placeholder is
+    left, a request that met its end stops there, and every page and slot comes back."""
+    from llm_b200.engine.scheduler import PENDING_TOKEN
+    rng = random.Random(100 + seed)
+    page = rng.choice([4, 8, 16])
+    groups = [GroupSpec("full", page, rng.randint(10, 30))] + ([GroupSpec("window", page, 12, window=20)] if seed % 2 else [])
+    c = CacheManager(groups, 4, 200)
+    s = Scheduler(c, SchedulerConfig(4, 32, eos_token_id=3))
+    limit, given = {}, {}
+    for _ in range(10):
+        n, m = rng.randint(1, 60), rng.randint(1, 25)
+        rid = s.add_request([rng.randint(4, 90) for _ in range(n)], m)
+        if rid >= 0:
+            limit[rid], given[rid] = m, []
+    done, pending = {}, None
+    for _ in range(5000):
+        if not s.num_requests():
+            break
+        b = s.schedule()
+        assert not b.empty() and b.num_tokens <= 32 and len(b.entries) <= 4
+        for e in b.entries:
+            if not c.is_live(e.request_id):
+                c.admit(e.request_id)
+            assert c.extend(e.request_id, len(e.tokens)) == e.start
+        c.check()
+        toks = {e.request_id: rng.choice([3, 5, 6, 7, 8, 9, 10, 11, 12]) for e in b.entries if e.samples}
+        if pending is not None:                           # the step before: its tokens arrive now
+            s.resolve(*pending)
+            pending = None
+        if all(len(e.tokens) == 1 for e in b.entries) and s.can_look_ahead(b) and rng.random() < 0.8:
+            s.update_pending(b)
+            pending = (b, toks)
+            for rid, t in toks.items():
+                given[rid].append(t)
+        else:
+            for rid, t in toks.items():
+                given[rid].append(t)
+            for r in s.update(b, toks):
+                done[r.id] = r
+    assert pending is None and set(done) == set(limit)
+    for rid, r in done.items():
+        gen = r.generated
+        assert PENDING_TOKEN not in gen and 1 <= len(gen) <= limit[rid]
+        assert gen == given[rid][:len(gen)]               # what ran one step too far was dropped
+        assert gen[-1] == 3 or len(gen) == limit[rid]
+        assert 3 not in gen[:-1]
+    assert all(c.num_free_pages(g) == c.group_spec(g).num_pages for g in range(c.num_groups))
+    assert c.num_free_slots() == 4
+    c.check()
