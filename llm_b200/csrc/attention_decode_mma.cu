@@ -22,18 +22,27 @@ int launch_decode_mma(void* out, long long out_stride, const void* q, long long 
   const int recv_bytes = (splits - 1) * group_rows * head_dim * 4;
   const bool cluster = splits >= 2 && splits <= 8 && (long long)splits * n_kv * n_entries <= 2 * 148 &&
                        recv_bytes <= RECV_LIMIT;
-  // per warp a few stages (one in a cluster; three at head size 64, else two) of a tile of keys
-  // and a tile of values: NST in the kernel
-  const int stage_bytes = 4 * (cluster ? 1 : head_dim == 64 ? 3 : 2) * 2 * decode_mma::TILE * head_dim * 2;
+  // Without a cluster: deep stages (three at head size 64, else two) while the whole grid fits on
+  // the SMs at once with them (two CTAs per SM at head size 64, one at 128); else the variant
+  // with one stage, which at head size 64 is also held to 128 registers so that four CTAs share
+  // an SM and the grid still runs as one wave where it can (128 requests x 4 kv heads at 640
+  // keys: 22.9 us against 28.0 us).
+  const long long ctas = (long long)splits * n_kv * n_entries;
+  const bool light = !cluster && ctas > (head_dim == 64 ? 2 : 1) * 148;
+  // per warp its stages of a tile of keys and a tile of values: NST in the kernel
+  const int stage_bytes = 4 * ((cluster || light) ? 1 : head_dim == 64 ? 3 : 2) * 2 * decode_mma::TILE * head_dim * 2;
   using Kernel = decltype(&decode_mma::decode_attention_mma_kernel<64, false, FUSED>);
   const Kernel kern = head_dim == 64
-      ? (cluster ? decode_mma::decode_attention_mma_kernel<64, true, FUSED> : decode_mma::decode_attention_mma_kernel<64, false, FUSED>)
-      : (cluster ? decode_mma::decode_attention_mma_kernel<128, true, FUSED> : decode_mma::decode_attention_mma_kernel<128, false, FUSED>);
-  static bool configured[2][2] = {{false, false}, {false, false}};
-  if (!configured[head_dim == 128][cluster]) {
+      ? (cluster ? decode_mma::decode_attention_mma_kernel<64, true, FUSED>
+                 : light ? decode_mma::decode_attention_mma_kernel<64, false, FUSED, true> : decode_mma::decode_attention_mma_kernel<64, false, FUSED>)
+      : (cluster ? decode_mma::decode_attention_mma_kernel<128, true, FUSED>
+                 : light ? decode_mma::decode_attention_mma_kernel<128, false, FUSED, true> : decode_mma::decode_attention_mma_kernel<128, false, FUSED>);
+  static bool configured[2][3] = {{false, false, false}, {false, false, false}};
+  const int variant = cluster ? 1 : light ? 2 : 0;
+  if (!configured[head_dim == 128][variant]) {
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, stage_bytes + (cluster ? RECV_LIMIT : 0));
     if (err != cudaSuccess) return llmk_fail((int)err, "attention_decode: cannot set the shared memory size: %s", cudaGetErrorString(err));
-    configured[head_dim == 128][cluster] = true;
+    configured[head_dim == 128][variant] = true;
   }
   if (cluster) {
     cudaLaunchConfig_t cfg = {};

@@ -104,8 +104,8 @@ struct FusedQkv {
   int write_kv;
 };
 
-template <int HS, bool CLUSTER, bool FUSED>
-__global__ void __launch_bounds__(THREADS)
+template <int HS, bool CLUSTER, bool FUSED, bool LIGHT = false>
+__global__ void __launch_bounds__(THREADS, (LIGHT && HS == 64) ? 4 : 1)
 decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_stride, float* __restrict__ scratch,
                             const __nv_bfloat16* __restrict__ q, long long q_stride,
                             __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
@@ -117,10 +117,13 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
   constexpr int CH = HS / 8;                   // 16-byte chunks of a row
   constexpr int V_BYTES = TILE * HS * 2;       // one tile of keys, or of values
   // Stages of (keys, values) per warp.  Several let the next tiles fly while one is computed,
-  // which pays for long ranges (three where two CTAs then still fit on an SM).  A cluster is only formed for short ranges on a small grid; there one
-  // stage keeps the CTA small enough to become resident beside the CTAs of the kernel before it,
-  // which is what lets its early requests overlap that kernel.
-  constexpr int NST = CLUSTER ? 1 : (HS == 64 ? 3 : 2);
+  // which pays for long ranges (three where two CTAs then still fit on an SM).  A cluster is only
+  // formed for short ranges on a small grid; there one stage keeps the CTA small enough to become
+  // resident beside the CTAs of the kernel before it, which is what lets its early requests
+  // overlap that kernel.  LIGHT: one stage without a cluster, for grids of more CTAs than fit on
+  // the SMs at once with deep stages: more CTAs per SM then keep as many bytes in flight, and
+  // the grid runs as one wave instead of two.
+  constexpr int NST = (CLUSTER || LIGHT) ? 1 : (HS == 64 ? 3 : 2);
   constexpr int WARP_BYTES = NST * 2 * V_BYTES;
   constexpr int RANGES = CLUSTER ? 8 : 64;     // most ranges that a merge in shared memory takes
   static_assert(4 * WARP_BYTES >= 4 * ROWS * HS * 4, "the warps' results are merged in the stage buffers");
