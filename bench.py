@@ -112,6 +112,106 @@ def prefill_flops(cfg, layers, tokens, head_rows=1):
     return 2.0 * body * tokens + 2.0 * head * head_rows + attn
 
 
+def reference_arm(args, warmup: int) -> int:
+    """The same measurements on the unmodified reference: its tree compiled with nvcc (it has no
+    Python package to install) and driven through Scheduler -> PipelineDriver -> LLM::inference by
+    baseline/ref_harness.cu, on the same seeded random checkpoint.  Nothing of llm_b200's engine or
+    kernels runs in that process."""
+    import shutil
+    import tempfile
+
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as ref
+
+    def unavailable(why: str) -> int:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+
+    if args.layers != FULL_LAYERS or args.batch > 64:
+        return unavailable(f"the reference arm runs the full model at batch <= 64 (asked: {args.layers} layers, batch {args.batch})")
+    peaks = load_peaks()
+    folder = tempfile.mkdtemp(prefix="llm_b200_ref_")
+    try:
+        try:
+            ref.build_harness()
+            t0 = time.time()
+            weights = ref.write_weights(folder, FULL_LAYERS, seed=20240531)
+            write_s = time.time() - t0
+        except ref.ReferenceUnavailable as e:
+            return unavailable(str(e))
+        out = {"metric": "decode tok/s at batch 8 (TinyLlama 1.1B shape, bf16, random weights)", "unit": "tok/s",
+               "n_gpus": 1, "steps": args.steps, "warmup": warmup, "higher_is_better": True, "scaling": "weak",
+               "vs_baseline": None, "dtype": "bf16", "data": "synthetic: seeded random weights and token ids",
+               "impl": "reference"}
+        points, extra = {}, {}
+        # the reference's own sizes (model/llm/tiny_llama.cpp:19): 8 sequences, 512 tokens per step.
+        # Its driver keeps two batches in flight, so requests whose prompts ended in different
+        # steps decode as two alternating groups (each reading every weight for part of the batch).
+        with ref.Harness(weights, max_seqs=max(8, args.batch), max_tokens=512, max_seq_len=2048) as h:
+            sampler = ClockSampler()
+            sampler.start()
+            stock = h.command(f"decode {args.batch} {PROMPT_LEN} {warmup} {args.steps}")
+            clocks = sampler.stop()
+            if "ms_per_step" not in stock:
+                return unavailable("the reference's decode run failed: " + json.dumps(stock)[:200])
+            load_s = h.ready.get("load_s")
+            if not args.no_points:
+                b1 = h.command(f"decode 1 {PROMPT_LEN} {warmup} {min(args.steps, 128)}")
+                points["decode_b1"] = round(b1["tok_s_device"], 1) if "tok_s_device" in b1 else b1
+                extra["reference_load"] = h.command("load 32 128 128")
+        head, mode = stock, "stock sizes (8 sequences, 512 tokens a step): two alternating groups in flight"
+        # the same code with larger constructor arguments: every prompt of the batch in ONE step, so
+        # that the batch decodes whole (and is waited for each step); batch 64; a 2,048-token step
+        big_tokens = max(PREFILL_TOKENS, args.batch * PROMPT_LEN)
+        with ref.Harness(weights, max_seqs=64, max_tokens=big_tokens, max_seq_len=2 * PREFILL_TOKENS) as h:
+            whole = h.command(f"decode {args.batch} {PROMPT_LEN} {warmup} {args.steps}")
+            points["decode_whole_batch"] = {k: whole.get(k) for k in ("tok_s_device", "tok_s_e2e", "ms_per_step", "batches_per_step")}
+            points["decode_two_groups"] = {k: stock.get(k) for k in ("tok_s_device", "tok_s_e2e", "ms_per_step", "batches_per_step")}
+            if whole.get("tok_s_e2e", 0) > stock["tok_s_e2e"]:
+                head, mode = whole, f"all prompts in one step ({big_tokens} tokens a step): the batch decodes whole"
+            if not args.no_points:
+                b64 = h.command(f"decode 64 {PROMPT_LEN} {warmup} {min(args.steps, 128)}")
+                points["decode_b64"] = round(b64["tok_s_device"], 1) if "tok_s_device" in b64 else b64
+                pf = h.command(f"prefill {PREFILL_TOKENS} 2 5")
+                if "ms" in pf:
+                    fl = prefill_flops(MODEL, FULL_LAYERS, PREFILL_TOKENS, head_rows=PREFILL_TOKENS)
+                    out["prefill"] = {"value": round(pf["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(pf["ms"], 3),
+                                      "frac": round(fl / (pf["ms"] / 1e3) / (peaks["bf16_tflops"] * 1e12), 4),
+                                      "peak_tflops": peaks["bf16_tflops"], "peak_source": peaks["source"],
+                                      "note": "LM head on all rows, as the reference runs it"}
+                else:
+                    out["prefill"] = pf
+        ms = head["ms_per_step"]
+        mean_ctx = (head["ctx_min"] + head["ctx_max"]) / 2.0 - args.steps / 2.0
+        step_bytes = decode_bytes(MODEL, FULL_LAYERS, args.batch, args.batch * mean_ctx)
+        achieved = step_bytes / (ms / 1e3) / 1e9
+        out.update({"value": round(args.batch / (ms / 1e3), 1), "ms_per_step": round(ms, 4),
+                    "ms_per_step_with_gaps": round(head["ms_per_step_span"], 4), "clocks": clocks,
+                    "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                 "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
+                                 "bytes_per_step": int(step_bytes)},
+                    "e2e": {"value": round(head["tok_s_e2e"], 1), "unit": "tok/s",
+                            "h2d_bytes_per_step": head["h2d_bytes_per_step"], "d2h_bytes_per_step": head["d2h_bytes_per_step"],
+                            "decode_steps": args.steps},
+                    "points": points})
+        out.update(extra)
+        out["config"] = {"model": "TinyLlama-1.1B shape", "layers": FULL_LAYERS, "layers_full": FULL_LAYERS,
+                         "hidden": MODEL["hidden_size"], "heads": MODEL["num_attention_heads"],
+                         "kv_heads": MODEL["num_key_value_heads"], "head_dim": MODEL["head_dim"],
+                         "intermediate": MODEL["intermediate_size"], "vocab": MODEL["vocab_size"],
+                         "global_batch": args.batch, "prompt_len": PROMPT_LEN, "new_tokens": args.steps,
+                         "seq_len": MODEL["max_position_embeddings"], "kv_block": 16, "parallelism": "none (1 GPU)",
+                         "l2": "inputs larger than L2 (2.2 GB of weights per step)", "cuda_graphs": True,
+                         "load_s": load_s, "reference_mode": mode}
+        out["build"] = "nvcc -O3 -std=c++17 sm_100a on a verbatim copy of the reference (baseline/_ref)"
+        out["ctx_at_end"] = [head["ctx_min"], head["ctx_max"]]
+        out["checkpoint_write_s"] = round(write_s, 1)
+        print(json.dumps(out))
+        return 0
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -125,15 +225,12 @@ def main() -> int:
                     help="decode / prefill: only that measurement, for small profiling runs (not the benchmark line)")
     args = ap.parse_args()
 
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference",
-                          "unavailable": "zhan-wei-919/llm is a header-only C++/CUDA tree without setup.py or "
-                                         "pyproject.toml: pip cannot install it into baseline/_ref"}))
-        return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return reference_arm(args, warmup)
 
     import numpy as np
     import torch
