@@ -4,8 +4,12 @@ Whole sequences, no cache, one function per part, float64 on the CPU.  It shares
 no code with the engine: everything here is written from the formulas of the
 reference project (zhan-wei-919/llm), cited by file:line next to each function.
 The reference's own model code is CUDA-only and its attention kernel is locked to
-one shape, so it cannot be imported or run on a CPU; this file therefore rests on
-the formulas alone.
+one shape, so it cannot be imported or run on a CPU.  Two things pin this file to
+it all the same: tests/test_cpu_golden.py compares the functions here with outputs
+of the plain C++ loops that the reference ships inside its kernel tests
+(tests/golden/, made by tests/golden/make_golden.py), and on a GPU
+tests/test_reference_parity_gpu.py compares forward() with the logits of the
+reference's own model at the one shape it runs.
 """
 from __future__ import annotations
 
