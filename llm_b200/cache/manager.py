@@ -210,6 +210,21 @@ class CacheManager:
         n = self._lib.llmh_pool_take_fresh(self._pool, self._fresh, self.max_requests)
         return list(self._fresh[:n])
 
+    def log_freed_pages(self, on: bool = True) -> None:
+        """Debug aid: remember every page that goes back to a free list until take_freed_pages
+        collects it."""
+        self._lib.llmh_pool_log_freed(self._pool, int(on))
+
+    def take_freed_pages(self, g: int) -> List[int]:
+        """Pages of group g that were given back since the last call (after log_freed_pages)."""
+        out: List[int] = []
+        buf = (ctypes.c_int * 256)()
+        while True:
+            n = self._lib.llmh_pool_take_freed(self._pool, g, buf, 256)
+            out.extend(buf[:n])
+            if n < 256:
+                return out
+
     def extend(self, req: Hashable, n_new: int) -> int:
         """The request is about to write n_new tokens: give back window pages that are out
         of sight, take the pages that the new tokens need, and return the position of the

@@ -33,6 +33,9 @@ def bytes_per_page(instances: List[CacheInstance], group: int, page_size: int, d
                for i in instances if i.group == group)
 
 
+POISON = 1e30
+
+
 class CacheStorage:
     def __init__(self, instances: List[CacheInstance], pages_per_group: List[int], page_size: int,
                  dtype: torch.dtype, device: torch.device):
@@ -49,6 +52,20 @@ class CacheStorage:
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.k + self.v)
+
+    def poison(self, group: int, pages: List[int]) -> None:
+        """Debug aid: fill these pages of every instance of the group with POISON, so that a kernel
+        that reads a key or value its request no longer (or not yet) holds gives logits that are far
+        off instead of nearly right.  The value is huge but finite, not NaN: a kernel may load a
+        whole tile and give the keys beyond a request's length weight zero, which is sound for any
+        finite leftover."""
+        if not pages:
+            return
+        idx = torch.tensor(sorted(set(pages)), dtype=torch.long, device=self.k[0].device if self.k else None)
+        for inst, k, v in zip(self.instances, self.k, self.v):
+            if inst.group == group:
+                k.index_fill_(0, idx, POISON)
+                v.index_fill_(0, idx, POISON)
 
 
 class StateStorage:

@@ -26,6 +26,7 @@ class EngineOptions:
     max_logit_rows: Optional[int] = None       # most rows of logits one step returns
     use_cuda_graphs: bool = True
     device: str = "cuda:0"
+    poison_freed_pages: bool = False           # debug: pages that go back to the pool are overwritten with a huge value
 
     def validate(self) -> None:
         if self.dtype not in DTYPES:

@@ -533,11 +533,8 @@ LLMK_API int llmk_attention_tc(void* out, long long out_stride, const void* q, l
                "attention_tc: needs head_dim 64 or 128, page_size 16/32/64/128 and at most %d query heads per kv head "
                "(got heads %d/%d, head_dim %d, page_size %d)", ROWS, n_heads, n_kv, head_dim, page_size);
   LLMK_REQUIRE(out_stride % 8 == 0 && (uintptr_t)out % 16 == 0, "attention_tc: out must have 16-byte aligned rows");
-  if (!g_attn_err) {
-    cudaError_t e = cudaMalloc(&g_attn_err, sizeof(int));
-    if (e != cudaSuccess) return llmk_fail((int)e, "attention_tc: cannot allocate the error word");
-    cudaMemset(g_attn_err, 0, sizeof(int));
-  }
+  g_attn_err = llmk_error_word(2);
+  LLMK_REQUIRE(g_attn_err != nullptr, "attention_tc: cannot allocate the error word");
   const int group = n_heads / n_kv, tq = ROWS / group;
   const int max_tiles = (n_tokens + tq - 1) / tq + n_entries;
   CUtensorMap mq, mk, mv;
@@ -555,6 +552,7 @@ LLMK_API int llmk_attention_tc(void* out, long long out_stride, const void* q, l
 
 // The code the attention kernel left when one of its bounded waits gave up (0 = none).
 LLMK_API int llmk_attention_tc_take_error() {
+  g_attn_err = llmk_error_word(2);
   if (!g_attn_err) return 0;
   int v = 0;
   cudaMemcpy(&v, g_attn_err, sizeof(int), cudaMemcpyDeviceToHost);

@@ -853,13 +853,11 @@ int get_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, ui
   return 0;
 }
 
-int* g_err_flag = nullptr;      // device word; one per process
+int* g_err_flag = nullptr;      // the device word of this call: the caller's block or the library's own
 
 int ensure_err_flag() {
-  if (g_err_flag) return 0;
-  cudaError_t e = cudaMalloc(&g_err_flag, sizeof(int));
-  if (e != cudaSuccess) return llmk_fail((int)e, "gemm_tc: cannot allocate the error word");
-  cudaMemset(g_err_flag, 0, sizeof(int));
+  g_err_flag = llmk_error_word(1);
+  if (!g_err_flag) return llmk_fail(-1, "gemm_tc: cannot allocate the error word");
   return 0;
 }
 
@@ -1116,7 +1114,7 @@ LLMK_API int llmk_gemm_tc_qkv_rope(const void* A, const void* W, void* q_out, in
 // (1 = producer, 2 = MMA issuer, 3 = epilogue of the one-tile kernel; 4 to 6 the same of the
 // persistent kernel, 7 to 9 of the pair kernel).  Synchronises the device.
 LLMK_API int llmk_gemm_tc_take_error() {
-  if (!g_err_flag) return 0;
+  if (ensure_err_flag()) return 0;
   int v = 0;
   cudaMemcpy(&v, g_err_flag, sizeof(int), cudaMemcpyDeviceToHost);
   if (v) cudaMemset(g_err_flag, 0, sizeof(int));

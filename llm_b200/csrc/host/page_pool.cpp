@@ -44,6 +44,7 @@ LLMH_API void* llmh_pool_create(int n_groups, const int* kinds, const int* page_
   for (int i = 0; i < max_requests; ++i) p->free_slots[i] = max_requests - 1 - i;
   p->len.assign(max_requests, -1);
   p->key.assign(max_requests, 0);
+  p->freed.resize(n_groups);
   return p;
 }
 
@@ -105,16 +106,9 @@ LLMH_API int llmh_pool_extend(void* h, int slot, int n_new) {
   for (size_t g = 0; g < p->groups.size(); ++g)
     if (needs[g] > (int)p->groups[g].free.size())
       return p->fail(ERR_OUT_OF_PAGES, "group %d: slot %d needs %d pages, %d free", (int)g, slot, needs[g], (int)p->groups[g].free.size());
+  p->give_back_window(slot, cur);
   for (Group& grp : p->groups) {
     int* row = grp.table.data() + (size_t)slot * grp.width;
-    if (grp.kind == KIND_WINDOW) {
-      const int dead = std::min(grp.dead_before(cur), grp.n_pages[slot]);
-      for (int i = grp.first_live[slot]; i < dead; ++i) {
-        grp.free.push_back(row[i]);
-        row[i] = -1;
-      }
-      grp.first_live[slot] = std::max(grp.first_live[slot], dead);
-    }
     const int want = grp.pages_for(cur + n_new);
     for (int i = grp.n_pages[slot]; i < want; ++i) {
       row[i] = grp.free.back();
@@ -131,7 +125,10 @@ LLMH_API int llmh_pool_release(void* h, int slot) { return static_cast<Pool*>(h)
 
 // The start of a step, all or nothing: entries b = 0..B-1 are requests (by key; new ones are
 // admitted) that bring counts[b] tokens each.  First sees that every entry fits (request slots,
-// max_seq_len, pages of every group), before any page moves; then admits and extends.  slots[b]
+// max_seq_len, pages of every group), before any page moves; then every entry gives back the
+// window pages that are out of its sight, and only then the entries are admitted and take their
+// pages in order, so that an entry ahead of one that frees pages can already use them (the sum
+// that was checked counts them).  slots[b]
 // and starts[b] get the request's slot and the position of its first new token.  Returns 0,
 // ERR_CONTRACT (*bad = the entry at fault, or -1) or ERR_OUT_OF_PAGES (*bad = the group).
 LLMH_API int llmh_pool_begin_step(void* h, int B, const long long* keys, const int* counts, int* slots, int* starts,
@@ -161,6 +158,10 @@ LLMH_API int llmh_pool_begin_step(void* h, int B, const long long* keys, const i
       return p->fail(ERR_OUT_OF_PAGES, "cache group %d: the step needs %d pages, %d free", g, need[g], (int)p->groups[g].free.size());
     }
   for (int b = 0; b < B; ++b) {
+    const int slot = p->slot_of(keys[b]);
+    if (slot >= 0) p->give_back_window(slot, p->len[slot]);
+  }
+  for (int b = 0; b < B; ++b) {
     int slot = p->slot_of(keys[b]);
     if (slot < 0) slot = p->admit(keys[b]);
     if (slot < 0) return slot;
@@ -169,6 +170,26 @@ LLMH_API int llmh_pool_begin_step(void* h, int B, const long long* keys, const i
     if (starts[b] < 0) return starts[b];
   }
   return 0;
+}
+
+// Debug aid: with on != 0 the pool remembers every page that goes back to a free list (a request
+// ended, was preempted, or a window passed the page) until llmh_pool_take_freed collects them, so
+// that the device side can overwrite them and a read of a stale page shows.
+LLMH_API void llmh_pool_log_freed(void* h, int on) {
+  Pool* p = static_cast<Pool*>(h);
+  p->log_freed = on != 0;
+  for (auto& v : p->freed) v.clear();
+}
+
+// The pages of group g freed since the last call, into out (up to capacity); returns their
+// number and forgets them.
+LLMH_API int llmh_pool_take_freed(void* h, int g, int* out, int capacity) {
+  Pool* p = static_cast<Pool*>(h);
+  std::vector<int>& v = p->freed[g];
+  const int n = std::min((int)v.size(), capacity);
+  std::copy(v.begin(), v.begin() + n, out);
+  v.erase(v.begin(), v.begin() + n);
+  return n;
 }
 
 // The slot's table row in group g (width entries; -1 where no page is held), the number of

@@ -42,6 +42,8 @@ struct Pool {
   std::vector<long long> key;                        // per slot: the caller's key
   std::unordered_map<long long, int> slot_of_key;    // the live requests
   std::vector<int> fresh;                            // admitted since the last take: state to be zeroed
+  bool log_freed = false;                            // debug: remember which pages went back to the free lists
+  std::vector<std::vector<int>> freed;               // per group, since the last take
   char error[512] = "";
 
   int fail(int code, const char* fmt, ...) {
@@ -90,12 +92,33 @@ struct Pool {
     return slot;
   }
 
+  void give(size_t g, int page) {
+    groups[g].free.push_back(page);
+    if (log_freed) freed[g].push_back(page);
+  }
+
+  // Window pages of the slot that no token at position cur or later can see go back.
+  void give_back_window(int slot, int cur) {
+    for (size_t g = 0; g < groups.size(); ++g) {
+      Group& grp = groups[g];
+      if (grp.kind != KIND_WINDOW) continue;
+      int* row = grp.table.data() + (size_t)slot * grp.width;
+      const int dead = std::min(grp.dead_before(cur), grp.n_pages[slot]);
+      for (int i = grp.first_live[slot]; i < dead; ++i) {
+        give(g, row[i]);
+        row[i] = -1;
+      }
+      grp.first_live[slot] = std::max(grp.first_live[slot], dead);
+    }
+  }
+
   // The request ended: all its pages and its slot go back.
   int release(int slot) {
     if (!live(slot)) return fail(ERR_CONTRACT, "slot %d is not live (released twice?)", slot);
-    for (Group& grp : groups) {
+    for (size_t g = 0; g < groups.size(); ++g) {
+      Group& grp = groups[g];
       int* row = grp.table.data() + (size_t)slot * grp.width;
-      for (int i = grp.first_live[slot]; i < grp.n_pages[slot]; ++i) grp.free.push_back(row[i]);
+      for (int i = grp.first_live[slot]; i < grp.n_pages[slot]; ++i) give(g, row[i]);
       std::fill(row, row + grp.n_pages[slot], -1);
       grp.n_pages[slot] = 0;
       grp.first_live[slot] = 0;

@@ -648,6 +648,29 @@ def set_pdl(on: bool) -> None:
     load_tensor().llmk_set_pdl(c_int(int(on)))
 
 
+def set_error_block(block) -> None:
+    """Point the tensor-core kernels' error words at `block` (int32 [4] on the device: word 1 is
+    the product's, word 2 the attention's), or back at the library's own words with None."""
+    if block is not None:
+        assert block.dtype == torch.int32 and block.numel() >= 4 and block.is_contiguous()
+    load_tensor().llmk_set_error_block(_ptr(block))
+
+
+_WAIT_NAMES = {1: "TMA producer", 2: "MMA issuer", 0: "epilogue"}
+_ATTN_WAITS = {11: "the query tile", 12: "a key/value tile", 13: "the scores", 14: "the probabilities",
+               15: "the output product", 16: "tile alignment"}
+
+
+def describe_wait(word: int, code: int) -> str:
+    """What a code in an error word (1: tensor-core product, 2: tensor-core attention) stands for."""
+    if word == 1:
+        kernel = {0: "one-tile", 1: "persistent", 2: "pair"}.get((code - 1) // 3, "unknown")
+        return f"the tensor-core product ({kernel} kernel): its {_WAIT_NAMES[code % 3]} gave up a bounded wait (code {code})"
+    if word == 2:
+        return f"the tensor-core attention gave up a bounded wait for {_ATTN_WAITS.get(code, 'code ' + str(code))} (code {code})"
+    return f"error word {word}: code {code}"
+
+
 def gemm_tc_take_error() -> int:
     """The code a tensor-core kernel left when one of its bounded waits gave up (0 = none)."""
     return int(load_tensor().llmk_gemm_tc_take_error())

@@ -20,6 +20,26 @@ int llmk_fail(int code, const char* fmt, ...) {
 
 bool llmk_pdl_enabled() { return g_pdl; }
 
+// Error words of the kernels whose waits are bounded: a kernel whose wait gave up stores a code
+// in its word and returns.  The words live in a block of four ints that the caller owns
+// (llmk_set_error_block: an engine points it at its own status buffer, so that one copy shows
+// every word) or, without one, in a block that the library allocates at first use.
+static int* g_error_block = nullptr;
+static int* g_own_error_block = nullptr;
+
+int* llmk_error_word(int which) {
+  if (g_error_block) return g_error_block + which;
+  if (!g_own_error_block) {
+    if (cudaMalloc(&g_own_error_block, 4 * sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(g_own_error_block, 0, 4 * sizeof(int));
+  }
+  return g_own_error_block + which;
+}
+
+// block: four device ints (word 1: tensor-core product, word 2: tensor-core attention), zero
+// when nothing went wrong; nullptr: back to the library's own block.
+LLMK_API void llmk_set_error_block(int* block) { g_error_block = block; }
+
 LLMK_API const char* llmk_last_error() { return g_last_error; }
 LLMK_API int llmk_abi_version() { return 2; }
 // Programmatic dependent launch between the kernels of a step (on by default).

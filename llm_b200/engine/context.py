@@ -75,7 +75,7 @@ class StepContext:
     kv_lens: torch.Tensor          # [entries]: tokens held after this step
     state_slots: torch.Tensor      # [entries]
     logit_rows: torch.Tensor       # [rows]
-    status: torch.Tensor           # [1], set by kernels that meet bad input
+    status: torch.Tensor           # [4]: word 0 is set by kernels that meet bad input, 1 and 2 by tensor-core kernels whose wait gave up
     # host copies for planning (not read by kernels)
     host_entry_tokens: np.ndarray = None      # [entries] tokens per entry
     host_entry_start: np.ndarray = None       # [entries] first position of each entry

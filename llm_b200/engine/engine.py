@@ -33,7 +33,7 @@ _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 
 class StepError(ValueError):
-    """A batch that the step function refuses."""
+    """A batch that the step function refuses, or a step whose kernels reported a failure."""
 
 
 @dataclass
@@ -176,6 +176,8 @@ class Engine:
         self.cache = CacheManager(specs, self.max_entries, self.max_seq_len)
         self.cache_storage = CacheStorage(model.cache_instances, pages, self.page_size, self.dtype, self.device)
         self.state_storage = StateStorage(model.state_needs, self.max_entries, self.device)
+        if opt.poison_freed_pages:
+            self.cache.log_freed_pages(True)
 
     def _activation_estimate(self) -> int:
         widest = 4 * self.spec.hidden_size * 8          # a generous guess of scratch columns per row
@@ -189,7 +191,9 @@ class Engine:
         self._host_events = [None] * len(self._host_ring)
         self._ring_at = 0
         self.meta = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # word 0: a token id outside the vocabulary; words 1 and 2: a tensor-core product or attention
+        # kernel whose bounded wait gave up (the kernels write there while this engine's step runs)
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.resid = torch.zeros((self.max_tokens, self.hidden), dtype=torch.float32, device=self.device)
         self.workspace = Workspace(self.max_tokens, self.device)
         self._head_rows = None
@@ -322,6 +326,12 @@ class Engine:
         if n_feed < 0:
             raise StepError(lib.llmh_pool_error(pool).decode("utf-8", "replace"))
         entry_tokens, entry_start, entry_slots = ns, starts, slots
+        if self.options.poison_freed_pages:
+            # everything freed since the last step (requests that ended or were preempted, pages a
+            # window has passed) is overwritten before this step's kernels run: those launched
+            # earlier, which may still read the pages, are ahead of the fill on the stream
+            for g in range(cache.num_groups):
+                self.cache_storage.poison(g, cache.take_freed_pages(g))
         fresh = cache.take_fresh_slots()
         if fresh:
             self.state_storage.zero_slots(fresh)
@@ -348,10 +358,14 @@ class Engine:
 
     def _forward(self, ctx: StepContext) -> None:
         ops.set_stream(torch.cuda.current_stream().cuda_stream)     # looked up once per step, not per kernel
+        if self.dtype == torch.bfloat16:
+            ops.set_error_block(self.status)
         try:
             self._forward_on_stream(ctx)
         finally:
             ops.set_stream(None)
+            if self.dtype == torch.bfloat16:
+                ops.set_error_block(None)
 
     def _forward_on_stream(self, ctx: StepContext) -> None:
         stream = ResidualStream(self.resid, ctx.n_tokens)
@@ -406,10 +420,17 @@ class Engine:
         return self._logits[:R] if R else torch.empty((0, self.vocab), dtype=torch.float32, device=self.device)
 
     def check_status(self) -> None:
-        """Raise if a kernel flagged bad input since the last check (synchronises)."""
-        if int(self.status.item()) != 0:
+        """Raise if, since the last check, a kernel met a token id outside the vocabulary or gave
+        up one of its bounded waits (its output is then zeros, so the step's logits are not to be
+        used).  One small copy; synchronises."""
+        words = self.status.tolist()
+        if any(words):
             self.status.zero_()
-            raise StepError("a kernel met a token id outside the vocabulary")
+            problems = []
+            if words[0]:
+                problems.append("a kernel met a token id outside the vocabulary")
+            problems += [ops.describe_wait(i, words[i]) for i in (1, 2) if words[i]]
+            raise StepError("; ".join(problems))
 
     def memory_report(self) -> dict:
         return {"weights": self.model.weight_bytes(), "cache": self.cache_storage.bytes(),

@@ -86,8 +86,10 @@ class LLM:
         self.last_num_preemptions = scheduler.num_preemptions
         return [results[rid] for rid in ids]
 
-    def _run_to_idle(self, scheduler: Scheduler, on_finished: Callable[[Request], None]) -> None:
-        """Steps until no request is left.
+    def _run_to_idle(self, scheduler: Scheduler, on_finished: Callable[[Request], None],
+                     poll: Optional[Callable[[], None]] = None) -> None:
+        """Steps until no request is left; poll(), if given, is called before every step is
+        scheduled and may add requests.
 
         While requests only decode, a step is launched before the tokens of the step before it
         have reached the host: its input tokens are fed on the device from the sampler's output,
@@ -102,6 +104,8 @@ class LLM:
         previous = None              # (batch, rows, handle) of a launched step whose tokens are not read yet
         t_mark = time.perf_counter()
         while scheduler.num_requests():
+            if poll is not None:
+                poll()
             batch = scheduler.schedule()
             if batch.empty():
                 raise RuntimeError("the scheduler has requests but nothing can run: the cache pool is too "
@@ -144,19 +148,21 @@ class LLM:
             if rid < 0:
                 emit(-1, [])
 
+        def poll():
+            while True:
+                more = receive(False)
+                if more is None:
+                    return
+                submit(more)
+
+        def finished(r: Request):
+            self.engine.check_status()           # tokens leave only after the kernels that made them reported no failure
+            emit(r.id, r.generated)
+
         while True:
             prompt = receive(True)
             if prompt is None:
                 break
             submit(prompt)
-            while scheduler.num_requests():
-                while True:
-                    more = receive(False)
-                    if more is None:
-                        break
-                    submit(more)
-                batch = scheduler.schedule()
-                if batch.empty():
-                    raise RuntimeError("the scheduler has requests but nothing can run")
-                for r in scheduler.update(batch, self.inference(scheduler, batch)):
-                    emit(r.id, r.generated)
+            # the same loop as generate(): decode steps are launched one ahead of the host
+            self._run_to_idle(scheduler, finished, poll)

@@ -63,6 +63,7 @@ def main(argv=None, stdin=None, stdout=None) -> int:
         entries = [StepEntry(e["id"], e["tokens"], e.get("want", [])) for e in rec.get("entries", [])]
         if entries:
             logits = engine.step(entries)
+            engine.check_status()          # a step whose kernels reported a failure writes no logits
             if logits.shape[0]:
                 arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
                 tmp = os.path.join(args.out, f".{step}.f32.tmp")

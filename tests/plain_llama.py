@@ -127,14 +127,16 @@ def normalise_config(cfg: dict) -> dict:
     return cfg
 
 
-def forward(cfg: dict, w: dict, ids) -> torch.Tensor:
+def forward(cfg: dict, w: dict, ids, rows=None) -> torch.Tensor:
     """Logits [T, V] (float64) of one whole sequence starting at position 0
-    (model/llm/tiny_llama.cpp:53-62)."""
+    (model/llm/tiny_llama.cpp:53-62); with `rows`, only at those positions."""
     cfg = normalise_config(cfg)
     positions = list(range(len(ids)))
     x = embedding(w["model.embed_tokens.weight"], ids)
     for layer in range(cfg["num_hidden_layers"]):
         x = block(x, w, layer, cfg, positions)
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long)]
     x = rmsnorm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
     head = w["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else w["lm_head.weight"]
     return x @ head.to(F64).T

@@ -344,3 +344,40 @@ def test_random_load_with_lookahead_keeps_tokens_and_pages_straight(seed):
     assert all(c.num_free_pages(g) == c.group_spec(g).num_pages for g in range(c.num_groups))
     assert c.num_free_slots() == 4
     c.check()
+
+
+def test_begin_step_uses_pages_that_a_later_entry_of_the_same_step_gives_back():
+    """All or nothing: the step's page count nets what window entries give back, so an entry that
+    takes pages may stand before the entry whose window frees them."""
+    import numpy as np
+    c = CacheManager([GroupSpec("window", 8, 6, window=8)], 3, 200)
+    slots, starts = np.zeros(1, np.int32), np.zeros(1, np.int32)
+    c.begin_step(["old"], np.array([40], np.int32), slots, starts)          # 5 of 6 pages held
+    assert c.num_free_pages(0) == 1
+    # "new" needs 2 pages, one is free; "old" gives back 4 (keys below 33 are out of sight) and takes 1
+    slots, starts = np.zeros(2, np.int32), np.zeros(2, np.int32)
+    c.begin_step(["new", "old"], np.array([16, 8], np.int32), slots, starts)
+    assert list(starts) == [0, 40] and c.length("new") == 16 and c.length("old") == 48
+    c.check()
+    # and a step that does not fit changes nothing
+    before = (c.num_free_pages(0), c.length("new"), c.length("old"), c.table(0, "old"))
+    with pytest.raises(OutOfPages):
+        c.begin_step(["new", "third"], np.array([8, 40], np.int32), slots, starts)
+    assert before == (c.num_free_pages(0), c.length("new"), c.length("old"), c.table(0, "old"))
+    assert not c.is_live("third")
+    c.check()
+
+
+def test_freed_pages_are_logged_for_the_poison_fill():
+    c = CacheManager([GroupSpec("full", 8, 10), GroupSpec("window", 8, 10, window=8)], 2, 200)
+    c.log_freed_pages(True)
+    c.admit("a")
+    c.extend("a", 30)
+    held_full, held_win = c.table(0, "a"), c.table(1, "a")
+    assert c.take_freed_pages(0) == [] and c.take_freed_pages(1) == []
+    c.extend("a", 1)                       # keys below 23 are out of sight: two window pages go back
+    assert sorted(c.take_freed_pages(1)) == sorted(held_win[:2]) and c.take_freed_pages(1) == []
+    c.release("a")
+    assert sorted(c.take_freed_pages(0)) == sorted(held_full)
+    assert sorted(c.take_freed_pages(1)) == sorted(held_win[2:])
+    c.check()

@@ -18,10 +18,10 @@ def models(tmp_path_factory):
     root = tmp_path_factory.mktemp("models")
     cache = {}
 
-    def get(name, dtype):
-        key = (name, dtype)
+    def get(name, dtype, peaked=False):
+        key = (name, dtype, peaked)
         if key not in cache:
-            d = make_model_dir(root, name, dtype)
+            d = make_model_dir(root, name, dtype, peaked=peaked)
             w = load_plain_weights(d)
             cfg, page = CONFIGS[name]
             reqs = {f"r{i}": random_tokens(n, cfg["vocab_size"], 100 + i) for i, n in enumerate(LENGTHS[name])}
@@ -31,12 +31,14 @@ def models(tmp_path_factory):
     return get
 
 
-def make_engine(model_dir, dtype, page, num_blocks, max_tokens=512, max_seqs=4):
+def make_engine(model_dir, dtype, page, num_blocks, max_tokens=512, max_seqs=4, poison=True):
+    """poison: pages that go back to the pool are overwritten with a huge value, so that a kernel
+    that reads a page its request does not hold gives logits that are far off."""
     from llm_b200.config import EngineOptions
     from llm_b200.engine.engine import Engine
     return Engine(model_dir, EngineOptions(dtype=dtype, kv_block_size=page, max_num_seqs=max_seqs,
                                            max_num_batched_tokens=max_tokens, num_kv_blocks=num_blocks,
-                                           use_cuda_graphs=False))
+                                           use_cuda_graphs=False, poison_freed_pages=poison))
 
 
 def compare(got, ref, dtype, what):
@@ -68,6 +70,46 @@ def test_every_cut_matches_plain(models, name, dtype):
     eng = make_engine(d, dtype, page, pool)
     compare(replay.run_steps(eng, replay.steps_mixed(reqs)), ref, dtype, "mixed")
     eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C", "D", "E"])
+def test_every_cut_matches_plain_with_peaked_attention(models, name, dtype):
+    """The same cuts on weights whose attention is peaked (a few keys carry each row), where one
+    wrong key, page or window edge moves a logit by far more than the bound; freed pages poisoned."""
+    d, cfg, page, reqs, ref = models(name, dtype, peaked=True)
+    longest = max(len(t) for t in reqs.values())
+    eng = make_engine(d, dtype, page, (longest + page - 1) // page + 1)
+    compare(replay.run_steps(eng, replay.steps_whole(reqs)), ref, dtype, "whole")
+    compare(replay.run_steps(eng, replay.steps_tail_decode(reqs)), ref, dtype, "tail decode")
+    compare(replay.run_steps(eng, replay.steps_portions(reqs)), ref, dtype, "portions")
+    lens = sorted((len(t) for t in reqs.values()), reverse=True)
+    eng = make_engine(d, dtype, page, sum((n + page - 1) // page for n in lens[:4]) + 1)
+    compare(replay.run_steps(eng, replay.steps_mixed(reqs)), ref, dtype, "mixed")
+    eng.cache.check()
+
+
+def test_peaked_attention_shows_one_wrong_page(models):
+    """What the peaked weights are for: two pages of values that trade places (the keys stay) move
+    the bfloat16 logits of the next token far beyond the bound, while on the plain random weights,
+    where every softmax is nearly uniform, the same fault stays inside it."""
+    from llm_b200.engine.engine import StepEntry
+    moved = {}
+    for peaked in (False, True):
+        d, cfg, page, reqs, ref = models("D", "bfloat16", peaked=peaked)
+        toks = reqs["r2"]                                   # 300 tokens
+        eng = make_engine(d, "bfloat16", page, 40, poison=False)
+        eng.step([StepEntry("x", toks[:-1], [])])
+        table = eng.cache.table(0, "x")
+        a, b = table[-2], table[-4]
+        for inst in range(len(eng.cache_storage.k)):
+            v_pages = eng.cache_storage.pages(inst)[1]
+            tmp = v_pages[a].clone()
+            v_pages[a] = v_pages[b]
+            v_pages[b] = tmp
+        got = eng.step([StepEntry("x", toks[-1:], [0])])[0].double().cpu()
+        moved[peaked] = float((got - ref["r2"][-1]).abs().max() / ref["r2"].abs().max())
+    assert moved[False] < TOL["bfloat16"] and moved[True] > 3 * TOL["bfloat16"], moved
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

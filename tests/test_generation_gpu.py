@@ -145,3 +145,98 @@ def test_lookahead_changes_nothing(folders, dtype):
     assert mk(True, -1).generate(prompts, max_new_tokens=12, temperature=0.7, seed=2) == \
         mk(False, -1).generate(prompts, max_new_tokens=12, temperature=0.7, seed=2)
     llm.engine.cache.check()
+
+
+def _same_or_near_tie(cfg, w, prompts, got, want):
+    """Two bfloat16 runs that batch the same requests differently (other kernels, other split counts)
+    may part ways at a near-tie: the first differing token must be one of the plain logits."""
+    for p, g, wnt in zip(prompts, got, want):
+        assert len(g) == len(wnt)
+        if g != wnt:
+            k = next(i for i, (a, b) in enumerate(zip(g, wnt)) if a != b)
+            row = pl.forward(cfg, w, list(p) + g[:k])[-1]
+            assert abs(float(row[g[k]] - row[wnt[k]])) <= TOL["bfloat16"] * float(row.abs().max()), (k, g[k], wnt[k])
+
+
+def test_a_given_up_wait_is_reported_by_the_step_function(folders):
+    """The tensor-core kernels bound their waits; one that gives up stores a code in a word of the
+    engine's status block and writes zeros.  The word is set here from the host (no kernel is made
+    to wait): check_status, generate and the server's emit then refuse to pass tokens on."""
+    from llm_b200 import LLM
+    from llm_b200.csrc import ops
+    from llm_b200.engine.engine import StepError
+    cfg, page = CONFIGS["D"]
+    llm = LLM(folders("D", "bfloat16"), dtype="bfloat16", max_num_seqs=4, max_num_batched_tokens=64, num_kv_blocks=40,
+              eos_token_id=-1)
+    eng = llm.engine
+    prompts = [random_tokens(20, cfg["vocab_size"], 3)]
+    assert len(llm.generate(prompts, max_new_tokens=4)[0]) == 4          # a clean run raises nothing
+    # the word the product kernels are given while this engine steps is a word of its status block
+    eng.status[1] = 8
+    ops.set_error_block(eng.status)
+    try:
+        assert ops.gemm_tc_take_error() == 8 and int(eng.status[1]) == 0
+    finally:
+        ops.set_error_block(None)
+    eng.status[1] = 5
+    with pytest.raises(StepError, match="tensor-core product .persistent kernel.*MMA issuer"):
+        eng.check_status()
+    eng.check_status()                                                    # reported once, then clear
+    eng.status[2] = 12
+    with pytest.raises(StepError, match="tensor-core attention.*key/value tile"):
+        llm.generate(prompts, max_new_tokens=2)
+    eng.status[2] = 13
+    emitted = []
+    feed = iter(prompts)
+    with pytest.raises(StepError, match="the scores"):
+        llm.server(lambda wait: next(feed, None), lambda rid, toks: emitted.append(toks), max_new_tokens=3)
+    assert emitted == []
+
+
+def test_server_runs_ahead_like_generate(folders):
+    """The serving loop (what the command line runs) launches decode steps one ahead of the host,
+    as generate does, and emits the same tokens; requests that arrive while others decode join."""
+    from llm_b200 import LLM
+    cfg, page = CONFIGS["D"]
+    d = folders("D", "bfloat16")
+    prompts = [random_tokens(n, cfg["vocab_size"], 270 + n) for n in (9, 50, 3, 130)]
+    llm = LLM(d, dtype="bfloat16", max_num_seqs=4, max_num_batched_tokens=64, num_kv_blocks=60, eos_token_id=-1)
+    base = llm.generate(prompts, max_new_tokens=24)
+    calls = {"n": 0}
+    waiting = list(prompts)
+
+    def receive(wait):
+        calls["n"] += 1
+        # two prompts at once, the others only after some steps have run
+        if wait or calls["n"] in (2, 9, 15):
+            return waiting.pop(0) if waiting else None
+        return None
+
+    got = {}
+    llm.server(receive, lambda rid, toks: got.__setitem__(rid, toks), max_new_tokens=24)
+    _same_or_near_tie(cfg, load_plain_weights(d), prompts, [got[i] for i in range(4)], base)
+    assert llm.last_stats["lookahead_steps"] >= 10
+    llm.engine.cache.check()
+
+
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_preemption_in_bfloat16_with_graphs_and_lookahead(folders, name):
+    """So few pages that decoding preempts and recomputes, with CUDA graphs and the one-step
+    lookahead on: the tokens equal those of a pool that holds everything."""
+    from llm_b200 import LLM
+    cfg, page = CONFIGS[name]
+    d = folders(name, "bfloat16")
+    prompts = [random_tokens(n, cfg["vocab_size"], 340 + n) for n in (30, 29, 31, 12)]
+    roomy = LLM(d, dtype="bfloat16", max_num_seqs=4, max_num_batched_tokens=32, kv_block_size=page, num_kv_blocks=64,
+                eos_token_id=-1)
+    want = roomy.generate(prompts, max_new_tokens=40)
+    assert roomy.last_num_preemptions == 0
+    tight_pages = -(-(31 + 40) // page) * 2 + 1        # two requests fit whole, four do not
+    tight = LLM(d, dtype="bfloat16", max_num_seqs=4, max_num_batched_tokens=32, kv_block_size=page,
+                num_kv_blocks=tight_pages, eos_token_id=-1, use_cuda_graphs=True, lookahead=True)
+    got = tight.generate(prompts, max_new_tokens=40)
+    assert tight.last_num_preemptions > 0
+    assert tight.last_stats["lookahead_steps"] > 0 and tight.engine.counters["graph_replays"] > 0
+    _same_or_near_tie(cfg, load_plain_weights(d), prompts, got, want)
+    tight.engine.cache.check()
+    assert tight.engine.cache.num_free_pages(0) == tight_pages

@@ -575,6 +575,73 @@ def test_decode_attention_fused_with_rotation_and_store(ops, partial, NH, NKV, H
     assert rel_err(out2, ref) < 1e-2
 
 
+def _plain_decode_attention(q, kp, vp, bt, lens, NH, NKV, HS, page, window, scale):
+    """softmax(q K^T scale) V per entry and head in float64 over the entry's own pages."""
+    G = NH // NKV
+    ref = torch.zeros(len(lens), NH * HS, dtype=torch.float64)
+    kp64, vp64, bt_h = kp.double().cpu(), vp.double().cpu(), bt.cpu()
+    for b, n in enumerate(lens):
+        lo = max(0, n - window) if window else 0
+        pages = bt_h[b, :-(-n // page)].long()
+        K = kp64[pages].permute(1, 0, 2, 3).reshape(NKV, -1, HS)[:, lo:n]           # [NKV, keys, HS]
+        V = vp64[pages].permute(1, 0, 2, 3).reshape(NKV, -1, HS)[:, lo:n]
+        qb = q[b, :NH * HS].double().cpu().view(NKV, G, HS)
+        p = torch.softmax(torch.einsum("kgd,ktd->kgt", qb, K) * scale, dim=-1)
+        ref[b] = torch.einsum("kgt,ktd->kgd", p, V).reshape(-1)
+    return ref
+
+
+@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("B,NH,NKV,HS,splits", [(80, 32, 4, 64, 1),      # 320 CTAs of one range each
+                                                (40, 32, 4, 64, 2),      # two ranges, merged by the last CTA to arrive
+                                                (41, 16, 8, 64, 3),      # three ranges, two heads per group
+                                                (160, 8, 1, 128, 1)])    # the same choice at head size 128
+def test_decode_attention_with_more_ctas_than_one_wave(ops, fused, B, NH, NKV, HS, splits):
+    """A grid that does not fit the SMs at once with deep stages runs the one-stage variant of the
+    MMA decode kernel (at head size 64 also held to 128 registers): requests of ragged lengths,
+    pages in shuffled order, queries given and rotated-and-stored by the kernel itself, against
+    the float64 formula."""
+    torch.manual_seed(21)
+    dtype, page, window = torch.bfloat16, 16, 0
+    g = torch.Generator().manual_seed(B)
+    lens = [int(x) for x in torch.randint(1, 300, (B,), generator=g)]
+    lens[0], lens[1], lens[2] = 1, page, page + 1
+    W = -(-max(lens) // page) + 1
+    n_pages = sum(-(-n // page) for n in lens) + 5
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    kp = torch.randn(n_pages, NKV, page, HS, device=DEV).to(dtype)
+    vp = torch.randn(n_pages, NKV, page, HS, device=DEV).to(dtype)
+    bt = torch.zeros(B, W, dtype=torch.int32)
+    at = 0
+    for b, n in enumerate(lens):
+        k = -(-n // page)
+        bt[b, :k] = torch.tensor(perm[at:at + k], dtype=torch.int32)
+        at += k
+    bt_d = bt.to(DEV)
+    kv_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1.3 / math.sqrt(HS)                  # scores wide enough that the far keys matter
+    out = torch.zeros(B, NH * HS, device=DEV, dtype=dtype)
+    assert splits * NKV * B > (2 if HS == 64 else 1) * torch.cuda.get_device_properties(0).multi_processor_count
+    if not fused:
+        q = torch.randn(B, NH * HS, device=DEV).to(dtype)
+        ops.paged_attention_decode(out, q, kp, vp, bt_d, kv_lens, B, NH, NKV, HS, window, scale, splits=splits)
+    else:
+        qkv = torch.randn(B, (NH + 2 * NKV) * HS, device=DEV).to(dtype)
+        cos = torch.cos(torch.rand(300, HS // 2, device=DEV) * 6)
+        sin = torch.sqrt(1 - cos * cos)
+        slot = torch.tensor([int(bt[b, (n - 1) // page]) * page + (n - 1) % page for b, n in enumerate(lens)],
+                            dtype=torch.int32, device=DEV)
+        kp1, vp1 = kp.clone(), vp.clone()
+        q = torch.zeros(B, NH * HS, device=DEV, dtype=dtype)
+        ops.rope_kv_write(qkv.clone(), cos, sin, kv_lens - 1, slot, kp1, vp1, B, NH, NKV, HS, q_out=q)
+        ops.decode_attention_fused(out, qkv, cos, sin, kp, vp, bt_d, kv_lens, B, NH, NKV, HS, window, scale, splits=splits)
+        torch.cuda.synchronize()
+        assert torch.equal(kp, kp1) and torch.equal(vp, vp1)
+    ref = _plain_decode_attention(q, kp, vp, bt, lens, NH, NKV, HS, page, window, scale)
+    err = (out.double().cpu() - ref).abs().max(dim=1).values / ref.abs().max()
+    assert float(err.max()) < 1e-2, f"entry {int(err.argmax())} of length {lens[int(err.argmax())]}: {float(err.max()):.3e}"
+
+
 def test_decode_attention_fused_refuses_other_sizes(ops):
     cos = torch.ones(8, 24, device=DEV)
     assert not ops.decode_attention_fused_supported(torch.zeros(2, 48 * 3, device=DEV, dtype=torch.bfloat16), cos, cos, 48)

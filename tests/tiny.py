@@ -36,12 +36,32 @@ CONFIGS = {"A": (CONFIG_A, 16), "B": (CONFIG_B, 8), "C": (CONFIG_C, 32),
            "D": (CONFIG_D, 16), "E": (CONFIG_E, 32)}   # name -> (config, page size)
 
 
-def make_model_dir(tmp_root, name: str, dtype: str, seed: int = 1234, scale_far_key: bool = False) -> str:
+def make_model_dir(tmp_root, name: str, dtype: str, seed: int = 1234, peaked: bool = False) -> str:
+    """A model folder of configuration `name` with seeded random weights.  peaked: the query and
+    key projections are scaled so that the attention scores have a standard deviation of about 1.5
+    instead of about 0.05 (more than that and bfloat16's own rounding of the scores, which grows with
+    them, no longer fits the bound of these tests).  With the plain random weights every softmax is nearly uniform and the
+    attention output is close to the mean of the values whatever keys are read; with peaked scores
+    a few keys carry each row, so one wrong key, page or mask edge moves the logits by far more
+    than the bfloat16 bound."""
+    import math
+
     from llm_b200.weights.loader import write_random_model
+    from llm_b200.weights.safetensors_io import SafetensorsFile, write_safetensors
     cfg, _ = CONFIGS[name]
-    d = os.path.join(str(tmp_root), f"tiny_{name}_{dtype}")
+    d = os.path.join(str(tmp_root), f"tiny_{name}_{dtype}" + ("_peaked" if peaked else ""))
     if not os.path.isdir(d):
         write_random_model(d, cfg, seed, dtype)
+        if peaked:
+            path = os.path.join(d, "model.safetensors")
+            f = SafetensorsFile(path)
+            tensors = {n: f.tensor(n).clone() for n in f.names()}
+            f.close()
+            factor = math.sqrt(1.5 / (0.0004 * cfg["hidden_size"]))
+            for n, t in tensors.items():
+                if n.endswith(("q_proj.weight", "k_proj.weight")):
+                    tensors[n] = (t.float() * factor).to(t.dtype)
+            write_safetensors(path, tensors, metadata={"format": "pt"})
     return d
 
 
