@@ -20,7 +20,7 @@ int launch_decode_mma(void* out, long long out_stride, const void* q, long long 
   // clusters against 23 us with the counter-based merge; at 8 requests 9.3 us against 13.5 us.)
   constexpr int RECV_LIMIT = 64 * 1024;
   const int recv_bytes = (splits - 1) * group_rows * head_dim * 4;
-  const bool cluster = splits >= 2 && splits <= 8 && (long long)splits * n_kv * n_entries <= 2 * 148 &&
+  const bool cluster = splits >= 2 && splits <= 8 && (long long)splits * n_kv * n_entries <= 2 * llmk_sm_count() &&
                        recv_bytes <= RECV_LIMIT;
   // Without a cluster: deep stages (three at head size 64, else two) while the whole grid fits on
   // the SMs at once with them (two CTAs per SM at head size 64, one at 128); else the variant
@@ -28,7 +28,7 @@ int launch_decode_mma(void* out, long long out_stride, const void* q, long long 
   // an SM and the grid still runs as one wave where it can (128 requests x 4 kv heads at 640
   // keys: 22.9 us against 28.0 us).
   const long long ctas = (long long)splits * n_kv * n_entries;
-  const bool light = !cluster && ctas > (head_dim == 64 ? 2 : 1) * 148;
+  const bool light = !cluster && ctas > (long long)(head_dim == 64 ? 2 : 1) * llmk_sm_count();
   // per warp its stages of a tile of keys and a tile of values: NST in the kernel
   const int stage_bytes = 4 * ((cluster || light) ? 1 : head_dim == 64 ? 3 : 2) * 2 * decode_mma::TILE * head_dim * 2;
   using Kernel = decltype(&decode_mma::decode_attention_mma_kernel<64, false, FUSED>);

@@ -140,7 +140,17 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
   const int split = blockIdx.x, g = blockIdx.y, e = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = n_heads / n_kv;
-  const int pos = kv_lens[e] - 1;
+  // a length beyond the entry's table row is cut to what the row can hold; an entry without keys
+  // gets zeros (every range of it sees the same length and leaves here, so nobody waits for anybody)
+  const int n_held = min(kv_lens[e], table_width * page_size);
+  if (n_held <= 0) {
+    pdl_wait();
+    if (split == 0)
+      for (int i = tid; i < group * HS; i += THREADS)
+        out[(size_t)e * out_stride + (size_t)g * group * HS + i] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int pos = n_held - 1;
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   const int n_keys = pos - lo + 1;
   int chunk = (n_keys + splits - 1) / splits;

@@ -81,6 +81,7 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 bool llmk_pdl_enabled();
+int llmk_sm_count();                    // SMs of the current device (runtime.cu)
 int* llmk_error_word(int which);      // the device word kernels of one kind report a given-up wait in (runtime.cu)
 
 template <typename... KArgs, typename... Args>

@@ -908,7 +908,7 @@ int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, void* C, lon
     configured = true;
   }
   const int tiles = ((M + BP - 1) / BP) * (SWIGLU ? (N / 2 + 127) / 128 : (N + tile_q - 1) / tile_q);
-  launch_kernel(kern, dim3(tiles < 148 ? tiles : 148), dim3(THREADS), (size_t)smem, stream, mp, mq, (TOut*)C, ldc, M, N, K,
+  launch_kernel(kern, dim3(tiles < llmk_sm_count() ? tiles : llmk_sm_count()), dim3(THREADS), (size_t)smem, stream, mp, mq, (TOut*)C, ldc, M, N, K,
                 tile_q, g_err_flag);
   LLMK_LAUNCH_CHECK("gemm_tc_persistent");
 }
@@ -917,7 +917,7 @@ int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, void* C, lon
 template <typename Kernel>
 int max_pairs(Kernel kern) {
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * 148);
+  cfg.gridDim = dim3(2 * llmk_sm_count());
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
   cudaLaunchAttribute attr[1];
@@ -932,7 +932,7 @@ int max_pairs(Kernel kern) {
     cudaGetLastError();
     return 0;
   }
-  return n < 74 ? n : 74;
+  return n < llmk_sm_count() / 2 ? n : llmk_sm_count() / 2;
 }
 
 template <typename TOut, int EPI>
@@ -1137,7 +1137,7 @@ LLMK_API int llmk_reduce_partials(void* out, const float* partials, long long mn
                                   cudaStream_t stream) {
   if (mn == 0) return 0;
   size_t blocks = ((size_t)mn + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > (size_t)llmk_sm_count() * 8) blocks = (size_t)llmk_sm_count() * 8;
   return dispatch_dtype(out_dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     launch_kernel(reduce_partials_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, partials, (size_t)mn, splits);

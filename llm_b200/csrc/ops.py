@@ -144,6 +144,14 @@ def gather_rows(out: torch.Tensor, resid: torch.Tensor, delta, rows: torch.Tenso
                                    c_int(resid.shape[-1]), c_int(kind), _stream()))
 
 
+def cast_rows(out: torch.Tensor, rows_f32: torch.Tensor, n_rows: int) -> None:
+    """out[:n_rows] = rows_f32[:n_rows] rounded to out's dtype (float32 or bfloat16)."""
+    assert rows_f32.dtype == torch.float32 and out.is_contiguous() and rows_f32.is_contiguous()
+    assert out.shape[-1] == rows_f32.shape[-1]
+    _check(load().llmk_cast_rows(_ptr(out), _ptr(rows_f32), c_longlong(n_rows * out.shape[-1]), c_int(_kind(out.dtype)),
+                                 _stream()))
+
+
 def silu_mul(out: torch.Tensor, gate_up, rows: int) -> None:
     """out[:rows, :I] = silu(gate_up[:, :I]) * gate_up[:, I:]; gate_up a tensor or a PartialSum."""
     inter = out.shape[-1]
@@ -407,7 +415,6 @@ def rope_store_attend(out, qkv, cos, sin, k_pages, v_pages, group, ctx, n_heads:
 
 # ---- tensor-core product ------------------------------------------------------------
 
-_SMS = 148
 _PARTIALS = {}      # device -> float32 scratch for split-K partial sums
 _PARTIAL_BYTES = 64 << 20
 
@@ -416,16 +423,22 @@ def _ceil_div(a: int, b: int) -> int:
     return -(-a // b)
 
 
+@functools.lru_cache(maxsize=None)
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (the planners size grids and rounds by it)."""
+    return max(1, int(load().llmk_device_sm_count()))
+
+
 PERSISTENT_GEMM = True
 PAIR_GEMM = True
 
 
 def plan_gemm(M: int, N: int, K: int, fused_reduce: bool = False):
-    return _plan_gemm(M, N, K, fused_reduce, PERSISTENT_GEMM, PAIR_GEMM)
+    return _plan_gemm(M, N, K, fused_reduce, PERSISTENT_GEMM, PAIR_GEMM, sm_count())
 
 
 @functools.lru_cache(maxsize=4096)
-def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool, pair: bool = False):
+def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool, pair: bool = False, _SMS: int = 148):
     """(swap, tile, splits, k-blocks per split, mode) for the tensor-core product; mode 0 = one
     CTA per tile, 1 = the splits of a tile sum on chip in a cluster, 2 = persistent CTAs, 3 =
     persistent pairs of CTAs on tiles of 256 rows.
@@ -440,7 +453,7 @@ def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool, pai
     at 129 to 4,096 rows; plus the sum of the partial results where K is split."""
     kb = _ceil_div(K, 64)
     if M <= 128:
-        return _plan_swapped(M, N, kb, fused_reduce)
+        return _plan_swapped(M, N, kb, fused_reduce, _SMS)
     best = None
     for tile in (256, 224, 192, 160, 128):
         tiles = _ceil_div(M, 128) * _ceil_div(N, tile)
@@ -480,7 +493,7 @@ def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool, pai
 _SWAPPED_STAGES = {16: 6, 32: 5, 64: 4, 128: 3}      # as stages_for() in gemm_tc.cu
 
 
-def _plan_swapped(M: int, N: int, kb: int, fused_reduce: bool):
+def _plan_swapped(M: int, N: int, kb: int, fused_reduce: bool, _SMS: int):
     """The swapped mode (up to 128 rows): a stream of weights.  Two CTAs share an SM, so up to 296
     run at a time.  A CTA alone is bound by what its ring keeps in flight (stages x stage bytes per
     memory latency of about 2 us), the CTAs of one SM by its way to L2, all CTAs together by HBM;
@@ -593,6 +606,7 @@ def _qkv_rope_tile(rows: int, n: int, k: int, head_dim: int) -> int:
     """The tile width (whole heads, up to 256 columns) with the fewest rounds of pair tiles, by
     the pair kernel's terms of plan_gemm."""
     best = None
+    _SMS = sm_count()
     for tile in range(head_dim, 257, head_dim):
         t_kb = max(0.31 + 0.0004 * (tile - 128), 1.43 * 256 * tile * 64 * 2 / 2 / 15.2e6)
         cost = _ceil_div(_ceil_div(rows, 256) * _ceil_div(n, tile), _SMS // 2) * t_kb

@@ -151,6 +151,27 @@ LLMK_API int llmk_gather_rows(float* out, const float* resid, const void* delta,
   });
 }
 
+// out[i] = in[i] rounded to the element type: float32 rows handed to a product without a norm
+// between (a head that takes the stream as it is).
+template <typename T>
+__global__ void cast_rows_kernel(T* __restrict__ out, const float* __restrict__ in, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_f32<T>(in[i]);
+}
+
+LLMK_API int llmk_cast_rows(void* out, const float* in, long long n, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  size_t blocks = ((size_t)n + 255) / 256;
+  if (blocks > (size_t)llmk_sm_count() * 8) blocks = (size_t)llmk_sm_count() * 8;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    launch_kernel(cast_rows_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, in, (size_t)n);
+    LLMK_LAUNCH_CHECK("cast_rows");
+  });
+}
+
 // ---- SiLU(gate) * up --------------------------------------------------------
 // in [rows, 2*inter]: gate in the first half of a row, up in the second.
 // act = g / (1 + exp(-g)) * u in float32 (kernel/activation/SwiGLU.h:31-33).
@@ -191,7 +212,7 @@ LLMK_API int llmk_silu_mul(void* out, const void* gate_up, const float* partials
     MaybePartial<T> in{(const T*)gate_up, partials, splits, split_stride};
     const bool vec = inter % 8 == 0 && in.vector_ok() && (uintptr_t)out % 16 == 0;
     size_t blocks = ((vec ? total / 8 : total) + 255) / 256;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (blocks > (size_t)llmk_sm_count() * 32) blocks = (size_t)llmk_sm_count() * 32;
     if (vec)
       launch_kernel(silu_mul_kernel<T, true>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, in, inter, total);
     else

@@ -20,6 +20,20 @@ int llmk_fail(int code, const char* fmt, ...) {
 
 bool llmk_pdl_enabled() { return g_pdl; }
 
+// Streaming multiprocessors of the current device, asked once per device.
+int llmk_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+  if (cached[dev] <= 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+LLMK_API int llmk_device_sm_count() { return llmk_sm_count(); }
+
 // Error words of the kernels whose waits are bounded: a kernel whose wait gave up stores a code
 // in its word and returns.  The words live in a block of four ints that the caller owns
 // (llmk_set_error_block: an engine points it at its own status buffer, so that one copy shows

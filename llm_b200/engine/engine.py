@@ -10,6 +10,7 @@ head runs on wanted rows only, and sampling is a layer above.
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -90,6 +91,7 @@ class _NativeLayout(ctypes.Structure):
 
 class Engine:
     MAX_PROMPT_GRAPHS = 64        # captured shapes of steps that bring prompt portions
+    MAX_GRAPHS = 512              # captured shapes in all; the one replayed longest ago goes first
 
     def __init__(self, model_dir: Optional[str], options: Optional[EngineOptions] = None, *,
                  random_config: Optional[dict] = None, random_seed: int = 0):
@@ -137,9 +139,7 @@ class Engine:
 
         self._init_cache()
         self._init_buffers()
-        self._graphs: Dict[tuple, tuple] = {}            # key -> (graph, kernel launches inside)
-        self._graph_seen: Dict[tuple, int] = {}          # how often a shape that is not yet captured has come
-        self._prompt_graphs = 0
+        self._drop_graphs()
         self.counters = {"steps": 0, "tokens": 0, "graph_captures": 0, "graph_replays": 0}
 
     # ---- set-up -------------------------------------------------------------
@@ -227,13 +227,19 @@ class Engine:
             logit_rows=dev(lay.logit_rows, self.max_rows), status=self.status,
             groups=self._groups, workspace=self.workspace)
 
+    def _drop_graphs(self) -> None:
+        """Forget every captured step (their buffers' addresses changed, or none exist yet)."""
+        self._graphs: "OrderedDict[tuple, tuple]" = OrderedDict()     # key -> (graph, kernel launches inside), by last use
+        self._graph_seen: Dict[tuple, int] = {}          # how often a shape that is not yet captured has come
+        self._prompt_graphs = 0
+
     def _logit_buffers(self, rows: int):
         if self._logits is None or self._logits.shape[0] < rows:
             n = max(rows, min(self.max_rows, 64))
             self._head_rows = torch.zeros((n, self.hidden), dtype=torch.float32, device=self.device)
             self._head_normed = torch.zeros((n, self.hidden), dtype=self.dtype, device=self.device)
             self._logits = torch.zeros((n, self.vocab), dtype=torch.float32, device=self.device)
-            self._graphs.clear()         # captured graphs hold the old addresses
+            self._drop_graphs()          # captured graphs hold the old addresses
         return self._head_rows, self._head_normed, self._logits
 
     # ---- requests -----------------------------------------------------------
@@ -370,12 +376,8 @@ class Engine:
     def _forward_on_stream(self, ctx: StepContext) -> None:
         stream = ResidualStream(self.resid, ctx.n_tokens)
         self.model.forward(ctx, stream, self._views)
-        R = ctx.n_logit_rows
-        if R:
-            rows, normed, logits = self._logit_buffers(R)
-            ops.gather_rows(rows, stream.resid, stream.pending, ctx.logit_rows, R)
-            self.model.final_norm.forward_rows(rows, R, normed)
-            self.model.head.forward(normed, R, logits)
+        if ctx.n_logit_rows:
+            self.model.head.logits(stream, ctx, self.model.final_norm, self._logit_buffers(ctx.n_logit_rows))
 
     def _run(self, ctx: StepContext) -> torch.Tensor:
         R = ctx.n_logit_rows
@@ -387,7 +389,7 @@ class Engine:
         # key and replayed (the reference captures per GraphShape{batch, tokens} the same way,
         # runtime/LLM.h:63-72,192-201): steps of single tokens at once, other shapes when they come
         # a second time (a portion of the full token budget recurs, a ragged last portion does not).
-        graphable = self.options.use_cuda_graphs
+        graphable = self.options.use_cuda_graphs and self.model.is_graph_safe(ctx)
         if graphable:
             key = (ctx.n_entries, ctx.n_tokens, R, ctx.kv_bucket if ctx.decode_only else 0)
             entry = self._graphs.get(key)
@@ -398,6 +400,7 @@ class Engine:
                     graphable = False
         if graphable:
             if entry is not None:
+                self._graphs.move_to_end(key)
                 entry[0].replay()
                 ops.count_launches(entry[1])
                 self.counters["graph_replays"] += 1
@@ -409,6 +412,10 @@ class Engine:
                 with torch.cuda.graph(graph):
                     self._forward(ctx)                   # recorded only; same inputs, same result when replayed
                 self._graphs[key] = (graph, ops.launch_count() - before)
+                while len(self._graphs) > self.MAX_GRAPHS:
+                    old_key, _old = self._graphs.popitem(last=False)
+                    if old_key[3] == 0:
+                        self._prompt_graphs -= 1
                 ops.count_launches(-(ops.launch_count() - before))
                 self.counters["graph_captures"] += 1
                 if not ctx.decode_only:

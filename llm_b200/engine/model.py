@@ -34,7 +34,7 @@ class Model:
         self.spec, self.dtype, self.device = spec, dtype, device
         self.embedding = build_part("embedding", spec.embedding, dtype, device)
         self.blocks = [part_class("block", layer.block)(layer.parts, dtype, device) for layer in spec.layers]
-        self.final_norm = build_part("norm", spec.final_norm, dtype, device)
+        self.final_norm = build_part("norm", spec.final_norm, dtype, device) if spec.final_norm is not None else None
         self.head = build_part("head", spec.head, dtype, device)
 
         self.group_keys: List[tuple] = []            # (kind, window) per group
@@ -70,11 +70,22 @@ class Model:
             self.occurrences.append(Occurrence(layer_idx, inst, owns, st))
 
     def parts(self):
-        yield self.embedding
+        """Every part of the model, the parts that parts are built from included."""
+        def walk(part):
+            yield part
+            for child in getattr(part, "children", lambda: [])():
+                yield from walk(child)
+        yield from walk(self.embedding)
         for block in self.blocks:
-            yield from block.parts.values()
-        yield self.final_norm
-        yield self.head
+            for part in block.parts.values():
+                yield from walk(part)
+        if self.final_norm is not None:
+            yield from walk(self.final_norm)
+        yield from walk(self.head)
+
+    def is_graph_safe(self, ctx) -> bool:
+        """Whether every part says that this step may be captured in, or replayed from, a CUDA graph."""
+        return all(getattr(part, "is_graph_safe", lambda c: True)(ctx) for part in self.parts())
 
     def parameters(self) -> Dict[str, ParamInfo]:
         out: Dict[str, ParamInfo] = {}

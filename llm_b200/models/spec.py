@@ -39,7 +39,7 @@ class ModelSpec:
     embedding: PartSpec
     layers: Tuple[LayerSpec, ...]
     order: Tuple[int, ...]            # indices into layers, in execution order; may repeat
-    final_norm: PartSpec
+    final_norm: Optional[PartSpec]    # None: the head takes the stream as it is
     head: PartSpec
     eos_token_id: Optional[int] = None
 

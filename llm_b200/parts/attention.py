@@ -63,24 +63,40 @@ class PagedAttention(Part):
     def state_need(self):
         return None
 
+    def children(self):
+        return [self.position] if self.position is not None else []
+
     def forward(self, x: torch.Tensor, ctx, view) -> torch.Tensor:
         T = ctx.n_tokens
         ws = ctx.workspace
         width = self.q_size + 2 * self.kv_size
         cos = sin = None
+        own_transform = None
         if self.position is not None:
-            cos, sin = self.position.tables()
+            if hasattr(self.position, "tables"):
+                cos, sin = self.position.tables()
+            elif hasattr(self.position, "apply"):
+                own_transform = self.position.apply
         k_pages, v_pages = view.k_pages, view.v_pages
         attn = ws.get("attn_out", T, self.q_size, self.dtype)
-        # many rows: one kernel projects, rotates and stores; then the attention over the pages
-        q = ops.qkv_rope_store(x, self.w_qkv, lambda: ws.get("q_rot", T, self.q_size, self.dtype), T, cos, sin,
-                               ctx.positions, view.group.slot_map, k_pages, v_pages, self.num_heads,
-                               0 if self.shares_cache else k_pages.shape[1], self.head_dim)
-        if q is not None:
-            ops.paged_attention(attn, q, k_pages, v_pages, view.group, ctx, self.num_heads, k_pages.shape[1],
-                                self.head_dim, self.window or 0, self.scale)
-            return linear(attn, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
-        qkv = linear(x, self.w_qkv, ws.get("qkv", T, width, self.dtype), T, allow_partial=FUSE_PARTIALS)
+        if own_transform is not None:
+            # a position part with a transform of its own: it runs on the summed projection, between
+            # the product and the cache store; the kernels after it neither rotate nor sum
+            qkv = linear(x, self.w_qkv, ws.get("qkv", T, width, self.dtype), T)
+            q_view = qkv[:, :self.q_size].view(T, self.num_heads, self.head_dim)
+            k_view = (qkv[:, self.q_size:self.q_size + self.kv_size].view(T, -1, self.head_dim)
+                      if self.kv_size else None)
+            own_transform(q_view, k_view, ctx)
+        else:
+            # many rows: one kernel projects, rotates and stores; then the attention over the pages
+            q = ops.qkv_rope_store(x, self.w_qkv, lambda: ws.get("q_rot", T, self.q_size, self.dtype), T, cos, sin,
+                                   ctx.positions, view.group.slot_map, k_pages, v_pages, self.num_heads,
+                                   0 if self.shares_cache else k_pages.shape[1], self.head_dim)
+            if q is not None:
+                ops.paged_attention(attn, q, k_pages, v_pages, view.group, ctx, self.num_heads, k_pages.shape[1],
+                                    self.head_dim, self.window or 0, self.scale)
+                return linear(attn, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
+            qkv = linear(x, self.w_qkv, ws.get("qkv", T, width, self.dtype), T, allow_partial=FUSE_PARTIALS)
         ops.rope_store_attend(attn, qkv, cos, sin, k_pages, v_pages, view.group, ctx, self.num_heads,
                               k_pages.shape[1], self.head_dim, self.window or 0, self.scale,
                               write_kv=not self.shares_cache,

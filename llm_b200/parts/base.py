@@ -12,10 +12,21 @@ Roles and what each must provide, beyond Part:
              stream's pending term into the residual first.
   mixer      cache_need() / state_need(); forward(x, ctx, view) -> [T, H].
   ffn        forward(x, ctx) -> [T, H].
-  position   a rotation table (tables()) or its own in-place transform (apply()).
+  position   either tables() -> (cos, sin) float32 [max_position, head_dim/2] for the kernels that
+             rotate half a head against the other (fused with the cache store), or apply(q, k,
+             ctx): its own in-place transform of the step's queries [T, heads, head_dim] and new
+             keys [T, kv_heads, head_dim] (views of one buffer), run by the mixer between the
+             projection and the cache store.  A part with neither leaves q and k as they are.
   block      forward(stream, ctx, view): arranges norm / mixer / ffn on the stream.
   embedding  forward(ctx, stream): fills the residual stream from token ids.
-  head       forward(rows, n_rows, ctx) -> float32 logits [R, V].
+  head       logits(stream, ctx, final_norm, buffers) -> float32 logits [R, V] at ctx.logit_rows:
+             everything after the last layer (row gather, final norm, projection, and whatever
+             else a model does to its logits) belongs to this role.
+
+A part whose launches are sized from host-side data of the step (ctx.host_*), so that a captured
+CUDA graph of one step would be wrong for another, says so with is_graph_safe(ctx) -> False; the
+engine then runs that step without capture or replay.  children() names the parts a part is
+built from (the position part inside a mixer), so that the engine can ask them too.
 """
 from __future__ import annotations
 
@@ -79,6 +90,15 @@ class Part:
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         """Receive the tensors named by parameters(), already on the device and in the
         dtype their kind asks for.  Called once."""
+
+    def children(self):
+        """Parts that this part is built from."""
+        return []
+
+    def is_graph_safe(self, ctx) -> bool:
+        """Whether this step's launches of the part depend only on the step's numbers of entries,
+        tokens and wanted rows (and the key bucket), so that a captured graph may be replayed."""
+        return True
 
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {

@@ -53,6 +53,20 @@ class LMHead(Part):
     def forward(self, rows: torch.Tensor, n_rows: int, out: torch.Tensor) -> torch.Tensor:
         return linear(rows, self.weight, out, n_rows)
 
+    def logits(self, stream: ResidualStream, ctx, final_norm, buffers) -> torch.Tensor:
+        """Everything after the last layer: the wanted rows of the stream (with its pending term)
+        are gathered, normalised by final_norm (None: the model has none) and projected.  buffers:
+        (float32 rows, rows in the compute dtype, float32 logits), each with room for
+        ctx.n_logit_rows rows, at addresses that stay fixed between steps."""
+        rows, normed, out = buffers
+        R = ctx.n_logit_rows
+        ops.gather_rows(rows, stream.resid, stream.pending, ctx.logit_rows, R)
+        if final_norm is not None:
+            final_norm.forward_rows(rows, R, normed)
+        else:
+            ops.cast_rows(normed, rows, R)
+        return linear(normed, self.weight, out, R)
+
 
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("head", "lm_head", LMHead)

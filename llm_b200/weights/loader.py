@@ -49,6 +49,18 @@ def _target_dtype(info: ParamInfo, compute_dtype: torch.dtype) -> torch.dtype:
     raise ValueError(f"unknown parameter kind '{info.kind}'")
 
 
+def _harmless_extra(name: str, f: SafetensorsFile, expected: Dict[str, ParamInfo]) -> bool:
+    """Tensors that checkpoints of this family often carry although no part binds them: the
+    rotary inverse-frequency buffers (the tables are rebuilt from rope_theta), and an lm_head.weight
+    beside tied embeddings when it has the embedding's shape.  Everything else that is not
+    expected stays an error."""
+    if name.endswith("rotary_emb.inv_freq"):
+        return True
+    if name == "lm_head.weight" and "model.embed_tokens.weight" in expected:
+        return tuple(f.entries[name].shape) == tuple(expected["model.embed_tokens.weight"].shape)
+    return False
+
+
 def load_tensors(model_dir: str, expected: Dict[str, ParamInfo], compute_dtype: torch.dtype,
                  device: torch.device) -> Dict[str, torch.Tensor]:
     """Read, validate, convert and move every expected tensor."""
@@ -57,7 +69,7 @@ def load_tensors(model_dir: str, expected: Dict[str, ParamInfo], compute_dtype: 
         raise SafetensorsError(f"{path}: no {WEIGHTS_FILE} in the model folder")
     f = SafetensorsFile(path)
     missing = sorted(n for n in expected if n not in f.entries)
-    unexpected = sorted(n for n in f.entries if n not in expected)
+    unexpected = sorted(n for n in f.entries if n not in expected and not _harmless_extra(n, f, expected))
     wrong = []
     for name, info in expected.items():
         e = f.entries.get(name)

@@ -151,3 +151,26 @@ def test_loaded_dtypes(tmp_path):
     t32 = load_tensors(d, expected_tensors(CONFIG_A), torch.float32, torch.device("cpu"))
     assert t32["lm_head.weight"].dtype == torch.float32
     assert torch.equal(t32["lm_head.weight"], t["lm_head.weight"].float())
+
+
+def test_buffers_that_checkpoints_carry_are_not_an_error(tmp_path):
+    """Rotary inverse-frequency buffers and an lm_head.weight beside tied embeddings load; any other
+    extra tensor is still refused."""
+    from llm_b200.weights import SafetensorsFile, WeightError, load_tensors, write_random_model, write_safetensors
+    from llm_b200.weights.loader import expected_tensors
+    from tiny import CONFIG_C
+    d = write_random_model(str(tmp_path / "m"), CONFIG_C, 1, "float32")            # tied embeddings
+    path = os.path.join(d, "model.safetensors")
+    f = SafetensorsFile(path)
+    t = {n: f.tensor(n).clone() for n in f.names()}
+    f.close()
+    t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(24)
+    t["lm_head.weight"] = t["model.embed_tokens.weight"].clone()
+    write_safetensors(path, t)
+    got = load_tensors(d, expected_tensors(CONFIG_C), torch.float32, torch.device("cpu"))
+    assert set(got) == set(expected_tensors(CONFIG_C))
+    t["lm_head.bias"] = torch.zeros(301)
+    write_safetensors(path, t)
+    with pytest.raises(WeightError) as ei:
+        load_tensors(d, expected_tensors(CONFIG_C), torch.float32, torch.device("cpu"))
+    assert ei.value.unexpected == ["lm_head.bias"]

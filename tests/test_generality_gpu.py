@@ -42,6 +42,9 @@ def _register_toy():
         def state_need(self):
             return StateNeed((self.hidden_size + 1,), torch.float32)     # running sum and count
 
+        def is_graph_safe(self, ctx):
+            return False                   # the loop below follows the step's host-side sizes
+
         def forward(self, x, ctx, view):
             T = ctx.n_tokens
             means = torch.empty((T, self.hidden_size), dtype=torch.float32, device=x.device)
@@ -151,7 +154,7 @@ def test_toy_mixer_with_state_repeated_layers_and_shared_cache(tmp_path, dtype):
     reqs = {f"t{i}": random_tokens(n, TOY["vocab_size"], 300 + i) for i, n in enumerate([4, 31, 19, 50])}
     ref = {rid: plain_toy(TOY, w_ffn, toks) for rid, toks in reqs.items()}
     eng = Engine(d, EngineOptions(dtype=dtype, kv_block_size=8, max_num_seqs=4, max_num_batched_tokens=64,
-                                  num_kv_blocks=24, use_cuda_graphs=False))
+                                  num_kv_blocks=24, use_cuda_graphs=True))      # the toy mixer itself keeps its steps out of graphs
     model = eng.model
     assert len(model.state_needs) == 2                      # the toy layer runs twice: two states
     assert len(model.cache_instances) == 3                  # layer 0 twice, layer 2 once, none for the sharer
@@ -192,6 +195,9 @@ def _register_toy_routed():
             self.router = tensors[self.name("router.weight")].float()
             self.w1 = [tensors[self.name(f"experts.{k}.w1.weight")] for k in range(self.e)]
             self.w2 = [tensors[self.name(f"experts.{k}.w2.weight")] for k in range(self.e)]
+
+        def is_graph_safe(self, ctx):
+            return False                   # which rows go to which expert is decided on the host
 
         def forward(self, x, ctx):
             T = ctx.n_tokens
@@ -345,7 +351,7 @@ def test_toy_routed_feed_forward_position_encoding_and_block():
                 used |= set(c.tolist())
         assert len(used) == TOY_ROUTED["experts"]                 # the random router spreads the tokens over all experts
         eng = Engine(d, EngineOptions(dtype="float32", kv_block_size=16, max_num_seqs=4, max_num_batched_tokens=96,
-                                      num_kv_blocks=16, use_cuda_graphs=False))
+                                      num_kv_blocks=16, use_cuda_graphs=True))
         for what, steps in (("whole", replay.steps_whole(reqs)), ("portions", replay.steps_portions(reqs)),
                             ("mixed", replay.steps_mixed(reqs))):
             got = replay.run_steps(eng, steps)
@@ -353,3 +359,213 @@ def test_toy_routed_feed_forward_position_encoding_and_block():
                 err = float((got[rid].double() - ref[rid]).abs().max() / ref[rid].abs().max())
                 assert err < TOL["float32"], (what, rid, err)
             eng.cache.check()
+
+
+# ---- a position encoding with a transform of its own, a head that owns everything after the last
+# ---- layer (no final norm, capped logits), and a part that says it must not be captured in a graph
+def _register_toy_positions_and_head():
+    from llm_b200.config.model_config import register_architecture
+    from llm_b200.csrc import ops
+    from llm_b200.models.spec import LayerSpec, ModelSpec, PartSpec
+    from llm_b200.parts.base import ParamInfo, Part, register_part
+    from llm_b200.parts.linear import linear
+
+    class PairwisePartialRotary(Part):
+        """Rotates the first `rotary_dim` dims of every head in neighbouring pairs (2i, 2i+1) by
+        pos * theta^(-2i/rotary_dim) and leaves the rest: neither a table for the built-in kernels
+        nor their pairing, so it brings apply()."""
+        role = "position"
+
+        def __init__(self, rotary_dim, theta, prefix="", dtype=None, device=None):
+            super().__init__(prefix, dtype, device)
+            self.rotary_dim, self.theta = rotary_dim, float(theta)
+            self.inv = torch.pow(torch.tensor(self.theta, dtype=torch.float64),
+                                 -torch.arange(0, rotary_dim, 2, dtype=torch.float64) / rotary_dim).to(device)
+
+        def apply(self, q, k, ctx):
+            T = ctx.n_tokens
+            pos = ctx.positions[:T].double()
+            ang = pos[:, None] * self.inv[None]
+            cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+            for x in (q, k):
+                if x is None:
+                    continue
+                a, b = x[:T, :, 0:self.rotary_dim:2].double(), x[:T, :, 1:self.rotary_dim:2].double()
+                x[:T, :, 0:self.rotary_dim:2] = (a * cos - b * sin).to(x.dtype)
+                x[:T, :, 1:self.rotary_dim:2] = (a * sin + b * cos).to(x.dtype)
+
+    register_part("position", "pairwise_partial_rotary", PairwisePartialRotary)
+
+    class CappedHead(Part):
+        """logits = cap * tanh(rows W^T / cap) on the stream as the last layer left it: no norm."""
+        role = "head"
+
+        def __init__(self, hidden_size, vocab_size, cap, prefix="", dtype=None, device=None):
+            super().__init__(prefix, dtype, device)
+            self.h, self.v, self.cap = hidden_size, vocab_size, float(cap)
+
+        def parameters(self):
+            return {self.name("weight"): ParamInfo((self.v, self.h))}
+
+        def bind(self, tensors):
+            self.weight = tensors[self.name("weight")].contiguous()
+
+        def logits(self, stream, ctx, final_norm, buffers):
+            assert final_norm is None
+            rows, cast, out = buffers
+            R = ctx.n_logit_rows
+            ops.gather_rows(rows, stream.resid, stream.pending, ctx.logit_rows, R)
+            ops.cast_rows(cast, rows, R)
+            linear(cast, self.weight, out, R)
+            out[:R] = self.cap * torch.tanh(out[:R] / self.cap)
+            return out
+
+    register_part("head", "capped_head", CappedHead)
+
+    class HostSizedFeedForward(Part):
+        """relu(x W1^T) W2^T, computed entry by entry from the step's host-side sizes: a captured
+        graph of one step would be wrong for a step that cuts the tokens differently, so it says so."""
+        role = "ffn"
+
+        def __init__(self, hidden_size, inner_size, prefix="", dtype=None, device=None):
+            super().__init__(prefix, dtype, device)
+            self.h, self.i = hidden_size, inner_size
+
+        def parameters(self):
+            return {self.name("w1.weight"): ParamInfo((self.i, self.h)), self.name("w2.weight"): ParamInfo((self.h, self.i))}
+
+        def bind(self, tensors):
+            self.w1, self.w2 = tensors[self.name("w1.weight")], tensors[self.name("w2.weight")]
+
+        def is_graph_safe(self, ctx):
+            return False
+
+        def forward(self, x, ctx):
+            out = ctx.workspace.get("toy_host_ffn", ctx.n_tokens, self.h, self.dtype)
+            at = 0
+            for n in ctx.host_entry_tokens.tolist():
+                hid = torch.relu(x[at:at + n].float() @ self.w1.float().T)
+                out[at:at + n] = (hid @ self.w2.float().T).to(self.dtype)
+                at += n
+            return out
+
+    register_part("ffn", "host_sized", HostSizedFeedForward)
+
+    class Cfg:
+        def __init__(self, d):
+            self.d = d
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+    def build_spec(cfg):
+        d = cfg.d
+        H, V = d["hidden_size"], d["vocab_size"]
+        norm = lambda p: PartSpec("rmsnorm", {"size": H, "eps": 1e-5}, p)
+        pos = PartSpec("pairwise_partial_rotary", {"rotary_dim": d["rotary_dim"], "theta": 5000.0})
+        layers = []
+        for i in range(d["layers"]):
+            p = f"toy.layers.{i}"
+            mixer = PartSpec("attention", {"hidden_size": H, "num_heads": d["heads"], "num_kv_heads": d["kv_heads"],
+                                           "head_dim": d["head_dim"], "position": pos}, p + ".attn")
+            ffn = (PartSpec("host_sized", {"hidden_size": H, "inner_size": 2 * H}, p + ".ffn") if d["host_sized_ffn"]
+                   else PartSpec("swiglu", {"hidden_size": H, "intermediate_size": 2 * H}, p + ".ffn"))
+            layers.append(LayerSpec("prenorm", {"norm1": norm(p + ".n1"), "mixer": mixer, "norm2": norm(p + ".n2"), "ffn": ffn}))
+        return ModelSpec(hidden_size=H, vocab_size=V, max_position=d["max_position"],
+                         embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, "toy.embed"),
+                         layers=tuple(layers), order=tuple(range(len(layers))), final_norm=None,
+                         head=PartSpec("capped_head", {"hidden_size": H, "vocab_size": V, "cap": d["cap"]}, "toy.head"))
+
+    register_architecture("ToyPositionsHeadForTest", Cfg, build_spec)
+
+
+TOY_POS = dict(architectures=["ToyPositionsHeadForTest"], hidden_size=128, vocab_size=203, head_dim=64, heads=4, kv_heads=2,
+               rotary_dim=24, layers=2, max_position=320, cap=0.05, host_sized_ffn=False)
+
+
+def plain_toy_positions(cfg, w, ids):
+    import plain_llama as pl
+    H, HS, NH, NKV, R = cfg["hidden_size"], cfg["head_dim"], cfg["heads"], cfg["kv_heads"], cfg["rotary_dim"]
+    T = len(ids)
+    f = lambda n: w[n].double()
+    x = f("toy.embed.weight")[torch.tensor(ids)]
+    inv = torch.pow(torch.tensor(5000.0, dtype=torch.float64), -torch.arange(0, R, 2, dtype=torch.float64) / R)
+    ang = torch.arange(T, dtype=torch.float64)[:, None] * inv[None]
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def rotate(t):
+        t = t.clone()
+        a, b = t[:, :, 0:R:2].clone(), t[:, :, 1:R:2].clone()
+        t[:, :, 0:R:2], t[:, :, 1:R:2] = a * cos - b * sin, a * sin + b * cos
+        return t
+
+    for i in range(cfg["layers"]):
+        p = f"toy.layers.{i}"
+        n = pl.rmsnorm(x, f(p + ".n1.weight"), 1e-5)
+        q = rotate((n @ f(p + ".attn.q_proj.weight").T).view(T, NH, HS))
+        k = rotate((n @ f(p + ".attn.k_proj.weight").T).view(T, NKV, HS))
+        v = (n @ f(p + ".attn.v_proj.weight").T).view(T, NKV, HS)
+        x = x + pl.attention(q, k, v).reshape(T, NH * HS) @ f(p + ".attn.o_proj.weight").T
+        m = pl.rmsnorm(x, f(p + ".n2.weight"), 1e-5)
+        if cfg["host_sized_ffn"]:
+            x = x + torch.relu(m @ f(p + ".ffn.w1.weight").T) @ f(p + ".ffn.w2.weight").T
+        else:
+            x = x + (pl.silu(m @ f(p + ".ffn.gate_proj.weight").T) * (m @ f(p + ".ffn.up_proj.weight").T)) @ f(p + ".ffn.down_proj.weight").T
+    return cfg["cap"] * torch.tanh((x @ f("toy.head.weight").T) / cfg["cap"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_position_transform_and_head_without_final_norm(dtype):
+    """A position encoding that is no table for the built-in kernels (its own apply() between the
+    projection and the cache store) and a head that does everything after the last layer itself
+    (no final norm, capped logits), defined here, through the unchanged engine with CUDA graphs
+    on: prompts in portions (the tensor-core attention in bfloat16) and decoded tokens."""
+    import tempfile
+    import replay
+    from llm_b200.config import EngineOptions
+    from llm_b200.engine.engine import Engine
+    from llm_b200.weights.loader import write_random_model
+    from tiny import load_plain_weights
+    _register_toy_positions_and_head()
+    with tempfile.TemporaryDirectory() as tmp:
+        d = write_random_model(os.path.join(tmp, "toy_pos"), TOY_POS, 9, dtype)
+        w = load_plain_weights(d)
+        reqs = {f"p{i}": random_tokens(n, TOY_POS["vocab_size"], 800 + i) for i, n in enumerate([5, 150, 47, 290])}
+        ref = {rid: plain_toy_positions(TOY_POS, w, toks) for rid, toks in reqs.items()}
+        eng = Engine(d, EngineOptions(dtype=dtype, kv_block_size=16, max_num_seqs=4, max_num_batched_tokens=320,
+                                      num_kv_blocks=40, use_cuda_graphs=True))
+        for what, steps in (("whole", replay.steps_whole(reqs)), ("tail decode", replay.steps_tail_decode(reqs)),
+                            ("mixed", replay.steps_mixed(reqs))):
+            got = replay.run_steps(eng, steps)
+            for rid in reqs:
+                err = float((got[rid].double() - ref[rid]).abs().max() / ref[rid].abs().max())
+                assert err < TOL[dtype], (what, rid, err)
+        assert eng.counters["graph_replays"] > 0           # every part here is safe to capture
+        eng.cache.check()
+
+
+def test_a_part_that_is_not_graph_safe_turns_capture_off_by_itself():
+    """The feed-forward of this model sizes its work from the step's host-side data and says so:
+    with CUDA graphs on for the engine, no step is captured or replayed, and the logits are right
+    however the tokens are cut (a replayed graph would repeat the first step's cut)."""
+    import tempfile
+    import replay
+    from llm_b200.config import EngineOptions
+    from llm_b200.engine.engine import Engine
+    from llm_b200.weights.loader import write_random_model
+    from tiny import load_plain_weights
+    _register_toy_positions_and_head()
+    cfg = dict(TOY_POS, host_sized_ffn=True)
+    with tempfile.TemporaryDirectory() as tmp:
+        d = write_random_model(os.path.join(tmp, "toy_host"), cfg, 10, "float32")
+        w = load_plain_weights(d)
+        reqs = {f"h{i}": random_tokens(n, cfg["vocab_size"], 900 + i) for i, n in enumerate([40, 9, 66])}
+        ref = {rid: plain_toy_positions(cfg, w, toks) for rid, toks in reqs.items()}
+        eng = Engine(d, EngineOptions(dtype="float32", kv_block_size=16, max_num_seqs=4, max_num_batched_tokens=96,
+                                      num_kv_blocks=16, use_cuda_graphs=True))
+        for steps in (replay.steps_tail_decode(reqs), replay.steps_mixed(reqs)):
+            got = replay.run_steps(eng, steps)
+            for rid in reqs:
+                assert float((got[rid].double() - ref[rid]).abs().max() / ref[rid].abs().max()) < TOL["float32"]
+        assert eng.counters["graph_captures"] == 0 and eng.counters["graph_replays"] == 0

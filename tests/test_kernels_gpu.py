@@ -642,6 +642,33 @@ def test_decode_attention_with_more_ctas_than_one_wave(ops, fused, B, NH, NKV, H
     assert float(err.max()) < 1e-2, f"entry {int(err.argmax())} of length {lens[int(err.argmax())]}: {float(err.max()):.3e}"
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("HS,splits", [(64, 1), (64, 3), (128, 12), (48, 2)])
+def test_decode_attention_with_an_entry_that_holds_no_keys(ops, dtype, HS, splits):
+    """The C entry points take lengths from device memory: an entry of length 0 gets zeros (and
+    holds nobody up), one whose length exceeds its table row is cut to the row."""
+    torch.manual_seed(31)
+    NH, NKV, page = 8, 2, 16
+    lens = [0, 37, 0, 90, 1]
+    given = [0, 37, -3, 90 + 1000, 1]               # what the kernel is told: 90 + 1000 is cut to the row's 96 keys
+    W = 6
+    n_pages = 5 * W
+    kp = torch.randn(n_pages, NKV, page, HS, device=DEV).to(dtype)
+    vp = torch.randn(n_pages, NKV, page, HS, device=DEV).to(dtype)
+    bt = torch.randperm(n_pages)[:5 * W].view(5, W).to(torch.int32)
+    lens[3] = W * page
+    q = torch.randn(5, NH * HS, device=DEV).to(dtype)
+    out = torch.full((5, NH * HS), 7.0, device=DEV, dtype=dtype)
+    ops.paged_attention_decode(out, q, kp, vp, bt.to(DEV), torch.tensor(given, dtype=torch.int32, device=DEV), 5, NH, NKV,
+                               HS, 0, 0.2, splits=splits)
+    ref = _plain_decode_attention(q, kp, vp, bt, [max(n, 1) for n in lens], NH, NKV, HS, page, 0, 0.2)
+    for e, n in enumerate(lens):
+        if n == 0:
+            assert float(out[e].abs().max()) == 0.0
+        else:
+            assert rel_err(out[e], ref[e]) < (2e-6 if dtype == torch.float32 else 1e-2)
+
+
 def test_decode_attention_fused_refuses_other_sizes(ops):
     cos = torch.ones(8, 24, device=DEV)
     assert not ops.decode_attention_fused_supported(torch.zeros(2, 48 * 3, device=DEV, dtype=torch.bfloat16), cos, cos, 48)
