@@ -37,7 +37,9 @@ def _take(d: Dict[str, Any], key: str, kind, default=_MISSING):
 @dataclass(frozen=True)
 class LlamaConfig:
     """config.json of a LlamaForCausalLM folder (pre-norm, RMSNorm, GQA with
-    rotate-half RoPE, SwiGLU, no biases)."""
+    rotate-half RoPE, SwiGLU; biases on the attention and feed-forward projections if
+    attention_bias / mlp_bias say so, as the reference's modules take them,
+    model/modules/Attention.h:16-19, MLP.h:9-13)."""
 
     architecture: str
     hidden_size: int
@@ -52,6 +54,8 @@ class LlamaConfig:
     max_position_embeddings: int
     tie_word_embeddings: bool = False
     hidden_act: str = "silu"
+    attention_bias: bool = False
+    mlp_bias: bool = False
     sliding_window: Optional[int] = None
     bos_token_id: Optional[int] = None
     eos_token_id: Optional[int] = None
@@ -92,6 +96,8 @@ class LlamaConfig:
             max_position_embeddings=_take(d, "max_position_embeddings", int),
             tie_word_embeddings=_take(d, "tie_word_embeddings", bool, False),
             hidden_act=_take(d, "hidden_act", str, "silu"),
+            attention_bias=_take(d, "attention_bias", bool, False),
+            mlp_bias=_take(d, "mlp_bias", bool, False),
             sliding_window=_take(d, "sliding_window", int, None),
             bos_token_id=_take(d, "bos_token_id", int, None),
             eos_token_id=eos,
@@ -99,9 +105,6 @@ class LlamaConfig:
         )
         if d.get("rope_scaling") is not None:
             raise ConfigError("config.json: rope_scaling is not supported (must be null or absent)")
-        for key in ("attention_bias", "mlp_bias"):
-            if d.get(key):
-                raise ConfigError(f"config.json: {key}=true is not supported")
         cfg.validate()
         return cfg
 

@@ -50,6 +50,15 @@ __device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* __restrict_
   return s;
 }
 
+// a row that does not start on a 16-byte boundary, or is no whole number of 16-byte pieces
+// (head sizes off the 8-grid in bfloat16, off the 4-grid in float32): element by element
+template <typename T>
+__device__ __forceinline__ float dot_row_scalar(const float* __restrict__ q, const T* __restrict__ k, int head_dim) {
+  float s = 0.f;
+  for (int d = 0; d < head_dim; ++d) s = fmaf(q[d], to_f32(k[d]), s);
+  return s;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const T* __restrict__ q,
@@ -57,7 +66,7 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
                                const T* __restrict__ v_pages, const int* __restrict__ block_table,
                                int table_width, const int* __restrict__ token_entry,
                                const int* __restrict__ positions, int n_tokens, int n_heads, int n_kv,
-                               int head_dim, int page_size, int window, float scale) {
+                               int head_dim, int page_size, int window, float scale, bool vec) {
   __shared__ float q_s[WARPS][MAX_HEAD_DIM];
   pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
@@ -87,7 +96,7 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
     if (valid) {
       const int page = table[kp / page_size];
       row = (((long long)page * n_kv + g) * page_size + kp % page_size) * head_dim;
-      s = dot_row<T>(q_s[warp], k_pages + row, head_dim) * scale;
+      s = (vec ? dot_row<T>(q_s[warp], k_pages + row, head_dim) : dot_row_scalar<T>(q_s[warp], k_pages + row, head_dim)) * scale;
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float alpha = expf(m - m_new);  // m = -inf at the first tile gives 0
@@ -130,8 +139,7 @@ LLMK_API int llmk_paged_attention_generic(void* out, long long out_stride, const
                                           int n_tokens, int n_heads, int n_kv, int head_dim, int page_size,
                                           int window, float scale, int dtype, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  LLMK_REQUIRE(head_dim > 0 && head_dim % 16 == 0 && head_dim <= MAX_HEAD_DIM,
-               "paged_attention: head_dim %d must be a multiple of 16 up to %d", head_dim, MAX_HEAD_DIM);
+  LLMK_REQUIRE(head_dim > 0 && head_dim <= MAX_HEAD_DIM, "paged_attention: head_dim %d must be 1 to %d", head_dim, MAX_HEAD_DIM);
   LLMK_REQUIRE(n_kv > 0 && n_heads % n_kv == 0, "paged_attention: %d query heads do not divide into %d kv heads",
                n_heads, n_kv);
   LLMK_REQUIRE(page_size > 0 && window >= 0, "paged_attention: bad page_size %d or window %d", page_size, window);
@@ -140,9 +148,10 @@ LLMK_API int llmk_paged_attention_generic(void* out, long long out_stride, const
   LLMK_REQUIRE(blocks < (1ll << 31), "paged_attention: too many (token, head) items");
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
+    const bool vec = head_dim % (16 / (int)sizeof(T)) == 0 && (uintptr_t)k_pages % 16 == 0;      // whole 16-byte pieces per key row
     launch_kernel(paged_attention_generic_kernel<T>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
         (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
-        table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, page_size, window, scale);
+        table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, page_size, window, scale, vec);
     LLMK_LAUNCH_CHECK("paged_attention_generic");
   });
 }

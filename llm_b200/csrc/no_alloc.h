@@ -19,8 +19,8 @@ extern "C" {
 // 4096 + n_entries * n_heads * splits * (head_dim + 2) floats.
 #define LLMK_DECODE_STATIC_SCRATCH_FLOATS (1 << 20)
 
-// Same computation and arguments as llmk_paged_attention_decode, without the two scratch
-// pointers: the partial results of the key ranges live in a fixed array inside the library
+// Same computation and arguments as llmk_paged_attention_decode, without its scratch
+// pointer: the partial results of the key ranges live in a fixed array inside the library
 // (every GPU that loads the library holds those 4 MiB until the process exits).
 //
 // * Allocates nothing: no cudaMalloc / cudaFree, no allocating library routine.

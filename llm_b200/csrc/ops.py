@@ -152,6 +152,14 @@ def cast_rows(out: torch.Tensor, rows_f32: torch.Tensor, n_rows: int) -> None:
                                  _stream()))
 
 
+def add_bias(x: torch.Tensor, bias: torch.Tensor, rows: int) -> None:
+    """x[:rows] += bias (float32 [cols]), in place."""
+    _rows_contig(x, "x")
+    assert bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == x.shape[1]
+    _check(load().llmk_add_bias(_ptr(x), c_longlong(x.stride(0)), _ptr(bias), c_int(rows), c_int(x.shape[1]),
+                                c_int(_kind(x.dtype)), _stream()))
+
+
 def silu_mul(out: torch.Tensor, gate_up, rows: int) -> None:
     """out[:rows, :I] = silu(gate_up[:, :I]) * gate_up[:, I:]; gate_up a tensor or a PartialSum."""
     inter = out.shape[-1]
@@ -372,8 +380,9 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
     """Attention of the step's tokens over their requests' pages; q is the first
     n_heads * head_dim columns of qkv.  Chooses the kernel for the batch: in bfloat16 the
     split-key decode kernel when every entry brings one token and the tcgen05 kernel otherwise,
-    where it takes the sizes; the general kernel for float32 and for all other sizes."""
-    if ctx.decode_only and qkv.dtype == torch.bfloat16:
+    where it takes the sizes; the general kernel for float32 and for all other sizes (head sizes
+    off the 16-grid among them)."""
+    if ctx.decode_only and qkv.dtype == torch.bfloat16 and head_dim % 16 == 0:
         max_keys = min(ctx.kv_bucket or 1 << 30, group.block_table.shape[1] * k_pages.shape[2])
         if window:
             max_keys = min(max_keys, window)

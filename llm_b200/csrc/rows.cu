@@ -172,6 +172,33 @@ LLMK_API int llmk_cast_rows(void* out, const float* in, long long n, int dtype, 
   });
 }
 
+// x[r, c] += bias[c] (float32 sum, rounded once): the bias of a projection whose product is
+// already summed.  The reference adds it in its products' epilogues (kernel/Gemm/QKVGemm.h:27-45,
+// model/modules/Linear.h:12-34).
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ x, long long stride, const float* __restrict__ bias, int rows, int cols) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t total = (size_t)rows * cols;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / cols;
+    const int c = (int)(i - r * cols);
+    T* p = x + r * stride + c;
+    *p = from_f32<T>(to_f32(*p) + bias[c]);
+  }
+}
+
+LLMK_API int llmk_add_bias(void* x, long long stride, const float* bias, int rows, int cols, int dtype, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  size_t blocks = ((size_t)rows * cols + 255) / 256;
+  if (blocks > (size_t)llmk_sm_count() * 16) blocks = (size_t)llmk_sm_count() * 16;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    launch_kernel(add_bias_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)x, stride, bias, rows, cols);
+    LLMK_LAUNCH_CHECK("add_bias");
+  });
+}
+
 // ---- SiLU(gate) * up --------------------------------------------------------
 // in [rows, 2*inter]: gate in the first half of a row, up in the second.
 // act = g / (1 + exp(-g)) * u in float32 (kernel/activation/SwiGLU.h:31-33).

@@ -25,9 +25,10 @@ def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
             "head_dim": cfg.head_dim,
             "window": cfg.sliding_window,
             "position": position,
+            "bias": cfg.attention_bias,
         }, p + ".self_attn")
         ffn = PartSpec("swiglu", {"hidden_size": cfg.hidden_size,
-                                  "intermediate_size": cfg.intermediate_size}, p + ".mlp")
+                                  "intermediate_size": cfg.intermediate_size, "bias": cfg.mlp_bias}, p + ".mlp")
         layers.append(LayerSpec("prenorm", {
             "norm1": norm(p + ".input_layernorm"),
             "mixer": mixer,

@@ -23,13 +23,13 @@ class PagedAttention(Part):
     role = "mixer"
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, position=None,
-                 window=None, scale=None, shares_cache: bool = False, prefix: str = "", dtype=None,
-                 device=None):
+                 window=None, scale=None, shares_cache: bool = False, bias: bool = False, prefix: str = "",
+                 dtype=None, device=None):
         super().__init__(prefix, dtype, device)
         if num_heads % num_kv_heads:
             raise ValueError(f"attention: {num_heads} heads do not divide into {num_kv_heads} kv heads")
-        if head_dim % 16 or head_dim > 256:
-            raise ValueError(f"attention: head_dim {head_dim} must be a multiple of 16 up to 256")
+        if head_dim <= 0 or head_dim > 256:
+            raise ValueError(f"attention: head_dim {head_dim} must be 1 to 256")
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
         self.window = int(window) if window else None
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
@@ -37,8 +37,11 @@ class PagedAttention(Part):
         self.position = build_part("position", position, dtype, device) if position is not None else None
         self.q_size = num_heads * head_dim
         self.kv_size = 0 if shares_cache else num_kv_heads * head_dim
+        self.bias = bool(bias)        # q/k/v and o projections carry bias vectors (model/modules/Attention.h:16-19)
         self.w_qkv = None
         self.w_o = None
+        self.b_qkv = None
+        self.b_o = None
 
     def parameters(self):
         p = {self.name("q_proj.weight"): ParamInfo((self.q_size, self.hidden_size))}
@@ -46,6 +49,12 @@ class PagedAttention(Part):
             p[self.name("k_proj.weight")] = ParamInfo((self.kv_size, self.hidden_size))
             p[self.name("v_proj.weight")] = ParamInfo((self.kv_size, self.hidden_size))
         p[self.name("o_proj.weight")] = ParamInfo((self.hidden_size, self.q_size))
+        if self.bias:
+            p[self.name("q_proj.bias")] = ParamInfo((self.q_size,), kind="gain", init="normal")
+            if not self.shares_cache:
+                p[self.name("k_proj.bias")] = ParamInfo((self.kv_size,), kind="gain", init="normal")
+                p[self.name("v_proj.bias")] = ParamInfo((self.kv_size,), kind="gain", init="normal")
+            p[self.name("o_proj.bias")] = ParamInfo((self.hidden_size,), kind="gain", init="normal")
         return p
 
     def bind(self, tensors):
@@ -54,6 +63,10 @@ class PagedAttention(Part):
             parts += [tensors[self.name("k_proj.weight")], tensors[self.name("v_proj.weight")]]
         self.w_qkv = torch.cat(parts, dim=0).contiguous() if len(parts) > 1 else parts[0].contiguous()
         self.w_o = tensors[self.name("o_proj.weight")].contiguous()
+        if self.bias:
+            names = ["q_proj.bias"] + ([] if self.shares_cache else ["k_proj.bias", "v_proj.bias"])
+            self.b_qkv = torch.cat([tensors[self.name(n)] for n in names]).contiguous()
+            self.b_o = tensors[self.name("o_proj.bias")].contiguous()
 
     def cache_need(self):
         if self.shares_cache:
@@ -82,11 +95,14 @@ class PagedAttention(Part):
         if own_transform is not None:
             # a position part with a transform of its own: it runs on the summed projection, between
             # the product and the cache store; the kernels after it neither rotate nor sum
-            qkv = linear(x, self.w_qkv, ws.get("qkv", T, width, self.dtype), T)
+            qkv = linear(x, self.w_qkv, ws.get("qkv", T, width, self.dtype), T, bias=self.b_qkv)
             q_view = qkv[:, :self.q_size].view(T, self.num_heads, self.head_dim)
             k_view = (qkv[:, self.q_size:self.q_size + self.kv_size].view(T, -1, self.head_dim)
                       if self.kv_size else None)
             own_transform(q_view, k_view, ctx)
+        elif self.bias:
+            # biased projections: the product is summed and the bias added before rotation and store
+            qkv = linear(x, self.w_qkv, ws.get("qkv", T, width, self.dtype), T, bias=self.b_qkv)
         else:
             # many rows: one kernel projects, rotates and stores; then the attention over the pages
             q = ops.qkv_rope_store(x, self.w_qkv, lambda: ws.get("q_rot", T, self.q_size, self.dtype), T, cos, sin,
@@ -101,7 +117,8 @@ class PagedAttention(Part):
                               k_pages.shape[1], self.head_dim, self.window or 0, self.scale,
                               write_kv=not self.shares_cache,
                               q_rot=lambda: ws.get("q_rot", T, self.q_size, self.dtype))
-        return linear(attn, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
+        return linear(attn, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS,
+                      bias=self.b_o)
 
 
 register_part("mixer", "attention", PagedAttention)

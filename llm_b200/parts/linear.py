@@ -19,18 +19,27 @@ from ..csrc import ops
 FUSE_PARTIALS = True
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int, allow_partial: bool = False):
-    """out[:rows] = x[:rows] @ weight.T; out may be float32 for bfloat16 inputs.
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int, allow_partial: bool = False,
+           bias: torch.Tensor = None):
+    """out[:rows] = x[:rows] @ weight.T (+ bias, float32 [out features]); out may be float32 for
+    bfloat16 inputs.  With a bias the product is summed into `out` and the bias added there by a
+    kernel of its own (the reference adds it in the product's epilogue, model/modules/Linear.h:12-34).
 
     With allow_partial the result may come back as an ops.PartialSum (a split-K product whose
     partial results are still to be summed) instead of in `out`: pass it straight to a kernel
     that takes one (add_rmsnorm, silu_mul, rope_kv_write, gather_rows), before any other product."""
     if rows == 0:
         return out
+    if bias is not None:
+        allow_partial = False
     if x.dtype == torch.bfloat16 and ops.gemm_fast_available(x, weight, out, rows):
-        return ops.gemm_fast(x, weight, out, rows, allow_partial=allow_partial)
-    ops.gemm_simt(x, weight, out, rows)
-    return out
+        res = ops.gemm_fast(x, weight, out, rows, allow_partial=allow_partial)
+    else:
+        ops.gemm_simt(x, weight, out, rows)
+        res = out
+    if bias is not None:
+        ops.add_bias(out, bias, rows)
+    return res
 
 
 def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int) -> bool:

@@ -79,18 +79,25 @@ def attention(q, k, v, window: int | None = None, scale: float | None = None):
     return out
 
 
+def project(x, w, name, bias=False):
+    """x W^T (+ b): the bias is added to the sum before anything else happens to it, rotation
+    included (model/modules/Linear.h:12-34; kernel/Gemm/QKVGemm.h:27-45)."""
+    y = x @ w[name + ".weight"].to(F64).T
+    return y + w[name + ".bias"].to(F64) if bias else y
+
+
 def attention_part(n, w, prefix, cfg, positions):
     """q/k/v projections, RoPE on q and k, attention, output projection
     (model/modules/Attention.h:16-19; model/modules/QKVLinear.h:20-33)."""
     T = n.shape[0]
     NH, NKV, HS = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
-    q = (n @ w[prefix + ".q_proj.weight"].to(F64).T).view(T, NH, HS)
-    k = (n @ w[prefix + ".k_proj.weight"].to(F64).T).view(T, NKV, HS)
-    v = (n @ w[prefix + ".v_proj.weight"].to(F64).T).view(T, NKV, HS)
+    q = project(n, w, prefix + ".q_proj", cfg.get("attention_bias")).view(T, NH, HS)
+    k = project(n, w, prefix + ".k_proj", cfg.get("attention_bias")).view(T, NKV, HS)
+    v = project(n, w, prefix + ".v_proj", cfg.get("attention_bias")).view(T, NKV, HS)
     cos, sin = rope_tables(positions, HS, cfg["rope_theta"])
     q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
     o = attention(q, k, v, window=cfg.get("sliding_window"))
-    return o.reshape(T, NH * HS) @ w[prefix + ".o_proj.weight"].to(F64).T
+    return project(o.reshape(T, NH * HS), w, prefix + ".o_proj", cfg.get("attention_bias"))
 
 
 def silu(a: torch.Tensor) -> torch.Tensor:
@@ -98,11 +105,11 @@ def silu(a: torch.Tensor) -> torch.Tensor:
     return a / (1.0 + torch.exp(-a))
 
 
-def swiglu_mlp(m, w, prefix):
+def swiglu_mlp(m, w, prefix, bias=False):
     """down( silu(gate(m)) * up(m) )  (model/modules/MLP.h:10-13)."""
-    g = m @ w[prefix + ".gate_proj.weight"].to(F64).T
-    u = m @ w[prefix + ".up_proj.weight"].to(F64).T
-    return (silu(g) * u) @ w[prefix + ".down_proj.weight"].to(F64).T
+    g = project(m, w, prefix + ".gate_proj", bias)
+    u = project(m, w, prefix + ".up_proj", bias)
+    return project(silu(g) * u, w, prefix + ".down_proj", bias)
 
 
 def block(x, w, layer: int, cfg, positions):
@@ -113,7 +120,7 @@ def block(x, w, layer: int, cfg, positions):
     n = rmsnorm(x, w[p + ".input_layernorm.weight"], eps)
     x = x + attention_part(n, w, p + ".self_attn", cfg, positions)
     m = rmsnorm(x, w[p + ".post_attention_layernorm.weight"], eps)
-    return x + swiglu_mlp(m, w, p + ".mlp")
+    return x + swiglu_mlp(m, w, p + ".mlp", cfg.get("mlp_bias"))
 
 
 def normalise_config(cfg: dict) -> dict:

@@ -174,3 +174,19 @@ def test_buffers_that_checkpoints_carry_are_not_an_error(tmp_path):
     with pytest.raises(WeightError) as ei:
         load_tensors(d, expected_tensors(CONFIG_C), torch.float32, torch.device("cpu"))
     assert ei.value.unexpected == ["lm_head.bias"]
+
+
+def test_bias_flags_add_bias_tensors():
+    from llm_b200.config import parse_config
+    from llm_b200.weights.loader import expected_tensors
+    from tiny import CONFIG_F, CONFIG_G
+    _, cfg = parse_config(CONFIG_F)
+    assert cfg.attention_bias and cfg.mlp_bias and cfg.head_dim == 80
+    names = expected_tensors(CONFIG_F)
+    for n, shape in (("self_attn.q_proj.bias", (320,)), ("self_attn.k_proj.bias", (160,)), ("self_attn.v_proj.bias", (160,)),
+                     ("self_attn.o_proj.bias", (160,)), ("mlp.gate_proj.bias", (208,)), ("mlp.up_proj.bias", (208,)),
+                     ("mlp.down_proj.bias", (160,))):
+        assert names[f"model.layers.1.{n}"].shape == shape
+    g = expected_tensors(CONFIG_G)
+    assert "model.layers.0.self_attn.o_proj.bias" in g and "model.layers.0.mlp.up_proj.bias" not in g
+    assert not any(n.endswith(".bias") for n in expected_tensors(CONFIG_A))

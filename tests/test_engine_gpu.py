@@ -10,7 +10,7 @@ from tiny import CONFIGS, TOL, load_plain_weights, make_model_dir, max_err, rand
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 40, 64, 97, 130], "C": [3, 50, 81, 120],
-           "D": [2, 129, 300, 47, 260], "E": [33, 290, 131, 380]}
+           "D": [2, 129, 300, 47, 260], "E": [33, 290, 131, 380], "F": [4, 150, 61, 280], "G": [9, 140, 77, 230]}
 
 
 @pytest.fixture(scope="module")
@@ -52,7 +52,7 @@ def compare(got, ref, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F", "G"])
 def test_every_cut_matches_plain(models, name, dtype):
     d, cfg, page, reqs, ref = models(name, dtype)
     longest = max(len(t) for t in reqs.values())

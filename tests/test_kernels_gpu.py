@@ -252,7 +252,8 @@ def paged_reference(q, k, v, window, scale):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("NH,NKV,HS,page,window", [(4, 2, 16, 16, 0), (3, 1, 32, 8, 0), (6, 3, 48, 32, 19),
-                                                   (8, 8, 64, 16, 40), (2, 1, 128, 64, 0), (5, 5, 256, 16, 0)])
+                                                   (8, 8, 64, 16, 40), (2, 1, 128, 64, 0), (5, 5, 256, 16, 0),
+                                                   (2, 2, 80, 16, 0), (3, 1, 100, 8, 25), (4, 2, 6, 16, 0)])   # off the 16-grid
 def test_rope_write_and_paged_attention(ops, dtype, NH, NKV, HS, page, window):
     """Two requests in one batch with reversed, interleaved pages: rope + cache write, then
     attention of a prompt portion beside a single decoded token."""
@@ -767,6 +768,23 @@ def test_tensor_core_attention_matches_the_general_kernel(ops, NH, NKV, HS, page
     err_rows = (out.double() - ref.double()).abs().max(dim=1).values / ref.double().abs().max()
     bad = torch.nonzero(err_rows > 1.2e-2)
     assert bad.numel() == 0, f"first differing row {int(bad[0])} (entry {int(ent[int(bad[0])])}, pos {int(pos[int(bad[0])])}): {float(err_rows[int(bad[0])]):.3e}"
+    # and against the formula itself, in float64 on the entries' own pages
+    want = torch.zeros(T, NH * HS, dtype=torch.float64)
+    G = NH // NKV
+    row = 0
+    for b, (a, n) in enumerate(plan):
+        pages = bt[b, :-(-total[b] // page)].long().cpu()
+        K = kp.double().cpu()[pages].permute(1, 0, 2, 3).reshape(NKV, -1, HS)[:, :total[b]]
+        V = vp.double().cpu()[pages].permute(1, 0, 2, 3).reshape(NKV, -1, HS)[:, :total[b]]
+        qb = q[row:row + n, :NH * HS].double().cpu().view(n, NKV, G, HS)
+        sc = torch.einsum("nkgd,ktd->nkgt", qb, K) * scale
+        p_new = torch.arange(a, a + n)[:, None]
+        keys = torch.arange(total[b])[None, :]
+        visible = (keys <= p_new) & ((keys > p_new - window) if window else torch.ones_like(keys, dtype=torch.bool))
+        sc = sc.masked_fill(~visible[:, None, None, :], float("-inf"))
+        want[row:row + n] = torch.einsum("nkgt,ktd->nkgd", torch.softmax(sc, -1), V).reshape(n, -1)
+        row += n
+    assert rel_err(out, want) < 1.2e-2
 
 
 def test_tensor_core_attention_refuses_other_sizes(ops):

@@ -54,6 +54,17 @@ def test_static_scratch_variant_matches_twice_in_a_row(dtype, kind):
         torch.cuda.synchronize()
         err = float((got.double() - want.double()).abs().max() / want.double().abs().max())
         assert err <= limit, err
+        # and against the formula itself: softmax(q K^T scale) V in float64 over each entry's own pages
+        G = NH // NKV
+        plain = torch.zeros(B, NH * HS, dtype=torch.float64)
+        for b, n in enumerate(lens):
+            lo = max(0, n - window) if window else 0
+            pages = bt[b, :-(-n // page)].long().cpu()
+            K = kp.double().cpu()[pages].permute(1, 0, 2, 3).reshape(NKV, -1, HS)[:, lo:n]
+            V = vp.double().cpu()[pages].permute(1, 0, 2, 3).reshape(NKV, -1, HS)[:, lo:n]
+            p = torch.softmax(torch.einsum("kgd,ktd->kgt", q[b].double().cpu().view(NKV, G, HS), K) * scale, dim=-1)
+            plain[b] = torch.einsum("kgt,ktd->kgd", p, V).reshape(-1)
+        assert float((got.double().cpu() - plain).abs().max() / plain.abs().max()) <= limit
 
 
 def test_static_scratch_variant_refuses_what_does_not_fit():

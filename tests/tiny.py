@@ -32,8 +32,19 @@ CONFIG_E = dict(architectures=["LlamaForCausalLM"], hidden_size=96, intermediate
                 vocab_size=333, rms_norm_eps=1e-6, rope_theta=300000.0, max_position_embeddings=400,
                 tie_word_embeddings=False, sliding_window=150, hidden_act="silu")
 
+# F and G: biases on the projections and head sizes off the 16-grid (80: whole 16-byte pieces per
+# row; 100: none in bfloat16), which run on the general kernels in both precisions.
+CONFIG_F = dict(architectures=["LlamaForCausalLM"], hidden_size=160, intermediate_size=208,
+                num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=80,
+                vocab_size=410, rms_norm_eps=1e-5, rope_theta=50000.0, max_position_embeddings=300,
+                tie_word_embeddings=False, attention_bias=True, mlp_bias=True, hidden_act="silu")
+CONFIG_G = dict(architectures=["LlamaForCausalLM"], hidden_size=96, intermediate_size=130,
+                num_hidden_layers=3, num_attention_heads=3, num_key_value_heads=3, head_dim=100,
+                vocab_size=277, rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=256,
+                tie_word_embeddings=True, sliding_window=53, attention_bias=True, hidden_act="silu")
+
 CONFIGS = {"A": (CONFIG_A, 16), "B": (CONFIG_B, 8), "C": (CONFIG_C, 32),
-           "D": (CONFIG_D, 16), "E": (CONFIG_E, 32)}   # name -> (config, page size)
+           "D": (CONFIG_D, 16), "E": (CONFIG_E, 32), "F": (CONFIG_F, 16), "G": (CONFIG_G, 8)}   # name -> (config, page size)
 
 
 def make_model_dir(tmp_root, name: str, dtype: str, seed: int = 1234, peaked: bool = False) -> str:
