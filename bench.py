@@ -30,6 +30,16 @@ NEW_TOKENS = 256          # and the benchmark definition generates 256 tokens
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
+# The larger shapes of the benchmark definition: layer sizes only, random weights.
+LLAMA2_7B = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, intermediate_size=11008,
+                 num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=32, head_dim=128,
+                 vocab_size=32000, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=4096,
+                 tie_word_embeddings=False)
+LLAMA3_8B = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, intermediate_size=14336,
+                 num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                 vocab_size=128256, rms_norm_eps=1e-5, rope_theta=500000.0, max_position_embeddings=8448,   # 8,000 + 256 positions are used
+                 tie_word_embeddings=False)
+
 
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -112,6 +122,105 @@ def prefill_flops(cfg, layers, tokens, head_rows=1):
     return 2.0 * body * tokens + 2.0 * head * head_rows + attn
 
 
+def generate_point(cfg, prompts, new_tokens, max_seqs, chunk, peaks, seed=20240531, llm=None):
+    """One workload through LLM.generate and the scheduler: the requests all at once, prompts taken
+    in portions of at most `chunk` tokens a step beside the decoded tokens of the others.  Timed on
+    the host around generate() (tokens in, tokens out), after one untimed run of the same
+    requests.  Fractions: the steps that only decode against the HBM roofline (weights once + the
+    live cache per step), the steps that bring prompt portions against the tensor peak."""
+    import torch
+
+    from llm_b200.engine.llm import LLM
+    from llm_b200.engine.scheduler import SchedulerConfig
+    layers = cfg["num_hidden_layers"]
+    longest = max(len(p) for p in prompts) + new_tokens
+    own = llm is None
+    if own:
+        pages = sum(-(-(len(p) + new_tokens) // 16) for p in prompts) + 64
+        llm = LLM(None, dtype="bfloat16", max_num_seqs=max_seqs, max_num_batched_tokens=chunk, max_seq_len=longest,
+                  eos_token_id=-1, kv_block_size=16, num_kv_blocks=pages, random_config=cfg, random_seed=seed,
+                  random_on_device=True)
+    else:
+        keep = llm.scheduler_config
+        llm.scheduler_config = SchedulerConfig(max_seqs, chunk, -1)
+    try:
+        llm.generate(prompts, max_new_tokens=new_tokens)               # untimed: kernels built, graphs captured
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        gen = llm.generate(prompts, max_new_tokens=new_tokens)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        st = llm.last_stats
+        counters = dict(llm.engine.counters)
+        free_pages = [llm.engine.cache.num_free_pages(g) for g in range(llm.engine.cache.num_groups)]
+    finally:
+        if not own:
+            llm.scheduler_config = keep
+    n_prompt = sum(len(p) for p in prompts)
+    n_new = sum(len(g) for g in gen)
+    out = {"requests": len(prompts), "prompt_tokens": n_prompt, "new_tokens": n_new, "max_num_seqs": max_seqs,
+           "chunk": chunk, "wall_s": round(wall, 4), "tok_s": round(n_new / wall, 1),
+           "total_tok_s": round((n_new + n_prompt) / wall, 1), "steps": st["steps"],
+           "preemptions": st["preemptions"], "free_pages_after": free_pages,
+           "graph_captures": counters["graph_captures"], "graph_replays": counters["graph_replays"]}
+    if st["decode_steps"]:
+        # every request decodes in these steps; their mean context is taken as prompt + half of the new tokens
+        batch = st["decode_tokens"] / st["decode_steps"]
+        ctx = batch * (n_prompt / len(prompts) + new_tokens / 2.0)
+        bytes_step = decode_bytes(cfg, layers, batch, ctx)
+        ms = st["decode_seconds"] / st["decode_steps"] * 1e3
+        out["decode"] = {"steps": st["decode_steps"], "batch": round(batch, 2), "ms_per_step": round(ms, 4),
+                         "tok_s": round(st["decode_tokens"] / st["decode_seconds"], 1),
+                         "frac_hbm": round(bytes_step / (ms / 1e3) / 1e9 / peaks["hbm_gbs"], 4)}
+    if st["prompt_steps"]:
+        fl = sum(prefill_flops(cfg, layers, len(p)) for p in prompts)
+        out["prefill"] = {"steps": st["prompt_steps"], "tokens": st["prompt_step_tokens"],
+                          "tok_s": round(st["prompt_step_tokens"] / st["prompt_seconds"], 1),
+                          "frac_tensor": round(fl / st["prompt_seconds"] / (peaks["bf16_tflops"] * 1e12), 4)}
+    if own:
+        del llm
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+    return out
+
+
+def float32_check(cfg, seed, peaks):
+    """The whole model in true 32-bit against the plain implementation on one short prompt, and
+    the bfloat16 engine against the 32-bit engine (error and greedy token)."""
+    import gc
+
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import plain_llama
+    from llm_b200.config import EngineOptions
+    from llm_b200.engine.engine import Engine, StepEntry
+    from llm_b200.weights.loader import expected_tensors, random_tensor
+    t0 = time.perf_counter()
+    w = {}
+    for name, info in expected_tensors(cfg).items():
+        t = random_tensor(name, info, seed)
+        w[name] = t.to(torch.bfloat16).float() if info.kind == "matrix" else t        # as a bfloat16 checkpoint stores them
+    toks = [int(x) for x in torch.randint(0, cfg["vocab_size"], (24,), generator=torch.Generator().manual_seed(3))]
+    ref = plain_llama.forward(cfg, w, toks, rows=[len(toks) - 1])[0]
+    rows = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(None, EngineOptions(dtype=dtype, kv_block_size=16, max_num_seqs=2, max_num_batched_tokens=64,
+                                         max_seq_len=64, num_kv_blocks=8), random_config=cfg, tensors=w)
+        rows[dtype] = eng.step([StepEntry("c", toks, [len(toks) - 1])])[0].double().cpu()
+        eng.check_status()
+        del eng
+        gc.collect()
+        torch.cuda.empty_cache()
+    scale = float(ref.abs().max())
+    return {"layers": cfg["num_hidden_layers"], "prompt_tokens": len(toks),
+            "float32_vs_plain": float((rows["float32"] - ref).abs().max() / scale),
+            "bfloat16_vs_float32": float((rows["bfloat16"] - rows["float32"]).abs().max() / scale),
+            "top1_plain": int(ref.argmax()), "top1_float32": int(rows["float32"].argmax()),
+            "top1_bfloat16": int(rows["bfloat16"].argmax()), "seconds": round(time.perf_counter() - t0, 1)}
+
+
 def reference_arm(args, warmup: int) -> int:
     """The same measurements on the unmodified reference: its tree compiled with nvcc (it has no
     Python package to install) and driven through Scheduler -> PipelineDriver -> LLM::inference by
@@ -158,7 +267,8 @@ def reference_arm(args, warmup: int) -> int:
             if not args.no_points:
                 b1 = h.command(f"decode 1 {PROMPT_LEN} {warmup} {min(args.steps, 128)}")
                 points["decode_b1"] = round(b1["tok_s_device"], 1) if "tok_s_device" in b1 else b1
-                extra["reference_load"] = h.command("load 32 128 128")
+                ld = h.command("load 32 128 128")       # its own benchmark (model/llm/test/bench_tiny_llama_load.cu:27-28)
+                extra["shapes"] = {"load_32x128_128": dict(ld, max_num_seqs=8, chunk=512) if "tok_s" in ld else ld}
         head, mode = stock, "stock sizes (8 sequences, 512 tokens a step): two alternating groups in flight"
         # the same code with larger constructor arguments: every prompt of the batch in ONE step, so
         # that the batch decodes whole (and is waited for each step); batch 64; a 2,048-token step
@@ -221,6 +331,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)
     ap.add_argument("--no-points", action="store_true", help="skip prefill and the batch 1 / 64 points")
+    ap.add_argument("--no-shapes", action="store_true",
+                    help="skip the runs at the Llama-2-7B and Llama-3-8B shapes, the many-request load and the 32-bit check")
     ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"],
                     help="decode / prefill: only that measurement, for small profiling runs (not the benchmark line)")
     args = ap.parse_args()
@@ -249,6 +361,7 @@ def main() -> int:
               max_seq_len=MODEL["max_position_embeddings"], eos_token_id=-1, kv_block_size=16,
               random_config=cfg, random_seed=20240531)
     eng = llm.engine
+    use_graphs = eng.options.use_cuda_graphs
     load_s = time.time() - t_load
     rng = np.random.default_rng(1)
 
@@ -360,13 +473,44 @@ def main() -> int:
             points[f"decode_b{b}"] = round(b / (pm / 1e3), 1)
         out["points"] = points
 
+    out["counters"] = dict(eng.counters, preemptions=llm.last_stats.get("preemptions", 0),
+                           free_pages=[eng.cache.num_free_pages(g) for g in range(eng.cache.num_groups)],
+                           pages=[eng.cache.group_spec(g).num_pages for g in range(eng.cache.num_groups)])
+
+    # ---- the other workloads of the benchmark definition, each through LLM.generate and the scheduler ----
+    if not (args.no_points or args.no_shapes) and args.layers == FULL_LAYERS:
+        shapes = {}
+
+        def attempt(name, fn):
+            try:
+                shapes[name] = fn()
+            except Exception as e:                   # a shape that cannot run here must not take the headline with it
+                shapes[name] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+
+        # the reference's own load (model/llm/test/bench_tiny_llama_load.cu:27-28): 32 requests of
+        # 128 + 128 tokens, at most 8 live, 512 tokens a step
+        attempt("load_32x128_128", lambda: generate_point(cfg, [prompt(128) for _ in range(32)], 128, 8, 512, peaks, llm=llm))
+        del llm, eng
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        # Llama-2-7B shape: 32 requests, prompts of 128 to 2,048 tokens, 128 new tokens each, one mixed batch
+        lens7 = [int(x) for x in rng.integers(128, 2049, size=32)]
+        attempt("llama2_7b_mixed", lambda: generate_point(
+            LLAMA2_7B, [[int(x) for x in rng.integers(0, 32000, size=n)] for n in lens7], 128, 32, 2048, peaks))
+        # Llama-3-8B shape: 8 requests of 8,000 tokens taken 2,048 a step, then 256 new tokens at batch 8
+        attempt("llama3_8b_long", lambda: generate_point(
+            LLAMA3_8B, [[int(x) for x in rng.integers(0, 128256, size=8000)] for _ in range(8)], 256, 8, 2048, peaks))
+        attempt("float32_check", lambda: float32_check(dict(MODEL), 20240531, peaks))
+        out["shapes"] = shapes
+
     out["config"] = {"model": "TinyLlama-1.1B shape", "layers": args.layers, "layers_full": FULL_LAYERS,
                      "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                      "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                      "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                      "global_batch": args.batch, "prompt_len": PROMPT_LEN, "new_tokens": args.steps,
                      "seq_len": MODEL["max_position_embeddings"], "kv_block": 16, "parallelism": "none (1 GPU)",
-                     "l2": "inputs larger than L2 (2.2 GB of weights per step)", "cuda_graphs": eng.options.use_cuda_graphs,
+                     "l2": "inputs larger than L2 (2.2 GB of weights per step)", "cuda_graphs": use_graphs,
                      "load_s": round(load_s, 1)}
     print(json.dumps(out))
     return 0

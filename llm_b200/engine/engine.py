@@ -26,7 +26,7 @@ from ..config.model_config import load_config, parse_config
 from ..csrc import ops
 from ..csrc.build import build as build_kernels, load as load_kernels
 from ..parts.base import ResidualStream
-from ..weights.loader import load_tensors, random_tensors_on_device
+from ..weights.loader import adopt_tensors, load_tensors, random_tensors_on_device
 from .context import GroupView, LayerView, StepContext, Workspace
 from .model import Model
 
@@ -94,10 +94,14 @@ class Engine:
     MAX_GRAPHS = 512              # captured shapes in all; the one replayed longest ago goes first
 
     def __init__(self, model_dir: Optional[str], options: Optional[EngineOptions] = None, *,
-                 random_config: Optional[dict] = None, random_seed: int = 0):
+                 random_config: Optional[dict] = None, random_seed: int = 0, random_on_device: bool = False,
+                 tensors: Optional[Dict[str, torch.Tensor]] = None):
         """model_dir: a folder with config.json and model.safetensors.  Without a folder,
         random_config (the contents of a config.json) and random_seed give the same seeded
-        random weights that write_random_model would have written, built in memory."""
+        random weights that write_random_model would have written, built in memory (with
+        random_on_device other values of the same distributions, drawn by the GPU's generator).
+        tensors: with random_config, the checkpoint's tensors by name, already in memory, instead
+        of drawing them (checked against what the parts expect like a file's)."""
         self.options = options = options or EngineOptions()
         options.validate()
         if not torch.cuda.is_available():
@@ -122,8 +126,11 @@ class Engine:
         self.model = Model(self.spec, self.dtype, self.device)
         if model_dir is not None:
             tensors = load_tensors(model_dir, self.model.parameters(), self.dtype, self.device)
+        elif tensors is not None:
+            tensors = adopt_tensors(tensors, self.model.parameters(), self.dtype, self.device)
         else:
-            tensors = random_tensors_on_device(self.model.parameters(), random_seed, self.dtype, self.device)
+            tensors = random_tensors_on_device(self.model.parameters(), random_seed, self.dtype, self.device,
+                                               on_device=random_on_device)
         self.model.bind(tensors)
         del tensors
 

@@ -26,14 +26,17 @@ class LLM:
                  eos_token_id: Optional[int] = None, kv_block_size: int = 16,
                  num_kv_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.9,
                  use_cuda_graphs: bool = True, device: str = "cuda:0", random_config: Optional[dict] = None,
-                 random_seed: int = 0, lookahead: bool = True):
+                 random_seed: int = 0, lookahead: bool = True, random_on_device: bool = False, tensors=None):
         """model: a folder with config.json and model.safetensors, or None together with
-        random_config (a config.json's contents) for seeded random weights."""
+        random_config (a config.json's contents) for seeded random weights (random_on_device:
+        drawn by the GPU's generator instead of the CPU's, for models of many billions of weights;
+        other values than the folder that write_random_model writes)."""
         options = EngineOptions(dtype=dtype, kv_block_size=kv_block_size, max_num_seqs=max_num_seqs,
                                 max_num_batched_tokens=max_num_batched_tokens, max_seq_len=max_seq_len,
                                 num_kv_blocks=num_kv_blocks, gpu_memory_utilization=gpu_memory_utilization,
                                 max_logit_rows=max_num_seqs, use_cuda_graphs=use_cuda_graphs, device=device)
-        self.engine = Engine(model, options, random_config=random_config, random_seed=random_seed)
+        self.engine = Engine(model, options, random_config=random_config, random_seed=random_seed,
+                             random_on_device=random_on_device, tensors=tensors)
         if eos_token_id is None:
             eos_token_id = self.engine.spec.eos_token_id
         self.eos_token_id = eos_token_id
@@ -100,6 +103,7 @@ class LLM:
         Host-side times of the steps that only decode are kept in last_stats, as the reference's
         driver keeps sched/wait/update times per step (runtime/Driver.h:16,74-83)."""
         stats = {"steps": 0, "decode_steps": 0, "decode_tokens": 0, "decode_seconds": 0.0, "lookahead_steps": 0,
+                 "prompt_steps": 0, "prompt_step_tokens": 0, "prompt_seconds": 0.0,
                  "h2d_bytes_per_step": self.engine.layout.total * 4, "d2h_bytes_per_step": 0}
         previous = None              # (batch, rows, handle) of a launched step whose tokens are not read yet
         t_mark = time.perf_counter()
@@ -131,8 +135,13 @@ class LLM:
                 stats["decode_tokens"] += len(batch.entries)
                 stats["decode_seconds"] += now - t_mark
                 stats["d2h_bytes_per_step"] = max(stats["d2h_bytes_per_step"], 4 * len(rows))
+            else:                        # a step that brings at least one prompt portion (decoded tokens may ride along)
+                stats["prompt_steps"] += 1
+                stats["prompt_step_tokens"] += sum(len(e.tokens) for e in batch.entries)
+                stats["prompt_seconds"] += now - t_mark
             t_mark = now
         assert previous is None
+        stats["preemptions"] = scheduler.num_preemptions
         self.last_stats = stats
         self.engine.check_status()
 

@@ -94,6 +94,18 @@ def load_tensors(model_dir: str, expected: Dict[str, ParamInfo], compute_dtype: 
     return out
 
 
+def adopt_tensors(given: Dict[str, torch.Tensor], expected: Dict[str, ParamInfo], compute_dtype: torch.dtype,
+                  device: torch.device) -> Dict[str, torch.Tensor]:
+    """Tensors that are already in memory, checked and converted like a file's."""
+    missing = sorted(n for n in expected if n not in given)
+    unexpected = sorted(n for n in given if n not in expected)
+    wrong = [f"{n}: given {list(given[n].shape)}, model expects {list(i.shape)}" for n, i in expected.items()
+             if n in given and tuple(given[n].shape) != tuple(i.shape)]
+    if missing or unexpected or wrong:
+        raise WeightError("the given tensors", missing, unexpected, wrong)
+    return {n: given[n].to(device=device, dtype=_target_dtype(i, compute_dtype)).contiguous() for n, i in expected.items()}
+
+
 def _tensor_seed(seed: int, name: str) -> int:
     h = hashlib.sha256(f"{seed}:{name}".encode()).digest()
     return int.from_bytes(h[:8], "little") >> 1
@@ -116,12 +128,24 @@ def random_tensor(name: str, info: ParamInfo, seed: int) -> torch.Tensor:
 
 
 def random_tensors_on_device(expected: Dict[str, ParamInfo], seed: int, compute_dtype: torch.dtype,
-                             device: torch.device, stored_dtype: str = "bfloat16") -> Dict[str, torch.Tensor]:
+                             device: torch.device, stored_dtype: str = "bfloat16",
+                             on_device: bool = False) -> Dict[str, torch.Tensor]:
     """What load_tensors would return for the folder that write_random_model(seed,
-    stored_dtype) writes, without the folder."""
+    stored_dtype) writes, without the folder.  on_device: the values come from the device's own
+    generator instead (seeded per tensor the same way, same distributions, other numbers): models
+    of billions of weights are drawn in a second instead of minutes."""
     store = {"bfloat16": torch.bfloat16, "float32": torch.float32}[stored_dtype]
     out = {}
     for name, info in expected.items():
+        if on_device and info.kind != "int_table" and info.init in ("normal", "ones_normal"):
+            g = torch.Generator(device=device)
+            g.manual_seed(_tensor_seed(seed, name))
+            t = torch.randn(info.shape, generator=g, dtype=torch.float32, device=device)
+            t = t * 0.02 if info.init == "normal" else 1.0 + t * 0.01
+            if info.kind == "matrix":
+                t = t.to(store)
+            out[name] = t.to(dtype=_target_dtype(info, compute_dtype)).contiguous()
+            continue
         t = random_tensor(name, info, seed)
         if info.kind == "matrix":
             t = t.to(store)
