@@ -357,7 +357,9 @@ def main() -> int:
         args.no_points = True
     max_batch = max(64, args.batch) if not args.no_points else args.batch
     t_load = time.time()
-    llm = LLM(None, dtype="bfloat16", max_num_seqs=max_batch, max_num_batched_tokens=PREFILL_TOKENS,
+    # a token budget that takes the whole batch's prompts in one step, so that in the end-to-end run
+    # every request starts to decode in the same step and the batch stays whole to the last token
+    llm = LLM(None, dtype="bfloat16", max_num_seqs=max_batch, max_num_batched_tokens=max(PREFILL_TOKENS, args.batch * PROMPT_LEN),
               max_seq_len=MODEL["max_position_embeddings"], eos_token_id=-1, kv_block_size=16,
               random_config=cfg, random_seed=20240531)
     eng = llm.engine

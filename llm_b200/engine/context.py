@@ -84,6 +84,7 @@ class StepContext:
     workspace: Workspace = None
     capturing: bool = False
     kv_bucket: int = 0                         # longest request of the step, rounded up to 256 keys
+    layer_views: List[LayerView] = None        # cache and state of every layer occurrence, over this step's metadata
 
     @property
     def max_entry_tokens(self) -> int:

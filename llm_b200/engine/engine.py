@@ -46,10 +46,12 @@ class StepEntry:
 
 
 class _MetaLayout:
-    """Offsets of the step's int32 metadata inside one buffer (one copy per step)."""
+    """Offsets of the step's int32 metadata inside one buffer (one copy per step).  The block
+    tables come last, entry by entry, so that a step of few entries copies a prefix."""
 
-    def __init__(self, max_tokens: int, max_entries: int, max_rows: int, table_widths: List[int]):
-        off = 0
+    def __init__(self, max_tokens: int, max_entries: int, max_rows: int, table_widths: List[int], base: int = 0):
+        off = base
+        self.base, self.max_tokens, self.max_entries, self.max_rows, self.widths = base, max_tokens, max_entries, max_rows, table_widths
 
         def take(n):
             nonlocal off
@@ -68,7 +70,13 @@ class _MetaLayout:
         self.feed_src = take(max_entries)
         self.slot_map = [take(max_tokens) for _ in table_widths]
         self.block_table = [take(max_entries * w) for w in table_widths]
-        self.total = off
+        self.end = off
+
+    def used_end(self, n_entries: int) -> int:
+        """One past the last word that a step of n_entries entries reads."""
+        if not self.widths:
+            return self.end
+        return self.block_table[-1] + n_entries * self.widths[-1]
 
 
 class _NativeLayout(ctypes.Structure):
@@ -192,12 +200,19 @@ class Engine:
 
     def _init_buffers(self) -> None:
         widths = [self.cache.table_width(g) for g in range(self.cache.num_groups)]
-        self.layout = lay = _MetaLayout(self.max_tokens, self.max_entries, self.max_rows, widths)
-        self._host_ring = [torch.zeros(lay.total, dtype=torch.int32).pin_memory() for _ in range(4)]
-        self._native_layout = _NativeLayout.of(lay)
+        # Two layouts in one buffer.  The small one holds a step in which every entry brings one token
+        # (its per-token arrays are as long as the most entries), so that such a step copies a few
+        # hundred words plus its entries' table rows instead of arrays sized for the token budget;
+        # the large one holds every other step.  The reference likewise uploads only the used part
+        # of each array (runtime/Engine.h:109-116).
+        small = _MetaLayout(self.max_entries, self.max_entries, min(self.max_rows, self.max_entries), widths)
+        large = _MetaLayout(self.max_tokens, self.max_entries, self.max_rows, widths, base=small.end)
+        self.layout = large
+        self._layouts = (small, large)
+        self._host_ring = [torch.zeros(large.end, dtype=torch.int32).pin_memory() for _ in range(4)]
         self._host_events = [None] * len(self._host_ring)
         self._ring_at = 0
-        self.meta = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
+        self.meta = torch.zeros(large.end, dtype=torch.int32, device=self.device)
         # word 0: a token id outside the vocabulary; words 1 and 2: a tensor-core product or attention
         # kernel whose bounded wait gave up (the kernels write there while this engine's step runs)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
@@ -205,34 +220,39 @@ class Engine:
         self.workspace = Workspace(self.max_tokens, self.device)
         self._head_rows = None
         self._logits = None
+        self._step_views = [self._views_of(lay) for lay in self._layouts]       # (native layout, context, layer views)
 
+    def _views_of(self, lay: "_MetaLayout"):
+        """The device views of one layout: what the parts see of a step that uses it."""
         def dev(off, n):
             return self.meta[off:off + n]
 
-        self._groups = {
+        groups = {
             g: GroupView(page_size=self.page_size,
-                         block_table=dev(lay.block_table[g], self.max_entries * widths[g]).view(self.max_entries, widths[g]),
-                         slot_map=dev(lay.slot_map[g], self.max_tokens),
+                         block_table=dev(lay.block_table[g], lay.max_entries * w).view(lay.max_entries, w),
+                         slot_map=dev(lay.slot_map[g], lay.max_tokens),
                          kind=self.cache.group_spec(g).kind, window=self.cache.group_spec(g).window)
-            for g in range(self.cache.num_groups)
+            for g, w in enumerate(lay.widths)
         }
-        self._views = []
+        views = []
         for occ in self.model.occurrences:
             view = LayerView(owns_cache=occ.owns_cache)
             if occ.cache_instance is not None:
                 inst = self.model.cache_instances[occ.cache_instance]
-                view.group = self._groups[inst.group]
+                view.group = groups[inst.group]
                 view.k_pages, view.v_pages = self.cache_storage.pages(occ.cache_instance)
             if occ.state_instance is not None:
                 view.state = self.state_storage.tensor(occ.state_instance)
-            self._views.append(view)
-        self._ctx = StepContext(
+            views.append(view)
+        ctx = StepContext(
             n_tokens=0, n_entries=0, n_logit_rows=0,
-            token_ids=dev(lay.token_ids, self.max_tokens), positions=dev(lay.positions, self.max_tokens),
-            token_entry=dev(lay.token_entry, self.max_tokens), cu_tokens=dev(lay.cu_tokens, self.max_entries + 1),
-            kv_lens=dev(lay.kv_lens, self.max_entries), state_slots=dev(lay.state_slots, self.max_entries),
-            logit_rows=dev(lay.logit_rows, self.max_rows), status=self.status,
-            groups=self._groups, workspace=self.workspace)
+            token_ids=dev(lay.token_ids, lay.max_tokens), positions=dev(lay.positions, lay.max_tokens),
+            token_entry=dev(lay.token_entry, lay.max_tokens), cu_tokens=dev(lay.cu_tokens, lay.max_entries + 1),
+            kv_lens=dev(lay.kv_lens, lay.max_entries), state_slots=dev(lay.state_slots, lay.max_entries),
+            logit_rows=dev(lay.logit_rows, lay.max_rows), status=self.status,
+            groups=groups, workspace=self.workspace)
+        ctx.layer_views = views
+        return _NativeLayout.of(lay), ctx, views
 
     def _drop_graphs(self) -> None:
         """Forget every captured step (their buffers' addresses changed, or none exist yet)."""
@@ -310,9 +330,11 @@ class Engine:
             raise StepError(f"{n_rows} wanted rows exceed the limit {self.max_rows}")
 
         cache = self.cache
-        lay = self.layout
-        host_t = self._next_host_buffer()
         B = len(entries)
+        which = 0 if n_tokens == B else 1                  # one token per entry: the small layout
+        lay = self._layouts[which]
+        native_layout, ctx, _views = self._step_views[which]
+        host_t = self._next_host_buffer()
         ns = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=B)
         starts = np.empty(B, dtype=np.int32)
         slots = np.empty(B, dtype=np.int32)
@@ -334,7 +356,7 @@ class Engine:
         # rest of the step's metadata into the pinned block, from the pool's own tables
         lib, pool = cache.native
         ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
-        n_feed = lib.llmh_prepare_step(pool, ctypes.byref(self._native_layout), ctypes.c_void_p(host_t.data_ptr()), B,
+        n_feed = lib.llmh_prepare_step(pool, ctypes.byref(native_layout), ctypes.c_void_p(host_t.data_ptr()), B,
                                        ptr(slots), ptr(ns), ptr(starts), ptr(tokens), ptr(want_counts), ptr(wants), ptr(feeds))
         if n_feed < 0:
             raise StepError(lib.llmh_pool_error(pool).decode("utf-8", "replace"))
@@ -348,15 +370,16 @@ class Engine:
         fresh = cache.take_fresh_slots()
         if fresh:
             self.state_storage.zero_slots(fresh)
-        self.meta.copy_(host_t, non_blocking=True)
+        a, b = lay.base, lay.used_end(B)
+        self.meta[a:b].copy_(host_t[a:b], non_blocking=True)
+        self.last_h2d_bytes = 4 * (b - a)
         ev = torch.cuda.Event()
         ev.record()
         self._host_events[self._ring_at] = ev
         if n_feed:
-            ops.feed_tokens(self._ctx.token_ids, feed_source, self.meta[lay.feed_dst: lay.feed_dst + n_feed],
+            ops.feed_tokens(ctx.token_ids, feed_source, self.meta[lay.feed_dst: lay.feed_dst + n_feed],
                             self.meta[lay.feed_src: lay.feed_src + n_feed], n_feed)
 
-        ctx = self._ctx
         ctx.n_tokens, ctx.n_entries, ctx.n_logit_rows = n_tokens, B, n_rows
         ctx.host_entry_tokens, ctx.host_entry_start, ctx.host_state_slots = entry_tokens, entry_start, entry_slots
         ctx.kv_bucket = (int((entry_start + entry_tokens).max()) + 255) // 256 * 256
@@ -382,7 +405,7 @@ class Engine:
 
     def _forward_on_stream(self, ctx: StepContext) -> None:
         stream = ResidualStream(self.resid, ctx.n_tokens)
-        self.model.forward(ctx, stream, self._views)
+        self.model.forward(ctx, stream, ctx.layer_views)
         if ctx.n_logit_rows:
             self.model.head.logits(stream, ctx, self.model.final_norm, self._logit_buffers(ctx.n_logit_rows))
 

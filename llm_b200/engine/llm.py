@@ -104,7 +104,7 @@ class LLM:
         driver keeps sched/wait/update times per step (runtime/Driver.h:16,74-83)."""
         stats = {"steps": 0, "decode_steps": 0, "decode_tokens": 0, "decode_seconds": 0.0, "lookahead_steps": 0,
                  "prompt_steps": 0, "prompt_step_tokens": 0, "prompt_seconds": 0.0,
-                 "h2d_bytes_per_step": self.engine.layout.total * 4, "d2h_bytes_per_step": 0}
+                 "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
         previous = None              # (batch, rows, handle) of a launched step whose tokens are not read yet
         t_mark = time.perf_counter()
         while scheduler.num_requests():
@@ -135,6 +135,7 @@ class LLM:
                 stats["decode_tokens"] += len(batch.entries)
                 stats["decode_seconds"] += now - t_mark
                 stats["d2h_bytes_per_step"] = max(stats["d2h_bytes_per_step"], 4 * len(rows))
+                stats["h2d_bytes_per_step"] = max(stats["h2d_bytes_per_step"], self.engine.last_h2d_bytes)
             else:                        # a step that brings at least one prompt portion (decoded tokens may ride along)
                 stats["prompt_steps"] += 1
                 stats["prompt_step_tokens"] += sum(len(e.tokens) for e in batch.entries)

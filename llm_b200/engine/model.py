@@ -37,6 +37,7 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm, dtype, device) if spec.final_norm is not None else None
         self.head = build_part("head", spec.head, dtype, device)
 
+        self._graph_askers = None
         self.group_keys: List[tuple] = []            # (kind, window) per group
         self.cache_instances: List[CacheInstance] = []
         self.state_needs: List[StateNeed] = []
@@ -84,8 +85,13 @@ class Model:
         yield from walk(self.head)
 
     def is_graph_safe(self, ctx) -> bool:
-        """Whether every part says that this step may be captured in, or replayed from, a CUDA graph."""
-        return all(getattr(part, "is_graph_safe", lambda c: True)(ctx) for part in self.parts())
+        """Whether every part says that this step may be captured in, or replayed from, a CUDA graph.
+        Only parts that bring an answer of their own are asked (found once)."""
+        if self._graph_askers is None:
+            from ..parts.base import Part
+            self._graph_askers = [p for p in self.parts() if hasattr(p, "is_graph_safe")
+                                  and getattr(type(p), "is_graph_safe", None) is not Part.is_graph_safe]
+        return all(p.is_graph_safe(ctx) for p in self._graph_askers)
 
     def parameters(self) -> Dict[str, ParamInfo]:
         out: Dict[str, ParamInfo] = {}
