@@ -42,6 +42,10 @@ NVCC_FLAGS = [
 ]
 
 
+# extra nvcc flags from the environment (for experiments, e.g. -DNAME=1); part of the build's digest
+NVCC_FLAGS += os.environ.get("LLM_B200_NVCC_FLAGS", "").split()
+
+
 class KernelBuildError(RuntimeError):
     pass
 

@@ -442,12 +442,15 @@ PERSISTENT_GEMM = True
 PAIR_GEMM = True
 
 
-def plan_gemm(M: int, N: int, K: int, fused_reduce: bool = False):
-    return _plan_gemm(M, N, K, fused_reduce, PERSISTENT_GEMM, PAIR_GEMM, sm_count())
+def plan_gemm(M: int, N: int, K: int, fused_reduce: bool = False, cta_limit: int = 0):
+    """cta_limit > 0 (swapped mode only): at most so many CTAs, for a product that should leave
+    SMs to the kernel after it."""
+    return _plan_gemm(M, N, K, fused_reduce, PERSISTENT_GEMM, PAIR_GEMM, sm_count(), cta_limit)
 
 
 @functools.lru_cache(maxsize=4096)
-def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool, pair: bool = False, _SMS: int = 148):
+def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool, pair: bool = False, _SMS: int = 148,
+               cta_limit: int = 0):
     """(swap, tile, splits, k-blocks per split, mode) for the tensor-core product; mode 0 = one
     CTA per tile, 1 = the splits of a tile sum on chip in a cluster, 2 = persistent CTAs, 3 =
     persistent pairs of CTAs on tiles of 256 rows.
@@ -462,7 +465,7 @@ def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool, pai
     at 129 to 4,096 rows; plus the sum of the partial results where K is split."""
     kb = _ceil_div(K, 64)
     if M <= 128:
-        return _plan_swapped(M, N, kb, fused_reduce, _SMS)
+        return _plan_swapped(M, N, kb, fused_reduce, _SMS, cta_limit)
     best = None
     for tile in (256, 224, 192, 160, 128):
         tiles = _ceil_div(M, 128) * _ceil_div(N, tile)
@@ -502,7 +505,7 @@ def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool, pai
 _SWAPPED_STAGES = {16: 6, 32: 5, 64: 4, 128: 3}      # as stages_for() in gemm_tc.cu
 
 
-def _plan_swapped(M: int, N: int, kb: int, fused_reduce: bool, _SMS: int):
+def _plan_swapped(M: int, N: int, kb: int, fused_reduce: bool, _SMS: int, cta_limit: int = 0):
     """The swapped mode (up to 128 rows): a stream of weights.  Two CTAs share an SM, so up to 296
     run at a time.  A CTA alone is bound by what its ring keeps in flight (stages x stage bytes per
     memory latency of about 2 us), the CTAs of one SM by its way to L2, all CTAs together by HBM;
@@ -523,6 +526,8 @@ def _plan_swapped(M: int, N: int, kb: int, fused_reduce: bool, _SMS: int):
         if s > 1 and s * M * N * 4 > _PARTIAL_BYTES:
             break
         n_cta = tiles * s
+        if cta_limit and s > 1 and n_cta > cta_limit:
+            break
         rounds = _ceil_div(n_cta, 2 * _SMS)
         conc = n_cta if rounds == 1 else 2 * _SMS
         per_sm = min(2, _ceil_div(n_cta, _SMS))           # CTAs on the fullest SM: they share its tensor pipe and its way to L2
@@ -555,14 +560,15 @@ def gemm_fast_available(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, row
                                               c_longlong(a.stride(0)), c_longlong(w.stride(0))))
 
 
-def gemm_fast(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, plan=None, allow_partial: bool = False):
+def gemm_fast(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, plan=None, allow_partial: bool = False,
+              cta_limit: int = 0):
     """out[:rows] = a[:rows] @ w.T on the tensor cores (bfloat16 in, float32 accumulation).
     Returns out; or, with allow_partial and a split-K plan, a PartialSum that the caller hands to
-    a kernel that sums it (out is then not written)."""
+    a kernel that sums it (out is then not written).  cta_limit: see plan_gemm."""
     _rows_contig(a, "a"); _rows_contig(w, "w"); _rows_contig(out, "out")
     n, k = w.shape
     assert a.shape[1] == k and out.shape[1] == n
-    plan = plan or plan_gemm(rows, n, k, fused_reduce=allow_partial)
+    plan = plan or plan_gemm(rows, n, k, fused_reduce=allow_partial, cta_limit=cta_limit)
     swap, tile, splits, per = plan[:4]
     cluster = int(plan[4]) if len(plan) > 4 else 0
     lib = load_tensor()

@@ -79,6 +79,21 @@ class PagedAttention(Part):
     def children(self):
         return [self.position] if self.position is not None else []
 
+    def _qkv_cta_limit(self, ctx, k_pages) -> int:
+        """A decode step whose attention has to read several times the bytes of the QKV weights
+        (many requests, long contexts) is bound by that reading, and the attention kernel asks for
+        its keys and values before it waits for the product: a product on fewer CTAs leaves it SMs
+        to start on.  Measured: 64 requests of 640 keys at TinyLlama sizes, 2 instead of 8 splits
+        of K: 5 % off the step; about 30 requests of 1,200 keys at Llama-2-7B sizes: 2 % off; with
+        8 requests (of 8,000 keys, Llama-3-8B sizes) or with a cache of under four times the
+        weights' bytes the full grid is faster."""
+        if not ctx.decode_only or self.w_qkv.dtype != torch.bfloat16 or ctx.n_entries < 24:
+            return 0
+        keys = min(ctx.kv_bucket or 0, self.window or (1 << 30))
+        cache_bytes = 2 * ctx.n_entries * keys * k_pages.shape[1] * self.head_dim * k_pages.element_size()
+        weight_bytes = self.w_qkv.numel() * self.w_qkv.element_size()
+        return ops.sm_count() // 3 if cache_bytes > 4 * weight_bytes else 0
+
     def forward(self, x: torch.Tensor, ctx, view) -> torch.Tensor:
         T = ctx.n_tokens
         ws = ctx.workspace
@@ -112,7 +127,8 @@ class PagedAttention(Part):
                 ops.paged_attention(attn, q, k_pages, v_pages, view.group, ctx, self.num_heads, k_pages.shape[1],
                                     self.head_dim, self.window or 0, self.scale)
                 return linear(attn, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
-            qkv = linear(x, self.w_qkv, ws.get("qkv", T, width, self.dtype), T, allow_partial=FUSE_PARTIALS)
+            qkv = linear(x, self.w_qkv, ws.get("qkv", T, width, self.dtype), T, allow_partial=FUSE_PARTIALS,
+                         cta_limit=self._qkv_cta_limit(ctx, k_pages))
         ops.rope_store_attend(attn, qkv, cos, sin, k_pages, v_pages, view.group, ctx, self.num_heads,
                               k_pages.shape[1], self.head_dim, self.window or 0, self.scale,
                               write_kv=not self.shares_cache,

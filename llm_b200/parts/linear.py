@@ -20,9 +20,10 @@ FUSE_PARTIALS = True
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int, allow_partial: bool = False,
-           bias: torch.Tensor = None):
+           bias: torch.Tensor = None, cta_limit: int = 0):
     """out[:rows] = x[:rows] @ weight.T (+ bias, float32 [out features]); out may be float32 for
-    bfloat16 inputs.  With a bias the product is summed into `out` and the bias added there by a
+    bfloat16 inputs.  cta_limit > 0 keeps a product of few rows to so many CTAs (it then leaves SMs
+    to the kernel after it).  With a bias the product is summed into `out` and the bias added there by a
     kernel of its own (the reference adds it in the product's epilogue, model/modules/Linear.h:12-34).
 
     With allow_partial the result may come back as an ops.PartialSum (a split-K product whose
@@ -33,7 +34,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int, 
     if bias is not None:
         allow_partial = False
     if x.dtype == torch.bfloat16 and ops.gemm_fast_available(x, weight, out, rows):
-        res = ops.gemm_fast(x, weight, out, rows, allow_partial=allow_partial)
+        res = ops.gemm_fast(x, weight, out, rows, allow_partial=allow_partial, cta_limit=cta_limit)
     else:
         ops.gemm_simt(x, weight, out, rows)
         res = out
