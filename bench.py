@@ -333,8 +333,9 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip prefill and the batch 1 / 64 points")
     ap.add_argument("--no-shapes", action="store_true",
                     help="skip the runs at the Llama-2-7B and Llama-3-8B shapes, the many-request load and the 32-bit check")
-    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"],
-                    help="decode / prefill: only that measurement, for small profiling runs (not the benchmark line)")
+    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill", "timeline"],
+                    help="decode / prefill: only that measurement, for small profiling runs (not the benchmark line); "
+                         "timeline: the kernels of one decode layer with their start and end inside the step's CUDA graph")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -419,6 +420,48 @@ def main() -> int:
             reps.append(a.elapsed_time(b))
             eng.release(rid)
         print(json.dumps({"mode": "prefill", "layers": args.layers, "tokens": PREFILL_TOKENS, "ms": reps}))
+        return 0
+    if args.mode == "timeline":
+        # When each kernel of a decode step starts and ends inside the replayed CUDA graph (CUPTI
+        # through torch.profiler): the kernels overlap (programmatic dependent launch), so the step's
+        # time is the chain of their ENDS, not the sum of their durations.
+        import collections
+
+        from torch.profiler import ProfilerActivity, profile
+        ids = prefill_requests(args.batch)
+        toks = rng.integers(0, cfg["vocab_size"], size=(warmup + 4, args.batch))
+        entries = lambda k: [StepEntry(r, [int(toks[k, j])], [0]) for j, r in enumerate(ids)]
+        for k in range(warmup):
+            eng.step(entries(k))
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for k in range(warmup, warmup + 4):
+                eng.step(entries(k))
+            torch.cuda.synchronize()
+        evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and e.name
+               and "Memcpy" not in e.name and "Memset" not in e.name]
+        evs.sort(key=lambda e: e.time_range.start)
+        per_step = len(evs) // 4
+        step = evs[2 * per_step:3 * per_step]
+        span = step[-1].time_range.end - step[0].time_range.start
+        print(f"batch {args.batch}, {args.layers} layers: {per_step} kernels a step, {span:.1f} us from the first start to the last end")
+        agg = collections.OrderedDict()
+        prev_end = None
+        for e in step:
+            name = e.name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0][:48]
+            gain = e.time_range.end - (prev_end if prev_end is not None else e.time_range.start)
+            prev_end = max(prev_end or 0, e.time_range.end)
+            d = agg.setdefault(name, [0, 0.0, 0.0])
+            d[0] += 1; d[1] += e.time_range.end - e.time_range.start; d[2] += max(gain, 0.0)
+        print(f"{'kernel':50s} {'launches':>8s} {'mean duration us':>17s} {'end after previous end us (sum)':>32s}")
+        for name, (n, dur, gain) in agg.items():
+            print(f"{name:50s} {n:8d} {dur / n:17.2f} {gain:32.1f}")
+        base = step[0].time_range.start
+        first = min(9, per_step - 1)
+        print("the second layer, microseconds from the step's first kernel: start .. end")
+        for e in step[first:first + 9]:
+            name = e.name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0][:60]
+            print(f"  {e.time_range.start - base:9.2f} .. {e.time_range.end - base:9.2f}  {name}")
         return 0
     if args.mode == "decode":
         ms, launches, _ = timed_decode(args.batch, args.steps, warmup)
