@@ -104,20 +104,29 @@ class LLM:
         driver keeps sched/wait/update times per step (runtime/Driver.h:16,74-83)."""
         stats = {"steps": 0, "decode_steps": 0, "decode_tokens": 0, "decode_seconds": 0.0, "lookahead_steps": 0,
                  "prompt_steps": 0, "prompt_step_tokens": 0, "prompt_seconds": 0.0,
-                 "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+                 "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                 # host seconds over all steps: choosing the batch, launching it, waiting for tokens, accounting for them
+                 "sched_seconds": 0.0, "launch_seconds": 0.0, "wait_seconds": 0.0, "update_seconds": 0.0}
         previous = None              # (batch, rows, handle) of a launched step whose tokens are not read yet
-        t_mark = time.perf_counter()
+        clock = time.perf_counter
+        t_mark = clock()
         while scheduler.num_requests():
             if poll is not None:
                 poll()
+            t0 = clock()
             batch = scheduler.schedule()
             if batch.empty():
                 raise RuntimeError("the scheduler has requests but nothing can run: the cache pool is too "
                                    "small for the request at the head of the queue")
+            t1 = clock()
             rows, handle = self.launch(scheduler, batch, (previous[1], previous[2]) if previous else None)
+            t2 = clock()
+            waited = 0.0
             if previous is not None:         # the GPU is busy with `batch`: now read the step before it
                 p_batch, p_rows, p_handle = previous
-                scheduler.resolve(p_batch, {e.request_id: t for e, t in zip(p_rows, p_handle.result())})
+                got = p_handle.result()
+                waited = clock() - t2
+                scheduler.resolve(p_batch, {e.request_id: t for e, t in zip(p_rows, got)})
                 previous = None
             decode_only = all(len(e.tokens) == 1 for e in batch.entries)
             if self.lookahead and decode_only and scheduler.can_look_ahead(batch):
@@ -125,11 +134,18 @@ class LLM:
                 previous = (batch, rows, handle)
                 stats["lookahead_steps"] += 1
             else:
-                tokens = {e.request_id: t for e, t in zip(rows, handle.result())}
+                t3 = clock()
+                got = handle.result()
+                waited += clock() - t3
+                tokens = {e.request_id: t for e, t in zip(rows, got)}
                 for r in scheduler.update(batch, tokens):
                     on_finished(r)
             stats["steps"] += 1
-            now = time.perf_counter()
+            now = clock()
+            stats["sched_seconds"] += t1 - t0
+            stats["launch_seconds"] += t2 - t1
+            stats["wait_seconds"] += waited
+            stats["update_seconds"] += now - t2 - waited
             if decode_only:
                 stats["decode_steps"] += 1
                 stats["decode_tokens"] += len(batch.entries)

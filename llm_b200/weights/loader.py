@@ -1,4 +1,5 @@
-"""Weights by tensor name, from model.safetensors or from a seed.
+"""Weights by tensor name, from model.safetensors (or the files of a model.safetensors.index.json)
+or from a seed.
 
 The reference binds tensors by the names its modules register
 (runtime/LLM.h:75-89,101-190) and looks each up with `infos.at(name)`: a missing
@@ -49,7 +50,57 @@ def _target_dtype(info: ParamInfo, compute_dtype: torch.dtype) -> torch.dtype:
     raise ValueError(f"unknown parameter kind '{info.kind}'")
 
 
-def _harmless_extra(name: str, f: SafetensorsFile, expected: Dict[str, ParamInfo]) -> bool:
+INDEX_FILE = "model.safetensors.index.json"
+
+
+class _Checkpoint:
+    """The tensors of a model folder: model.safetensors, or the files that
+    model.safetensors.index.json names ({"weight_map": {tensor name: file name}}), seen as one."""
+
+    def __init__(self, model_dir: str):
+        single = os.path.join(model_dir, WEIGHTS_FILE)
+        index = os.path.join(model_dir, INDEX_FILE)
+        self.files: Dict[str, SafetensorsFile] = {}
+        self.where: Dict[str, str] = {}
+        if os.path.isfile(single):
+            self.path = single
+            self.files[WEIGHTS_FILE] = SafetensorsFile(single)
+            self.where = {n: WEIGHTS_FILE for n in self.files[WEIGHTS_FILE].entries}
+        elif os.path.isfile(index):
+            self.path = index
+            try:
+                with open(index, "r", encoding="utf-8") as f:
+                    weight_map = json.load(f)["weight_map"]
+            except (json.JSONDecodeError, KeyError, TypeError) as e:
+                raise SafetensorsError(f"{index}: not an index with a 'weight_map': {e}") from e
+            for fname in sorted(set(weight_map.values())):
+                part = os.path.join(model_dir, str(fname))
+                if os.path.dirname(str(fname)) or not os.path.isfile(part):
+                    raise SafetensorsError(f"{index}: names the file '{fname}', which is not in the model folder")
+                self.files[fname] = SafetensorsFile(part)
+            for name, fname in weight_map.items():
+                if name not in self.files[fname].entries:
+                    raise SafetensorsError(f"{index}: says '{name}' is in {fname}, which does not hold it")
+                self.where[name] = fname
+            # tensors that a file holds but the index does not name are unexpected like any other
+            for fname, f in self.files.items():
+                for n in f.entries:
+                    self.where.setdefault(n, fname)
+        else:
+            raise SafetensorsError(f"{single}: no {WEIGHTS_FILE} (and no {INDEX_FILE}) in the model folder")
+
+    def entry(self, name: str):
+        return self.files[self.where[name]].entries[name]
+
+    def tensor(self, name: str) -> torch.Tensor:
+        return self.files[self.where[name]].tensor(name)
+
+    def close(self) -> None:
+        for f in self.files.values():
+            f.close()
+
+
+def _harmless_extra(name: str, ck: "_Checkpoint", expected: Dict[str, ParamInfo]) -> bool:
     """Tensors that checkpoints of this family often carry although no part binds them: the
     rotary inverse-frequency buffers (the tables are rebuilt from rope_theta), and an lm_head.weight
     beside tied embeddings when it has the embedding's shape.  Everything else that is not
@@ -57,24 +108,22 @@ def _harmless_extra(name: str, f: SafetensorsFile, expected: Dict[str, ParamInfo
     if name.endswith("rotary_emb.inv_freq"):
         return True
     if name == "lm_head.weight" and "model.embed_tokens.weight" in expected:
-        return tuple(f.entries[name].shape) == tuple(expected["model.embed_tokens.weight"].shape)
+        return tuple(ck.entry(name).shape) == tuple(expected["model.embed_tokens.weight"].shape)
     return False
 
 
 def load_tensors(model_dir: str, expected: Dict[str, ParamInfo], compute_dtype: torch.dtype,
                  device: torch.device) -> Dict[str, torch.Tensor]:
     """Read, validate, convert and move every expected tensor."""
-    path = os.path.join(model_dir, WEIGHTS_FILE)
-    if not os.path.isfile(path):
-        raise SafetensorsError(f"{path}: no {WEIGHTS_FILE} in the model folder")
-    f = SafetensorsFile(path)
-    missing = sorted(n for n in expected if n not in f.entries)
-    unexpected = sorted(n for n in f.entries if n not in expected and not _harmless_extra(n, f, expected))
+    ck = _Checkpoint(model_dir)
+    path = ck.path
+    missing = sorted(n for n in expected if n not in ck.where)
+    unexpected = sorted(n for n in ck.where if n not in expected and not _harmless_extra(n, ck, expected))
     wrong = []
     for name, info in expected.items():
-        e = f.entries.get(name)
-        if e is None:
+        if name not in ck.where:
             continue
+        e = ck.entry(name)
         if tuple(e.shape) != tuple(info.shape):
             wrong.append(f"{name}: file has {list(e.shape)}, model expects {list(info.shape)}")
         elif info.kind == "int_table" and e.dtype.is_floating_point:
@@ -82,15 +131,15 @@ def load_tensors(model_dir: str, expected: Dict[str, ParamInfo], compute_dtype: 
         elif info.kind != "int_table" and not e.dtype.is_floating_point:
             wrong.append(f"{name}: file has {e.dtype}, model expects floating point")
     if missing or unexpected or wrong:
-        f.close()
+        ck.close()
         raise WeightError(path, missing, unexpected, wrong)
     out = {}
     with warnings.catch_warnings():
         warnings.simplefilter("ignore", UserWarning)     # read-only mapping: tensors are copied, never written
         for name, info in expected.items():
-            t = f.tensor(name)
+            t = ck.tensor(name)
             out[name] = t.to(device=device, dtype=_target_dtype(info, compute_dtype)).contiguous()
-    f.close()
+    ck.close()
     return out
 
 

@@ -190,3 +190,40 @@ def test_bias_flags_add_bias_tensors():
     g = expected_tensors(CONFIG_G)
     assert "model.layers.0.self_attn.o_proj.bias" in g and "model.layers.0.mlp.up_proj.bias" not in g
     assert not any(n.endswith(".bias") for n in expected_tensors(CONFIG_A))
+
+
+def test_sharded_checkpoint_with_an_index(tmp_path):
+    """A folder whose tensors are spread over several files named by model.safetensors.index.json
+    loads like a single file, and its errors name what is missing or misplaced."""
+    from llm_b200.weights import SafetensorsError, SafetensorsFile, WeightError, load_tensors, write_random_model, write_safetensors
+    from llm_b200.weights.loader import expected_tensors
+    d = write_random_model(str(tmp_path / "m"), CONFIG_A, 4, "bfloat16")
+    single = os.path.join(d, "model.safetensors")
+    f = SafetensorsFile(single)
+    t = {n: f.tensor(n).clone() for n in f.names()}
+    f.close()
+    want = load_tensors(d, expected_tensors(CONFIG_A), torch.float32, torch.device("cpu"))
+    os.remove(single)
+    names = sorted(t)
+    parts = {"model-00001-of-00002.safetensors": names[:9], "model-00002-of-00002.safetensors": names[9:]}
+    for fname, ns in parts.items():
+        write_safetensors(os.path.join(d, fname), {n: t[n] for n in ns})
+    index = {"metadata": {"total_size": 0}, "weight_map": {n: fname for fname, ns in parts.items() for n in ns}}
+    with open(os.path.join(d, "model.safetensors.index.json"), "w") as fh:
+        json.dump(index, fh)
+    got = load_tensors(d, expected_tensors(CONFIG_A), torch.float32, torch.device("cpu"))
+    assert set(got) == set(want) and all(torch.equal(got[n], want[n]) for n in want)
+    # the index names a tensor that its file does not hold
+    index["weight_map"][names[0]] = "model-00002-of-00002.safetensors"
+    with open(os.path.join(d, "model.safetensors.index.json"), "w") as fh:
+        json.dump(index, fh)
+    with pytest.raises(SafetensorsError, match="does not hold it"):
+        load_tensors(d, expected_tensors(CONFIG_A), torch.float32, torch.device("cpu"))
+    # a tensor that no file holds is reported as missing
+    del index["weight_map"][names[0]]
+    write_safetensors(os.path.join(d, "model-00001-of-00002.safetensors"), {n: t[n] for n in names[1:9]})
+    with open(os.path.join(d, "model.safetensors.index.json"), "w") as fh:
+        json.dump(index, fh)
+    with pytest.raises(WeightError) as ei:
+        load_tensors(d, expected_tensors(CONFIG_A), torch.float32, torch.device("cpu"))
+    assert ei.value.missing == [names[0]]
