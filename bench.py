@@ -492,7 +492,9 @@ def main() -> int:
     e2e_value = st["decode_tokens"] / st["decode_seconds"] if st["decode_seconds"] > 0 else None
     out["e2e"] = {"value": round(e2e_value, 1) if e2e_value else None, "unit": "tok/s",
                   "h2d_bytes_per_step": int(st["h2d_bytes_per_step"]), "d2h_bytes_per_step": int(st["d2h_bytes_per_step"]),
-                  "decode_steps": st["decode_steps"], "generated": sum(len(g) for g in gen)}
+                  "decode_steps": st["decode_steps"], "generated": sum(len(g) for g in gen),
+                  "host_us_per_step": {k[:-8]: round(st[k] / max(st["steps"], 1) * 1e6, 1)
+                                       for k in ("sched_seconds", "launch_seconds", "wait_seconds", "update_seconds")}}
 
     # ---- prefill of 2,048 tokens ----
     if not args.no_points:
