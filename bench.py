@@ -333,7 +333,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip prefill and the batch 1 / 64 points")
     ap.add_argument("--no-shapes", action="store_true",
                     help="skip the runs at the Llama-2-7B and Llama-3-8B shapes, the many-request load and the 32-bit check")
-    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill", "timeline"],
+    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill", "timeline", "timeline_prefill"],
                     help="decode / prefill: only that measurement, for small profiling runs (not the benchmark line); "
                          "timeline: the kernels of one decode layer with their start and end inside the step's CUDA graph")
     args = ap.parse_args()
@@ -421,22 +421,29 @@ def main() -> int:
             eng.release(rid)
         print(json.dumps({"mode": "prefill", "layers": args.layers, "tokens": PREFILL_TOKENS, "ms": reps}))
         return 0
-    if args.mode == "timeline":
-        # When each kernel of a decode step starts and ends inside the replayed CUDA graph (CUPTI
-        # through torch.profiler): the kernels overlap (programmatic dependent launch), so the step's
-        # time is the chain of their ENDS, not the sum of their durations.
+    if args.mode in ("timeline", "timeline_prefill"):
+        # When each kernel of a step starts and ends inside the replayed CUDA graph (CUPTI through
+        # torch.profiler): the kernels overlap (programmatic dependent launch), so the step's time
+        # is the chain of their ENDS, not the sum of their durations.  timeline: a decode step of
+        # --batch requests; timeline_prefill: a prompt of PREFILL_TOKENS tokens in one step.
         import collections
 
         from torch.profiler import ProfilerActivity, profile
-        ids = prefill_requests(args.batch)
-        toks = rng.integers(0, cfg["vocab_size"], size=(warmup + 4, args.batch))
-        entries = lambda k: [StepEntry(r, [int(toks[k, j])], [0]) for j, r in enumerate(ids)]
+        if args.mode == "timeline":
+            ids = prefill_requests(args.batch)
+            toks = rng.integers(0, cfg["vocab_size"], size=(warmup + 4, args.batch))
+            entries = lambda k: [StepEntry(r, [int(toks[k, j])], [0]) for j, r in enumerate(ids)]
+            run = lambda k: eng.step(entries(k))
+        else:
+            def run(k):
+                eng.step([StepEntry(f"p{k}", prompt(PREFILL_TOKENS), [PREFILL_TOKENS - 1])])
+                eng.release(f"p{k}")
         for k in range(warmup):
-            eng.step(entries(k))
+            run(k)
         torch.cuda.synchronize()
         with profile(activities=[ProfilerActivity.CUDA]) as prof:
             for k in range(warmup, warmup + 4):
-                eng.step(entries(k))
+                run(k)
             torch.cuda.synchronize()
         evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and e.name
                and "Memcpy" not in e.name and "Memset" not in e.name]
@@ -444,7 +451,8 @@ def main() -> int:
         per_step = len(evs) // 4
         step = evs[2 * per_step:3 * per_step]
         span = step[-1].time_range.end - step[0].time_range.start
-        print(f"batch {args.batch}, {args.layers} layers: {per_step} kernels a step, {span:.1f} us from the first start to the last end")
+        what = f"batch {args.batch}" if args.mode == "timeline" else f"prompt of {PREFILL_TOKENS} tokens"
+        print(f"{what}, {args.layers} layers: {per_step} kernels a step, {span:.1f} us from the first start to the last end")
         agg = collections.OrderedDict()
         prev_end = None
         for e in step:

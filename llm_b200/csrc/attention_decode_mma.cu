@@ -20,8 +20,12 @@ int launch_decode_mma(void* out, long long out_stride, const void* q, long long 
   // clusters against 23 us with the counter-based merge; at 8 requests 9.3 us against 13.5 us.)
   constexpr int RECV_LIMIT = 64 * 1024;
   const int recv_bytes = (splits - 1) * group_rows * head_dim * 4;
+  // Only for short ranges (up to 512 keys of the longest request the table holds): a cluster's
+  // CTA has one stage, which is right when a range is a tile or two per warp and the merge is what
+  // counts; a long range wants the deep stages.
+  const long long range_keys = ((long long)table_width * page_size + splits - 1) / splits;
   const bool cluster = splits >= 2 && splits <= 8 && (long long)splits * n_kv * n_entries <= 2 * llmk_sm_count() &&
-                       recv_bytes <= RECV_LIMIT;
+                       recv_bytes <= RECV_LIMIT && range_keys <= 512;
   // Without a cluster: deep stages (three at head size 64, else two) while the whole grid fits on
   // the SMs at once with them (two CTAs per SM at head size 64, one at 128); else the variant
   // with one stage, which at head size 64 is also held to 128 registers so that four CTAs share

@@ -35,7 +35,8 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t sme
 }
 __device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* src, bool valid) {
   const int bytes = valid ? 16 : 0;                      // 0: the 16 bytes are filled with zeros
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(src), "r"(bytes) : "memory");
+  // .cg: the keys and values stream through once; they need no place in L1
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -200,8 +201,11 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
   for (int j = 0; j < NST; ++j)
     if (j < n_tiles) stage_tile(j);
   {
+    // at most 32 MB over the whole grid: asking for more than L2 keeps evicts the lines before
+    // they are used and fetches them from memory twice (long ranges stream through the stages)
     constexpr int LINES = HS * 2 / 128;                    // 128-byte lines per row
-    const int n_rows = max(0, k_end - k_begin - NST * 4 * TILE);
+    const int ask_limit = (32 << 20) / (int)(gridDim.x * gridDim.y * gridDim.z) / (HS * 4);
+    const int n_rows = min(ask_limit, max(0, k_end - k_begin - NST * 4 * TILE));
     for (int i = tid; i < n_rows * LINES * 2; i += THREADS) {
       const int which = i & 1, line = (i >> 1) % LINES, kp = k_begin + NST * 4 * TILE + (i >> 1) / LINES;
       const size_t row = row_of(kp);
@@ -320,8 +324,8 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
       cp_async_wait_pending(min(n_tiles - 1 - j, NST - 1));          // tile j has landed; later ones may still fly
       __syncwarp();
       if (pos < t + TILE) {                                       // pos >= t: the range ends at pos
-        // The newest row: not valid when the tile was requested early, and a copy of its line
-        // from before may sit in this SM's L1.  It is taken from the CTA's own copy, or from L2.
+        // The newest row: not valid when the tile was requested early (before the wait for the
+        // kernels of this step).  It is taken from the CTA's own copy, or from L2.
         if (lane < 2 * CH) {
           const int c = lane % CH, kl = pos - t;
           const bool is_v = lane >= CH;

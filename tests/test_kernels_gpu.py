@@ -643,6 +643,49 @@ def test_decode_attention_with_more_ctas_than_one_wave(ops, fused, B, NH, NKV, H
     assert float(err.max()) < 1e-2, f"entry {int(err.argmax())} of length {lens[int(err.argmax())]}: {float(err.max()):.3e}"
 
 
+@pytest.mark.parametrize("B,NH,NKV,HS,longest,window,splits", [
+    (1, 8, 2, 64, 9000, 0, None),        # the planner's choice for long ranges: 36 ranges of deep stages
+    (1, 8, 1, 128, 20000, 0, 64),        # the most ranges the merge takes
+    (3, 32, 4, 64, 5000, 0, None),       # 24 ranges, counter merge
+    (2, 4, 4, 64, 4100, 3000, 7),        # seven long ranges: no cluster although it would fit one
+    (40, 8, 8, 128, 2100, 0, None)])     # one long range per CTA
+def test_decode_attention_over_long_contexts(ops, B, NH, NKV, HS, longest, window, splits):
+    """Thousands of keys per request: many ranges merged through the scratch, deep stages, the
+    bounded request of later tiles into L2; one far key per request made to stand out, so that a
+    range lost or merged twice shows.  Against the float64 formula."""
+    torch.manual_seed(5)
+    dtype, page = torch.bfloat16, 16
+    g = torch.Generator().manual_seed(B + longest)
+    lens = [longest] + [int(x) for x in torch.randint(longest // 2, longest, (B - 1,), generator=g)]
+    W = -(-longest // page)
+    n_pages = sum(-(-n // page) for n in lens) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    kp = torch.randn(n_pages, NKV, page, HS, device=DEV).to(dtype)
+    vp = torch.randn(n_pages, NKV, page, HS, device=DEV).to(dtype)
+    bt = torch.zeros(B, W, dtype=torch.int32)
+    at = 0
+    for b, n in enumerate(lens):
+        k = -(-n // page)
+        bt[b, :k] = torch.tensor(perm[at:at + k], dtype=torch.int32)
+        at += k
+    q = torch.randn(B, NH * HS, device=DEV).to(dtype)
+    # the far key: one position per request (inside the window) whose key is the first head's query, scaled
+    for b, n in enumerate(lens):
+        lo = max(0, n - window) if window else 0
+        far = lo + (n - lo) // 7
+        pg, off = int(bt[b, far // page]), far % page
+        kp[pg, 0, off] = (q[b, :HS].float() * 1.5).to(dtype)      # score 12 or 17 against N(0, 1)
+    scale = 1.0 / math.sqrt(HS)
+    out = torch.zeros(B, NH * HS, device=DEV, dtype=dtype)
+    kv_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    if splits is None:
+        assert ops.decode_splits(B, NKV, W * page) > 16 or B * NKV >= 2 * ops.sm_count() // 2
+    ops.paged_attention_decode(out, q, kp, vp, bt.to(DEV), kv_lens, B, NH, NKV, HS, window, scale, splits=splits)
+    ref = _plain_decode_attention(q, kp, vp, bt, lens, NH, NKV, HS, page, window, scale)
+    err = (out.double().cpu() - ref).abs().max(dim=1).values / ref.abs().max()
+    assert float(err.max()) < 1e-2, f"entry {int(err.argmax())} of length {lens[int(err.argmax())]}: {float(err.max()):.3e}"
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("HS,splits", [(64, 1), (64, 3), (128, 12), (48, 2)])
 def test_decode_attention_with_an_entry_that_holds_no_keys(ops, dtype, HS, splits):
