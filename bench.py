@@ -445,12 +445,17 @@ def main() -> int:
             for k in range(warmup, warmup + 4):
                 run(k)
             torch.cuda.synchronize()
-        evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and e.name
-               and "Memcpy" not in e.name and "Memset" not in e.name]
+        on_gpu = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and e.name]
+        evs = [e for e in on_gpu if "Memcpy" not in e.name and "Memset" not in e.name]
         evs.sort(key=lambda e: e.time_range.start)
         per_step = len(evs) // 4
         step = evs[2 * per_step:3 * per_step]
         span = step[-1].time_range.end - step[0].time_range.start
+        # what lies between two steps launched back to back: the copies and fills of the step, the graph's start
+        gap0, gap1 = evs[2 * per_step - 1].time_range.end, step[0].time_range.start
+        between = [e for e in on_gpu if gap0 <= e.time_range.start < gap1 and ("Memcpy" in e.name or "Memset" in e.name)]
+        print(f"{gap1 - gap0:.1f} us from the last end of the step before to this step's first start; in between: "
+              + ", ".join(f"{e.name.split('(')[0].strip()} {e.time_range.start - gap0:.1f}..{e.time_range.end - gap0:.1f}" for e in between))
         what = f"batch {args.batch}" if args.mode == "timeline" else f"prompt of {PREFILL_TOKENS} tokens"
         print(f"{what}, {args.layers} layers: {per_step} kernels a step, {span:.1f} us from the first start to the last end")
         agg = collections.OrderedDict()
@@ -509,10 +514,11 @@ def main() -> int:
         reps = []
         for k in range(5):
             rid = f"p{k}"
+            tokens = prompt(PREFILL_TOKENS)              # the request's token ids exist before the step is asked for
             torch.cuda.synchronize()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            eng.step([StepEntry(rid, prompt(PREFILL_TOKENS), [PREFILL_TOKENS - 1])])
+            eng.step([StepEntry(rid, tokens, [PREFILL_TOKENS - 1])])
             b.record()
             torch.cuda.synchronize()
             reps.append(a.elapsed_time(b))

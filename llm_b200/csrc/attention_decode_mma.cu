@@ -11,7 +11,7 @@ template <bool FUSED>
 int launch_decode_mma(void* out, long long out_stride, const void* q, long long q_stride, const void* k_pages,
                       const void* v_pages, const int* block_table, int table_width, const int* kv_lens,
                       int n_entries, int n_heads, int n_kv, int head_dim, int page_size, float scale, int window,
-                      int splits, float* scratch, decode_mma::FusedQkv fused, cudaStream_t stream) {
+                      int splits, int max_keys, float* scratch, decode_mma::FusedQkv fused, cudaStream_t stream) {
   dim3 grid(splits, n_kv, n_entries);
   const float scale_log2e = scale * 1.4426950408889634f;
   const int group_rows = n_heads / n_kv < decode_mma::ROWS ? n_heads / n_kv : decode_mma::ROWS;
@@ -20,10 +20,11 @@ int launch_decode_mma(void* out, long long out_stride, const void* q, long long 
   // clusters against 23 us with the counter-based merge; at 8 requests 9.3 us against 13.5 us.)
   constexpr int RECV_LIMIT = 64 * 1024;
   const int recv_bytes = (splits - 1) * group_rows * head_dim * 4;
-  // Only for short ranges (up to 512 keys of the longest request the table holds): a cluster's
-  // CTA has one stage, which is right when a range is a tile or two per warp and the merge is what
-  // counts; a long range wants the deep stages.
-  const long long range_keys = ((long long)table_width * page_size + splits - 1) / splits;
+  // Only for short ranges (up to 512 keys of the longest request: max_keys, or what the table
+  // holds): a cluster's CTA has one stage, which is right when a range is a tile or two per warp
+  // and the merge is what counts; a long range wants the deep stages.
+  const long long most_keys = max_keys > 0 ? max_keys : (long long)table_width * page_size;
+  const long long range_keys = (most_keys + splits - 1) / splits;
   const bool cluster = splits >= 2 && splits <= 8 && (long long)splits * n_kv * n_entries <= 2 * llmk_sm_count() &&
                        recv_bytes <= RECV_LIMIT && range_keys <= 512;
   // Without a cluster: deep stages (three at head size 64, else two) while the whole grid fits on
@@ -85,12 +86,13 @@ LLMK_API int llmk_paged_attention_decode_mma_supported(const void* q, long long 
 }
 
 // As llmk_paged_attention_decode (same arguments, same scratch), on the warp-level tensor cores:
-// the query heads of a group as rows of the MMAs.
+// the query heads of a group as rows of the MMAs.  max_keys: an upper bound of kv_lens that the
+// host knows (0: what a row of the table holds); it only picks between variants of the kernel.
 LLMK_API int llmk_paged_attention_decode_mma(void* out, long long out_stride, const void* q, long long q_stride,
                                              const void* k_pages, const void* v_pages, const int* block_table,
                                              int table_width, const int* kv_lens, int n_entries, int n_heads, int n_kv,
                                              int head_dim, int page_size, int window, float scale, int splits,
-                                             float* scratch, int dtype, cudaStream_t stream) {
+                                             float* scratch, int dtype, int max_keys, cudaStream_t stream) {
   if (n_entries == 0) return 0;
   LLMK_REQUIRE(llmk_paged_attention_decode_mma_supported(q, q_stride, head_dim, page_size, dtype),
                "attention_decode_mma: needs bfloat16, a head size of 64 or 128 (got %d) and pages of a power of two (got %d)",
@@ -102,7 +104,7 @@ LLMK_API int llmk_paged_attention_decode_mma(void* out, long long out_stride, co
                n_entries, n_kv, decode_mma::COUNTER_WORDS);
   LLMK_REQUIRE(window >= 0, "attention_decode_mma: bad window %d", window);
   return launch_decode_mma<false>(out, out_stride, q, q_stride, k_pages, v_pages, block_table, table_width, kv_lens,
-                                  n_entries, n_heads, n_kv, head_dim, page_size, scale, window, splits, scratch,
+                                  n_entries, n_heads, n_kv, head_dim, page_size, scale, window, splits, max_keys, scratch,
                                   decode_mma::FusedQkv{}, stream);
 }
 
@@ -130,7 +132,7 @@ LLMK_API int llmk_decode_attention_fused(void* out, long long out_stride, const 
                                          void* v_pages, const int* block_table, int table_width, const int* kv_lens,
                                          int n_entries, int n_heads, int n_kv, int head_dim, int page_size,
                                          int window, float scale, int splits, int write_kv, float* scratch,
-                                         cudaStream_t stream) {
+                                         int max_keys, cudaStream_t stream) {
   if (n_entries == 0) return 0;
   LLMK_REQUIRE(llmk_decode_attention_fused_supported(qkv, partials, split_stride, src_stride, cos_table, sin_table, head_dim, LLMK_BF16),
                "decode_attention_fused: needs bfloat16, a head size of 64 or 128 (got %d) and 16-byte aligned rows", head_dim);
@@ -145,6 +147,6 @@ LLMK_API int llmk_decode_attention_fused(void* out, long long out_stride, const 
                "decode_attention_fused: a row of %lld values does not hold the heads", src_stride);
   decode_mma::FusedQkv f{{(const __nv_bfloat16*)qkv, partials, qkv_splits, split_stride}, src_stride, cos_table, sin_table, write_kv};
   return launch_decode_mma<true>(out, out_stride, nullptr, 0, k_pages, v_pages, block_table, table_width, kv_lens,
-                                 n_entries, n_heads, n_kv, head_dim, page_size, scale, window, splits, scratch, f, stream);
+                                 n_entries, n_heads, n_kv, head_dim, page_size, scale, window, splits, max_keys, scratch, f, stream);
 }
 

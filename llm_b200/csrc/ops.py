@@ -283,27 +283,28 @@ def decode_splits(n_entries: int, n_kv: int, max_keys: int) -> int:
 
 def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                            block_table: torch.Tensor, kv_lens: torch.Tensor, n_entries: int, n_heads: int,
-                           n_kv: int, head_dim: int, window: int, scale: float, splits=None) -> None:
-    """One query token per entry (row e of q), attending to its request's kv_lens[e] keys."""
+                           n_kv: int, head_dim: int, window: int, scale: float, splits=None, max_keys: int = 0) -> None:
+    """One query token per entry (row e of q), attending to its request's kv_lens[e] keys.
+    max_keys: an upper bound of kv_lens, if the host knows one below the table's width."""
     _rows_contig(out, "out"); _rows_contig(q, "q")
     assert block_table.dim() == 2 and block_table.is_contiguous() and block_table.dtype == torch.int32
     assert kv_lens.dtype == torch.int32 and k_pages.is_contiguous() and v_pages.is_contiguous()
     assert q.dtype == k_pages.dtype == out.dtype
     page = k_pages.shape[2]
     if splits is None:
-        splits = decode_splits(n_entries, n_kv, block_table.shape[1] * page)
+        splits = decode_splits(n_entries, n_kv, max_keys or block_table.shape[1] * page)
     buf = _attn_partials(q.device, _decode_scratch_floats(n_entries, n_heads, head_dim, splits))
     args = (_ptr(out), c_longlong(out.stride(0)), _ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
             _ptr(block_table), c_int(block_table.shape[1]), _ptr(kv_lens), c_int(n_entries), c_int(n_heads),
             c_int(n_kv), c_int(head_dim), c_int(page), c_int(window or 0), c_float(scale), c_int(splits),
-            c_void_p(buf.data_ptr()), c_int(_kind(q.dtype)), _stream())
+            c_void_p(buf.data_ptr()), c_int(_kind(q.dtype)))
     # bfloat16 with a head size of 64 or 128 and pages of a power of two: the query heads of a
     # group as rows of warp-level MMAs (tensor-core library); everything else on the CUDA cores
     if (q.dtype == torch.bfloat16 and head_dim in (64, 128) and page & (page - 1) == 0
             and q.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0):
-        _check_t(load_tensor().llmk_paged_attention_decode_mma(*args))
+        _check_t(load_tensor().llmk_paged_attention_decode_mma(*args, c_int(max_keys), _stream()))
     else:
-        _check(load().llmk_paged_attention_decode(*args))
+        _check(load().llmk_paged_attention_decode(*args, _stream()))
 
 
 def _decode_scratch_floats(n_entries: int, n_heads: int, head_dim: int, splits: int) -> int:
@@ -326,7 +327,7 @@ def decode_attention_fused_supported(qkv, cos, sin, head_dim: int, page_size: in
 def decode_attention_fused(out: torch.Tensor, qkv, cos, sin, k_pages: torch.Tensor, v_pages: torch.Tensor,
                            block_table: torch.Tensor, kv_lens: torch.Tensor, n_entries: int, n_heads: int,
                            n_kv: int, head_dim: int, window: int, scale: float, write_kv: bool = True,
-                           splits=None) -> None:
+                           splits=None, max_keys: int = 0) -> None:
     """One new token per entry: row e of qkv (a tensor or a PartialSum) holds its q, k and v
     heads (q alone if not write_kv).  q and k are rotated at position kv_lens[e] - 1, k and v are
     stored there in the entry's pages, and the token attends to its request's kv_lens[e] keys."""
@@ -336,7 +337,7 @@ def decode_attention_fused(out: torch.Tensor, qkv, cos, sin, k_pages: torch.Tens
     assert qkv.dtype == k_pages.dtype == out.dtype == torch.bfloat16
     page = k_pages.shape[2]
     if splits is None:
-        splits = decode_splits(n_entries, n_kv, block_table.shape[1] * page)
+        splits = decode_splits(n_entries, n_kv, max_keys or block_table.shape[1] * page)
     lib = load_tensor()
     buf = _attn_partials(out.device, _decode_scratch_floats(n_entries, n_heads, head_dim, splits))
     d, parts, qkv_splits, stride = _split_args(qkv)
@@ -347,7 +348,7 @@ def decode_attention_fused(out: torch.Tensor, qkv, cos, sin, k_pages: torch.Tens
         _ptr(out), c_longlong(out.stride(0)), d, parts, qkv_splits, stride, c_longlong(src_stride), _ptr(cos),
         _ptr(sin), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), c_int(block_table.shape[1]), _ptr(kv_lens),
         c_int(n_entries), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(page), c_int(window or 0),
-        c_float(scale), c_int(splits), c_int(int(write_kv)), c_void_p(buf.data_ptr()), _stream()))
+        c_float(scale), c_int(splits), c_int(int(write_kv)), c_void_p(buf.data_ptr()), c_int(max_keys), _stream()))
 
 
 def attention_tc_supported(dtype, n_heads: int, n_kv: int, head_dim: int, page_size: int) -> bool:
@@ -393,7 +394,7 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
             max_keys = min(max_keys, window)
         paged_attention_decode(out, qkv, k_pages, v_pages, group.block_table, ctx.kv_lens, ctx.n_entries,
                                n_heads, n_kv, head_dim, window, scale,
-                               splits=decode_splits(ctx.n_entries, n_kv, max_keys))
+                               splits=decode_splits(ctx.n_entries, n_kv, max_keys), max_keys=max_keys)
         return
     if attention_tc_supported(qkv.dtype, n_heads, n_kv, head_dim, k_pages.shape[2]) and qkv.stride(0) % 8 == 0:
         attention_tc(out, qkv, k_pages, v_pages, group.block_table, ctx.cu_tokens, ctx.kv_lens, ctx.n_tokens,
@@ -420,7 +421,7 @@ def rope_store_attend(out, qkv, cos, sin, k_pages, v_pages, group, ctx, n_heads:
             max_keys = min(max_keys, window)
         decode_attention_fused(out, qkv, cos, sin, k_pages, v_pages, group.block_table, ctx.kv_lens, ctx.n_entries,
                                n_heads, n_kv, head_dim, window, scale, write_kv=write_kv,
-                               splits=decode_splits(ctx.n_entries, n_kv, max_keys))
+                               splits=decode_splits(ctx.n_entries, n_kv, max_keys), max_keys=max_keys)
         return
     q = rope_kv_write(qkv, cos, sin, ctx.positions, group.slot_map, k_pages, v_pages, ctx.n_tokens, n_heads,
                       n_kv if write_kv else 0, head_dim, q_out=q_rot() if isinstance(qkv, PartialSum) else None)

@@ -42,10 +42,12 @@ def test_embedding_and_bad_id(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden,eps", [(72, 1e-5), (1000, 1e-6), (2048, 1e-2), (8961, 1e-5)])
-def test_add_rmsnorm(ops, dtype, hidden, eps):
+@pytest.mark.parametrize("rows,hidden,eps", [(7, 72, 1e-5), (7, 1000, 1e-6), (7, 2048, 1e-2), (7, 8961, 1e-5),
+                                             # as many rows as a prompt step has
+                                             (701, 2048, 1e-5), (650, 1000, 1e-5), (603, 4096, 1e-6), (600, 2056, 1e-5),
+                                             (1200, 8, 1e-5), (640, 4104, 1e-5)])
+def test_add_rmsnorm(ops, dtype, rows, hidden, eps):
     torch.manual_seed(1)
-    rows = 7
     resid = torch.randn(rows + 1, hidden, device=DEV) * 3
     delta = torch.randn(rows, hidden, device=DEV).to(dtype)
     gain = 1 + 0.1 * torch.randn(hidden, device=DEV)
@@ -405,7 +407,7 @@ def test_decode_kernels_find_a_far_key_and_respect_the_window_edge(ops, HS, page
         assert float((out3[0, h * HS:(h + 1) * HS].float().cpu() - v_new.float()).abs().max()) < 2e-2
 
 
-@pytest.mark.parametrize("HS,page", [(64, 16), (128, 64)])
+@pytest.mark.parametrize("HS,page", [(64, 16), (64, 32), (128, 64)])
 def test_tensor_core_attention_finds_a_far_key_and_respects_the_window_edge(ops, HS, page):
     """The prompt kernel: 40 new tokens after 660 cached ones, every query scoring one far key
     overwhelmingly.  Each row must return that key's value exactly as long as its own window
@@ -776,7 +778,8 @@ def test_consumers_sum_split_k_partials_themselves(ops):
                                                    (6, 2, 64, 16, 37), (2, 1, 128, 16, 0), (8, 2, 128, 32, 200), (5, 1, 128, 128, 0)])
 def test_tensor_core_attention_matches_the_general_kernel(ops, NH, NKV, HS, page, window):
     """A ragged batch: a long prompt portion that starts deep in its request, short portions,
-    single tokens, shuffled pages; compared with the general kernel on the same cache."""
+    single tokens, shuffled pages; compared with the general kernel on the same cache and with
+    the formula."""
     torch.manual_seed(13)
     # (keys already cached, new tokens) per entry
     plan = [(300, 150), (0, 37), (511, 1), (129, 1), (0, 1), (250, 6)]
