@@ -322,6 +322,50 @@ def reference_arm(args, warmup: int) -> int:
         shutil.rmtree(folder, ignore_errors=True)
 
 
+def decode_attention_sweep(args, peaks, torch, ops) -> int:
+    """The decode attention kernel alone: one query token per request over `ctx` cached keys, pages
+    in shuffled order, several sets of pages in turn so that no launch finds its keys in L2; timed
+    as one CUDA graph of all launches.  Bytes are the keys and values that a launch has to read."""
+    import math
+    n_heads, n_kv, hs = (int(x) for x in args.heads.split(","))
+    page, dev = 16, "cuda:0"
+    cases = [(args.batch, args.ctx)] if args.ctx else [(b, c) for b in (1, 8, 64) for c in (512, 2048, 8192, 32768)
+                                                       if b * c * 4 * n_kv * hs <= 2.2e9]
+    print(f"decode attention, {n_heads} query heads, {n_kv} kv heads, head size {hs}, pages of {page}; "
+          f"peak {peaks['hbm_gbs']:.0f} GB/s ({peaks['source']})")
+    for batch, ctx in cases:
+        per_req = -(-ctx // page)
+        nbytes = batch * ctx * 4 * n_kv * hs
+        sets = min(64, max(2, math.ceil(300e6 / nbytes)))
+        k_pages = torch.randn(sets * batch * per_req, n_kv, page, hs, device=dev, dtype=torch.bfloat16)
+        v_pages = torch.randn_like(k_pages)
+        tables = torch.randperm(sets * batch * per_req, device=dev).to(torch.int32).view(sets, batch, per_req).contiguous()
+        kv_lens = torch.full((batch,), ctx, dtype=torch.int32, device=dev)
+        q = torch.randn(batch, n_heads * hs, device=dev, dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        call = lambda i: ops.paged_attention_decode(out, q, k_pages, v_pages, tables[i % sets], kv_lens, batch, n_heads, n_kv,
+                                                    hs, 0, 1.0 / math.sqrt(hs), max_keys=ctx)
+        for i in range(3):
+            call(i)
+        torch.cuda.synchronize()
+        n = max(sets, 8)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(n):
+                call(i)
+        graph.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); graph.replay(); b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) / n * 1e3
+        gbs = nbytes / us / 1e3
+        print(f"batch {batch:3d} context {ctx:6d} ranges {ops.decode_splits(batch, n_kv, ctx):2d}: {us:8.1f} us a launch, "
+              f"{nbytes / 1e6:7.1f} MB, {gbs:7.1f} GB/s = {gbs / peaks['hbm_gbs']:.2f} of the peak")
+        del k_pages, v_pages, tables
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -333,9 +377,14 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip prefill and the batch 1 / 64 points")
     ap.add_argument("--no-shapes", action="store_true",
                     help="skip the runs at the Llama-2-7B and Llama-3-8B shapes, the many-request load and the 32-bit check")
-    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill", "timeline", "timeline_prefill"],
+    ap.add_argument("--mode", default="all",
+                    choices=["all", "decode", "prefill", "timeline", "timeline_prefill", "decode_attention"],
                     help="decode / prefill: only that measurement, for small profiling runs (not the benchmark line); "
-                         "timeline: the kernels of one decode layer with their start and end inside the step's CUDA graph")
+                         "timeline: the kernels of one decode layer with their start and end inside the step's CUDA graph; "
+                         "decode_attention: the decode attention kernel alone over batches and context lengths "
+                         "(--batch with --ctx: that one case)")
+    ap.add_argument("--ctx", type=int, default=0, help="decode_attention: the context length of the one case to run")
+    ap.add_argument("--heads", default="32,4,64", help="decode_attention: query heads, kv heads, head size")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -353,6 +402,8 @@ def main() -> int:
     from llm_b200.engine.llm import LLM
 
     peaks = load_peaks()
+    if args.mode == "decode_attention":
+        return decode_attention_sweep(args, peaks, torch, ops)
     cfg = dict(MODEL, num_hidden_layers=args.layers)
     if args.mode != "all":
         args.no_points = True
