@@ -267,16 +267,16 @@ def _attn_partials(device, n_floats: int) -> torch.Tensor:
     return buf
 
 
-def decode_splits(n_entries: int, n_kv: int, max_keys: int) -> int:
+def decode_splits(n_entries: int, n_kv: int, max_keys: int, sms: int = 0) -> int:
     """How many ranges the keys of one request are cut into.  Up to 2,048 keys: ranges of about
     128 keys (one tile of 32 per warp of a CTA) while the batch is small and the kernel bound by
     latency, fewer and longer ones as (requests x kv heads) grows, so that about 256 CTAs run; at
     most 16, and clusters of 7 or 8 CTAs measured slower than 6 longer ranges.  Beyond that the
     kernel is bound by bytes: as many ranges of at least 256 keys as fill the SMs with two CTAs
-    each in one wave, at most 64."""
+    each in one wave, at most 64.  sms: the device's SM count, if the caller has it."""
     pairs = max(1, n_entries * n_kv)
     if max_keys > 2048:
-        return max(1, min(64, (2 * sm_count()) // pairs, _ceil_div(max_keys, 256)))
+        return max(1, min(64, (2 * (sms or sm_count())) // pairs, max_keys // 256))
     s = max(1, min(16, _ceil_div(max_keys, 128), 256 // pairs))
     return 6 if s in (7, 8) else s
 

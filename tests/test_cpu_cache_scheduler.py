@@ -381,3 +381,23 @@ def test_freed_pages_are_logged_for_the_poison_fill():
     assert sorted(c.take_freed_pages(0)) == sorted(held_full)
     assert sorted(c.take_freed_pages(1)) == sorted(held_win[2:])
     c.check()
+
+
+def test_ranges_of_the_decode_attention():
+    """How many ranges the keys of a request are cut into (pure arithmetic, no device): always 1
+    to 64; short contexts in ranges of at least about 128 keys and at most 16 of them; long ones
+    in ranges of at least 256 keys, as many as give two CTAs per SM in one wave."""
+    from llm_b200.csrc.ops import decode_splits
+    sms = 148
+    for entries in (1, 2, 3, 8, 24, 64, 300):
+        for n_kv in (1, 4, 8):
+            for keys in (1, 100, 520, 1024, 2048, 2049, 4096, 8192, 40000, 1 << 20):
+                s = decode_splits(entries, n_kv, keys, sms)
+                assert 1 <= s <= 64
+                if keys <= 2048:
+                    assert s <= 16 and (s == 1 or keys / s >= 64)
+                else:
+                    assert s == 1 or (keys / s >= 256 and s * entries * n_kv <= 2 * sms)
+    assert decode_splits(8, 4, 520, sms) in (4, 5, 6)          # the benchmark's step: ranges of about 100 keys
+    assert decode_splits(8, 4, 16384, sms) == 9                # 288 CTAs on 148 SMs
+    assert decode_splits(1, 4, 1 << 20, sms) == 64

@@ -89,6 +89,33 @@ def test_every_cut_matches_plain_with_peaked_attention(models, name, dtype):
     eng.cache.check()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_at_a_context_of_thousands_of_keys(tmp_path_factory, dtype):
+    """A prompt of 5,100 tokens in portions of 1,024 (the prompt attention over a long cache), then
+    70 tokens one by one from replayed graphs (the decode attention cut into dozens of ranges, the
+    count of keys crossing a bucket's edge), with peaked attention so that a lost or doubled range
+    of keys would show; every decoded position against the plain implementation."""
+    from llm_b200.config import EngineOptions
+    from llm_b200.engine.engine import Engine, StepEntry
+    cfg, page = CONFIGS["H"]
+    d = make_model_dir(tmp_path_factory.mktemp("long"), "H", dtype, peaked=True)
+    n, tail = 5170, 70
+    toks = random_tokens(n, cfg["vocab_size"], 77)
+    rows = list(range(n - tail, n))
+    ref = plain_llama.forward(cfg, load_plain_weights(d), toks, rows=rows)
+    eng = Engine(d, EngineOptions(dtype=dtype, kv_block_size=page, max_num_seqs=2, max_num_batched_tokens=1024,
+                                  num_kv_blocks=n // page + 3, use_cuda_graphs=True, poison_freed_pages=True))
+    head = n - tail
+    for at in range(0, head, 1024):
+        eng.step([StepEntry("x", toks[at:min(at + 1024, head)], [])])
+    got = torch.stack([eng.step([StepEntry("x", [t], [0])])[0].double().cpu() for t in toks[head:]])
+    eng.check_status()
+    err_rows = (got - ref).abs().max(dim=1).values / ref.abs().max()
+    bad = torch.nonzero(err_rows > TOL[dtype])
+    assert bad.numel() == 0, f"first differs at position {head + int(bad[0])}: {float(err_rows[int(bad[0])]):.3e}"
+    assert eng.counters["graph_replays"] >= tail - 4
+
+
 def test_peaked_attention_shows_one_wrong_page(models):
     """What the peaked weights are for: two pages of values that trade places (the keys stay) move
     the bfloat16 logits of the next token far beyond the bound, while on the plain random weights,

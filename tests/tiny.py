@@ -43,8 +43,15 @@ CONFIG_G = dict(architectures=["LlamaForCausalLM"], hidden_size=96, intermediate
                 vocab_size=277, rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=256,
                 tie_word_embeddings=True, sliding_window=53, attention_bias=True, hidden_act="silu")
 
+# H: room for a context of thousands of keys (the decode attention's many ranges, long tables of pages).
+CONFIG_H = dict(architectures=["LlamaForCausalLM"], hidden_size=128, intermediate_size=200,
+                num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                vocab_size=290, rms_norm_eps=1e-5, rope_theta=100000.0, max_position_embeddings=6144,
+                tie_word_embeddings=False, hidden_act="silu")
+
 CONFIGS = {"A": (CONFIG_A, 16), "B": (CONFIG_B, 8), "C": (CONFIG_C, 32),
-           "D": (CONFIG_D, 16), "E": (CONFIG_E, 32), "F": (CONFIG_F, 16), "G": (CONFIG_G, 8)}   # name -> (config, page size)
+           "D": (CONFIG_D, 16), "E": (CONFIG_E, 32), "F": (CONFIG_F, 16), "G": (CONFIG_G, 8),
+           "H": (CONFIG_H, 16)}   # name -> (config, page size)
 
 
 def make_model_dir(tmp_root, name: str, dtype: str, seed: int = 1234, peaked: bool = False) -> str:
