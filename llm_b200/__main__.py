@@ -7,6 +7,8 @@ once all requests are finished.
 
     python -m llm_b200 --model DIR [--dtype bfloat16] [--max-new-tokens 256] < prompts.txt
     python -m llm_b200 --model DIR --random-config config.json --random-seed 1   # writes DIR first
+    python -m llm_b200 --model DIR --prompt-ids "1,2,3" --prompt-ids "7 8"       # requests from the command line
+    python -m llm_b200 --model DIR --prompt-file prompts.txt                     # or from a file, one per line
 """
 from __future__ import annotations
 
@@ -39,6 +41,9 @@ def main(argv=None) -> int:
     p.add_argument("--random-config", default=None,
                    help="a config.json: write a random-weights model into --model first")
     p.add_argument("--random-seed", type=int, default=0)
+    p.add_argument("--prompt-ids", action="append", default=[],
+                   help="a request's token ids (may be given several times); standard input is then not read")
+    p.add_argument("--prompt-file", default=None, help="requests from this file instead of standard input, one per line")
     args = p.parse_args(argv)
 
     if args.random_config:
@@ -53,7 +58,17 @@ def main(argv=None) -> int:
               num_kv_blocks=args.num_kv_blocks, gpu_memory_utilization=args.gpu_memory_utilization,
               use_cuda_graphs=not args.no_cuda_graphs)
 
+    given = None
+    if args.prompt_ids or args.prompt_file:
+        given = [parse_line(x) for x in args.prompt_ids]
+        if args.prompt_file:
+            with open(args.prompt_file, "r", encoding="utf-8") as f:
+                given += [parse_line(line) for line in f if line.strip()]
+        given.reverse()
+
     def receive(wait: bool):
+        if given is not None:                   # all requests are known: hand them over one by one
+            return given.pop() if given else None
         while True:
             if not wait and not select.select([sys.stdin], [], [], 0)[0]:
                 return None

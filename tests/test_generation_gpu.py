@@ -124,6 +124,15 @@ def test_command_line(folders, tmp_path):
     lines = dict(l.split(": ") for l in proc.stdout.strip().split("\n"))
     for i, p in enumerate(prompts):
         assert [int(x) for x in lines[str(i)].split()] == pl.greedy_generate(cfg, w, p, 6)
+    # the same requests named on the command line and in a file instead of standard input
+    listed = tmp_path / "prompts.txt"
+    listed.write_text(" ".join(str(t) for t in prompts[1]) + "\n")
+    proc = subprocess.run([sys.executable, "-m", "llm_b200", "--model", d, "--dtype", "float32", "--max-new-tokens", "6",
+                           "--eos-token-id", "-1", "--num-kv-blocks", "16", "--max-num-seqs", "2",
+                           "--prompt-ids", ",".join(str(t) for t in prompts[0]), "--prompt-file", str(listed)],
+                          stdin=subprocess.DEVNULL, capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert dict(l.split(": ") for l in proc.stdout.strip().split("\n")) == lines
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
