@@ -384,6 +384,7 @@ def main() -> int:
                          "decode_attention: the decode attention kernel alone over batches and context lengths "
                          "(--batch with --ctx: that one case)")
     ap.add_argument("--ctx", type=int, default=0, help="decode_attention: the context length of the one case to run")
+    ap.add_argument("--prompt-tokens", type=int, default=PREFILL_TOKENS, help="timeline_prefill: tokens of the prompt step")
     ap.add_argument("--heads", default="32,4,64", help="decode_attention: query heads, kv heads, head size")
     args = ap.parse_args()
 
@@ -487,7 +488,7 @@ def main() -> int:
             run = lambda k: eng.step(entries(k))
         else:
             def run(k):
-                eng.step([StepEntry(f"p{k}", prompt(PREFILL_TOKENS), [PREFILL_TOKENS - 1])])
+                eng.step([StepEntry(f"p{k}", prompt(args.prompt_tokens), [args.prompt_tokens - 1])])
                 eng.release(f"p{k}")
         for k in range(warmup):
             run(k)
@@ -507,7 +508,7 @@ def main() -> int:
         between = [e for e in on_gpu if gap0 <= e.time_range.start < gap1 and ("Memcpy" in e.name or "Memset" in e.name)]
         print(f"{gap1 - gap0:.1f} us from the last end of the step before to this step's first start; in between: "
               + ", ".join(f"{e.name.split('(')[0].strip()} {e.time_range.start - gap0:.1f}..{e.time_range.end - gap0:.1f}" for e in between))
-        what = f"batch {args.batch}" if args.mode == "timeline" else f"prompt of {PREFILL_TOKENS} tokens"
+        what = f"batch {args.batch}" if args.mode == "timeline" else f"prompt of {args.prompt_tokens} tokens"
         print(f"{what}, {args.layers} layers: {per_step} kernels a step, {span:.1f} us from the first start to the last end")
         agg = collections.OrderedDict()
         prev_end = None

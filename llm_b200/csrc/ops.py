@@ -470,8 +470,10 @@ def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool, pai
     k-blocks times a k-block's time, fitted to timings of the products of the 1.1B and 7B shapes
     at 129 to 4,096 rows; plus the sum of the partial results where K is split."""
     kb = _ceil_div(K, 64)
-    if M <= 128:
+    if M < NORMAL_MODE_FROM_ROWS:
         return _plan_swapped(M, N, kb, fused_reduce, _SMS, cta_limit)
+    if M <= 128:
+        return _plan_few_rows(M, N, kb, fused_reduce, _SMS, cta_limit)
     best = None
     for tile in (256, 224, 192, 160, 128):
         tiles = _ceil_div(M, 128) * _ceil_div(N, tile)
@@ -505,6 +507,46 @@ def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool, pai
             cost = waves * kb * t_kb + 8.6
             if cost < best[0] - 1e-9:
                 best = (cost, False, tile, 1, kb, 3)
+    return best[1:]
+
+
+# From this many rows on (up to 128) the rows take the 128-row side of the MMA like a prompt's, one
+# CTA per tile of 128 weight rows with the SM and a ring of 192 KB to itself, instead of the
+# swapped mode's two CTAs per SM with rings half that size.  Measured on the four products of the
+# 1.1B shape with the kernel that sums the partial results behind them (us, swapped -> normal):
+# 32 rows 9.2 -> 8.5, 7.5 -> 6.7, 15.0 -> 10.6, 9.5 -> 10.2; 64 rows 11.4 -> 9.8, 9.3 -> 7.7, 17.9 ->
+# 11.1, 11.6 -> 11.0; 128 rows 15.2 -> 10.7, 13.2 -> 9.1, 27.5 -> 11.8, 16.1 -> 12.6; at 16 rows and
+# fewer the swapped mode is ahead (7.9 against 8.2, 8.0 against 10.0).
+NORMAL_MODE_FROM_ROWS = 32
+
+
+def _plan_few_rows(M: int, N: int, kb: int, fused_reduce: bool, _SMS: int, cta_limit: int = 0):
+    """The normal mode for 32 to 128 rows: tiles of 128 or 256 weight rows, one per CTA, K split
+    over CTAs while there are too few tiles to draw the memory's bandwidth.  The estimate, in
+    microseconds: a CTA's ring holds 192 KB in flight against a latency of about 1.5 us, of which
+    the weights are a half (tiles of 128) or two thirds (of 256); the CTAs of a round share the
+    measured 6.5 TB/s; a round costs a microsecond beside its bytes, the launch 1.6; partial
+    results are written and read back where K is split.  Checked against timings of the products
+    of the 1.1B, 7B and 8B shapes at 32, 64 and 128 rows."""
+    best = None
+    for tile in (128, 256):
+        tiles = _ceil_div(N, tile)
+        per_cta = 0.128e6 * tile / (128 + tile)                   # bytes of weights per microsecond that one CTA can draw
+        for s in range(1, min(kb, 16) + 1):
+            per = _ceil_div(kb, s)
+            if _ceil_div(kb, per) != s:
+                continue
+            if s > 1 and (s * M * N * 4 > _PARTIAL_BYTES or (cta_limit and tiles * s > cta_limit)):
+                break
+            cta_bytes, left, cost = tile * per * 128, tiles * s, 1.6
+            while left > 0:
+                r = min(left, _SMS)
+                cost += cta_bytes * r / min(6.5e6, r * per_cta) + 1.0
+                left -= r
+            if s > 1:
+                cost += 2 * s * M * N * 4 / 7e6 + (0.5 * _ceil_div(s, 4) if fused_reduce else 3.0)
+            if best is None or cost < best[0] - 1e-9:
+                best = (cost, False, tile, s, per, 0)
     return best[1:]
 
 

@@ -92,7 +92,11 @@ class PagedAttention(Part):
         keys = min(ctx.kv_bucket or 0, self.window or (1 << 30))
         cache_bytes = 2 * ctx.n_entries * keys * k_pages.shape[1] * self.head_dim * k_pages.element_size()
         weight_bytes = self.w_qkv.numel() * self.w_qkv.element_size()
-        return ops.sm_count() // 3 if cache_bytes > 4 * weight_bytes else 0
+        if cache_bytes <= 4 * weight_bytes:
+            return 0
+        # from 32 rows on the product runs one CTA per SM (see ops.NORMAL_MODE_FROM_ROWS): half the SMs
+        # then measured best (64 requests: 1.29 ms a step with a third, 1.20 ms with half or all)
+        return ops.sm_count() // (2 if ctx.n_tokens >= ops.NORMAL_MODE_FROM_ROWS else 3)
 
     def forward(self, x: torch.Tensor, ctx, view) -> torch.Tensor:
         T = ctx.n_tokens
