@@ -116,7 +116,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   constexpr int Q_STAGE_BYTES = q_stage_bytes(BNQ);
   constexpr uint32_t TMEM_COLS = tmem_cols_for(BNQ);
   const uint32_t IDESC = idesc_bf16_f32(BP, tile_q);
-  const uint32_t stage_tx = (uint32_t)(P_STAGE_BYTES + tile_q * BK * 2);
+  // Fewer than 128 rows in the normal mode: the box of rows is only as tall as the tensor (the
+  // host encodes the map so), which keeps it inside and brings no bytes for rows that are not
+  // there; the MMA still reads 128 rows of the stage, and what it makes of the rest is not stored.
+  const int p_box = (!SWAP && M < BP) ? M : BP;
+  const uint32_t stage_tx = (uint32_t)(p_box * BK * 2 + tile_q * BK * 2);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -1051,7 +1055,8 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
   const void* P = swap ? W : A; const void* Q = swap ? A : W;
   const long long ldp = swap ? ldw : lda, ldq = swap ? lda : ldw;
   const int p_rows = swap ? N : M, q_rows = swap ? M : N;
-  if ((rc = get_map(&mp, P, p_rows, K, ldp, BP))) return rc;
+  // the one-tile kernel in the normal mode takes a box of rows no taller than the tensor (see the kernel)
+  if ((rc = get_map(&mp, P, p_rows, K, ldp, (!swap && cluster == 0 && M < BP) ? M : BP))) return rc;
   if ((rc = get_map(&mq, Q, q_rows, K, ldq, swiglu ? 128 : cluster == 3 ? tile / 2 : tile))) return rc;
   if (cluster == 3) {       // persistent kernel on pairs of CTAs: normal mode, no split
     LLMK_REQUIRE(!swap && splits == 1 && tile % 32 == 0 && tile >= 32 && tile <= 256,

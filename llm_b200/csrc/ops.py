@@ -516,8 +516,9 @@ def _plan_gemm(M: int, N: int, K: int, fused_reduce: bool, persistent: bool, pai
 # 1.1B shape with the kernel that sums the partial results behind them (us, swapped -> normal):
 # 32 rows 9.2 -> 8.5, 7.5 -> 6.7, 15.0 -> 10.6, 9.5 -> 10.2; 64 rows 11.4 -> 9.8, 9.3 -> 7.7, 17.9 ->
 # 11.1, 11.6 -> 11.0; 128 rows 15.2 -> 10.7, 13.2 -> 9.1, 27.5 -> 11.8, 16.1 -> 12.6; at 16 rows and
-# fewer the swapped mode is ahead (7.9 against 8.2, 8.0 against 10.0).
-NORMAL_MODE_FROM_ROWS = 32
+# fewer the swapped mode is ahead (7.9 against 8.2, 8.0 against 10.0).  Whole decode steps: 24 requests
+# 1.066 -> 1.055 ms, 31 requests 1.099 -> 1.087 ms, 64 requests 1.31 -> 1.20 ms; 17 requests the same.
+NORMAL_MODE_FROM_ROWS = 24
 
 
 def _plan_few_rows(M: int, N: int, kb: int, fused_reduce: bool, _SMS: int, cta_limit: int = 0):
