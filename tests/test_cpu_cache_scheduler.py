@@ -401,3 +401,25 @@ def test_ranges_of_the_decode_attention():
     assert decode_splits(8, 4, 520, sms) in (4, 5, 6)          # the benchmark's step: ranges of about 100 keys
     assert decode_splits(8, 4, 16384, sms) == 9                # 288 CTAs on 148 SMs
     assert decode_splits(1, 4, 1 << 20, sms) == 64
+
+
+def test_plans_of_the_tensor_core_product_cover_k():
+    """The planner's choices as arithmetic (no device): every plan splits K into parts that cover
+    it exactly once; up to 23 rows run the swapped mode, 24 to 128 rows one CTA per tile of 128 or
+    256 weight rows, and a limit on the CTAs is kept where K is split."""
+    from llm_b200.csrc import ops
+    for M in (1, 8, 16, 23, 24, 32, 64, 100, 128, 129, 300, 2048):
+        for N, K in ((2560, 2048), (2048, 5632), (11264, 2048), (32000, 2048), (22016, 4096), (344, 200), (72, 1000)):
+            for fused in (False, True):
+                swap, tile, splits, per, mode = ops._plan_gemm(M, N, K, fused, True, True, 148, 0)
+                kb = -(-K // 64)
+                assert splits >= 1 and per >= 1 and splits * per >= kb and -(-kb // per) == splits, (M, N, K)
+                assert swap == (M < ops.NORMAL_MODE_FROM_ROWS)
+                if swap:
+                    assert tile in (16, 32, 64, 128) and tile >= M
+                elif M <= 128:
+                    assert tile in (128, 256) and mode == 0
+                else:
+                    assert tile % 32 == 0 and 128 <= tile <= 256
+    swap, tile, splits, per, mode = ops._plan_gemm(64, 2560, 2048, True, True, True, 148, 49)
+    assert not swap and (splits == 1 or -(-2560 // tile) * splits <= 49)
