@@ -604,9 +604,11 @@ def gemm_fast_available(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, row
     """Whether the tcgen05 product takes this problem (bfloat16, rows of 16-byte multiples)."""
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         return False
+    # the conditions of llmk_gemm_tc_supported, checked here: this runs before every product of a
+    # step that is not replayed from a graph, and a call into the library costs microseconds
     n, k = w.shape
-    return bool(load_tensor().llmk_gemm_tc_supported(_ptr(a), _ptr(w), c_int(rows), c_int(n), c_int(k),
-                                              c_longlong(a.stride(0)), c_longlong(w.stride(0))))
+    return (rows > 0 and n > 0 and k > 0 and k % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and a.is_cuda and w.is_cuda)
 
 
 def gemm_fast(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, plan=None, allow_partial: bool = False,

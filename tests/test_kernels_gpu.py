@@ -237,6 +237,16 @@ def test_gemm_tensor_core_refuses_unaligned_rows(ops):
     w = torch.zeros(64, 172, device=DEV, dtype=torch.bfloat16)
     assert not ops.gemm_fast_available(a, w, torch.zeros(4, 64, device=DEV, dtype=torch.bfloat16), 4)
     assert not ops.gemm_fast_available(a.float(), w.float(), torch.zeros(4, 64, device=DEV), 4)
+    # the check made in Python agrees with the library's own
+    from ctypes import c_int, c_longlong, c_void_p
+    lib = ops.load_tensor()
+    base = torch.zeros(16, 520, device=DEV, dtype=torch.bfloat16)
+    for rows, k, col0, pitch_of in ((4, 512, 0, base), (4, 512, 8, base), (4, 512, 4, base), (4, 172, 0, base), (0, 512, 0, base)):
+        a2 = pitch_of[:max(rows, 1), col0:col0 + k]
+        w2 = torch.zeros(64, k, device=DEV, dtype=torch.bfloat16)
+        lib_says = bool(lib.llmk_gemm_tc_supported(c_void_p(a2.data_ptr()), c_void_p(w2.data_ptr()), c_int(rows), c_int(64), c_int(k),
+                                                    c_longlong(a2.stride(0)), c_longlong(w2.stride(0))))
+        assert ops.gemm_fast_available(a2, w2, None, rows) == lib_says, (rows, k, col0)
 
 
 def paged_reference(q, k, v, window, scale):
