@@ -1,5 +1,7 @@
 """GPU tests of the whole engine against the plain implementation: every way of
 cutting the work, in 32-bit and in bfloat16."""
+import random
+
 import pytest
 import torch
 
@@ -114,6 +116,69 @@ def test_decoding_at_a_context_of_thousands_of_keys(tmp_path_factory, dtype):
     bad = torch.nonzero(err_rows > TOL[dtype])
     assert bad.numel() == 0, f"first differs at position {head + int(bad[0])}: {float(err_rows[int(bad[0])]):.3e}"
     assert eng.counters["graph_replays"] >= tail - 4
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_workloads_match_plain(tmp_path_factory, seed):
+    """Random requests cut into random steps: portions of 1 to 160 tokens beside single tokens, up to
+    eight live, requests that sit a step out, entries in shuffled order, wanted rows picked at
+    random, a pool that only just holds the live requests (so pages are used again, poisoned in
+    between), graphs on or off; every wanted row against the plain implementation."""
+    from llm_b200.config import EngineOptions
+    from llm_b200.engine.engine import Engine, StepEntry
+    rng = random.Random(4000 + seed)
+    name = ["D", "E", "A", "C", "G", "H"][seed % 6]
+    dtype = "float32" if seed % 3 == 2 else "bfloat16"
+    cfg, page = CONFIGS[name]
+    d = make_model_dir(tmp_path_factory.mktemp("random"), name, dtype, peaked=seed % 2 == 0)
+    w = load_plain_weights(d)
+    lens = [rng.randint(1, min(cfg["max_position_embeddings"], 500)) for _ in range(rng.randint(3, 7))]
+    reqs = {f"r{i}": random_tokens(n, cfg["vocab_size"], seed * 100 + i) for i, n in enumerate(lens)}
+    ref = {rid: plain_llama.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    max_live = rng.randint(1, 8)
+    pool = sum((n + page - 1) // page for n in sorted(lens, reverse=True)[:max_live]) + rng.randint(0, 3)
+    budget = rng.choice([64, 200, 512])
+    eng = Engine(d, EngineOptions(dtype=dtype, kv_block_size=page, max_num_seqs=max_live, max_num_batched_tokens=budget,
+                                  num_kv_blocks=pool, use_cuda_graphs=rng.random() < 0.7, poison_freed_pages=True))
+    pending, live = list(reqs.items()), []
+    while pending or live:
+        while pending and len(live) < max_live and rng.random() < 0.7:
+            rid, toks = pending[0]
+            held = sum((len(t) + page - 1) // page for _, t, _ in live)
+            if held + (len(toks) + page - 1) // page > pool:
+                break
+            pending.pop(0)
+            live.append([rid, toks, 0])
+        entries, ended, left = [], [], budget
+        for item in live:
+            rid, toks, at = item
+            if rng.random() < 0.15 and len(live) > 1:
+                continue                                   # this request sits the step out
+            n = min(1 if rng.random() < 0.45 else rng.randint(1, 160), len(toks) - at, left)
+            if n <= 0:
+                continue
+            left -= n
+            want = sorted(rng.sample(range(n), rng.randint(0, min(n, 6)))) if rng.random() < 0.8 else list(range(n))
+            entries.append((rid, toks[at:at + n], want, at))
+            item[2] = at + n
+            if item[2] == len(toks):
+                ended.append(rid)
+        if not entries:
+            continue
+        rng.shuffle(entries)
+        out = eng.step([StepEntry(rid, t, wnt) for rid, t, wnt, _ in entries]).double().cpu()
+        row = 0
+        for rid, t, wnt, at in entries:
+            for k in wnt:
+                err = float((out[row] - ref[rid][at + k]).abs().max() / ref[rid].abs().max())
+                assert err <= TOL[dtype], (f"request {rid} position {at + k}: {err:.3e} in a step of "
+                                           f"{[(r, len(tt), a) for r, tt, _, a in entries]}")
+                row += 1
+        for rid in ended:
+            eng.release(rid)
+        live = [it for it in live if it[0] not in ended]
+    eng.check_status()
+    eng.cache.check()
 
 
 def test_peaked_attention_shows_one_wrong_page(models):
