@@ -2,6 +2,7 @@
 tokens of a sequence, temperature sampling against the plain sampler, running out of pages,
 CUDA graphs on and off."""
 import os
+import random
 import subprocess
 import sys
 
@@ -249,3 +250,37 @@ def test_preemption_in_bfloat16_with_graphs_and_lookahead(folders, name):
     _same_or_near_tie(cfg, load_plain_weights(d), prompts, got, want)
     tight.engine.cache.check()
     assert tight.engine.cache.num_free_pages(0) == tight_pages
+
+
+@pytest.mark.parametrize("seed", range(20))
+def test_random_generations_match_plain(folders, seed):
+    """Random prompts through LLM.generate and the scheduler with random limits: live requests,
+    token budget, a pool between what the longest request needs and what all need (so some runs
+    preempt and recompute), an end token or none, graphs and the one-step lookahead on or off.
+    The greedy tokens equal the plain implementation's, up to a near-tie of two logits."""
+    from llm_b200 import LLM
+    rng = random.Random(9000 + seed)
+    name = ["D", "E", "A", "B", "C", "F", "G"][seed % 7]
+    dtype = "float32" if seed % 2 else "bfloat16"
+    cfg, page = CONFIGS[name]
+    d = folders(name, dtype)
+    w = load_plain_weights(d)
+    new = rng.randint(1, 24)
+    prompts = [random_tokens(rng.randint(1, min(cfg["max_position_embeddings"] - new, 90)), cfg["vocab_size"], seed * 50 + i)
+               for i in range(rng.randint(1, 7))]
+    max_seqs = rng.randint(1, 6)
+    need_one = -(-(max(len(p) for p in prompts) + new) // page)
+    pool = need_one + rng.randint(0, need_one * (max_seqs - 1) + 2)
+    eos = rng.choice([-1, -1, rng.randrange(cfg["vocab_size"])])
+    llm = LLM(d, dtype=dtype, max_num_seqs=max_seqs, max_num_batched_tokens=rng.choice([16, 24, 64, 512]), kv_block_size=page,
+              num_kv_blocks=pool, eos_token_id=eos, use_cuda_graphs=rng.random() < 0.7, lookahead=rng.random() < 0.7)
+    got = llm.generate(prompts, max_new_tokens=new)
+    for p, g in zip(prompts, got):
+        want = pl.greedy_generate(cfg, w, p, new, eos_token_id=None if eos < 0 else eos)
+        if g != want:
+            k = next((i for i, (a, b) in enumerate(zip(g, want)) if a != b), min(len(g), len(want)))
+            assert k < len(g) and k < len(want), (g, want)
+            row = pl.forward(cfg, w, list(p) + want[:k])[-1]
+            assert abs(float(row[g[k]] - row[want[k]])) <= TOL[dtype] * float(row.abs().max()), (k, g, want)
+    llm.engine.cache.check()
+    assert llm.engine.cache.num_free_pages(0) == pool
