@@ -181,6 +181,51 @@ def test_random_workloads_match_plain(tmp_path_factory, seed):
     eng.cache.check()
 
 
+@pytest.mark.parametrize("seed", range(24))
+def test_random_configurations_match_plain(tmp_path_factory, seed):
+    """Random small configurations of the architecture: widths that are no powers of two (some with
+    rows that are no multiples of 16 bytes), any numbers of heads and groups, head sizes from 6 to
+    256, vocabularies, eps, theta, windows, tied heads, biases, page sizes; a prompt in two
+    portions and then tokens one by one, in 32-bit or bfloat16, against the plain implementation."""
+    import os
+
+    from llm_b200.config import EngineOptions
+    from llm_b200.engine.engine import Engine, StepEntry
+    from llm_b200.weights.loader import write_random_model
+    rng = random.Random(700 + seed)
+    n_kv, group = rng.choice([1, 1, 2, 3, 4, 5]), rng.choice([1, 1, 2, 3, 4, 8])
+    hidden = rng.choice([64, 72, 96, 128, 160, 200, 256]) + (rng.choice([2, 4, 6]) if rng.random() < 0.3 else 0)
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=hidden, intermediate_size=rng.choice([100, 172, 200, 256, 344]),
+               num_hidden_layers=rng.randint(1, 3), num_attention_heads=n_kv * group, num_key_value_heads=n_kv,
+               head_dim=rng.choice([16, 32, 48, 64, 64, 80, 96, 100, 128, 128, 112, 6, 256]),
+               vocab_size=rng.choice([97, 256, 301, 1000]), rms_norm_eps=rng.choice([1e-5, 1e-6, 1e-3]),
+               rope_theta=rng.choice([10000.0, 500000.0, 100.0]), max_position_embeddings=rng.choice([64, 200, 520]),
+               tie_word_embeddings=rng.random() < 0.3, hidden_act="silu")
+    if rng.random() < 0.3:
+        cfg["sliding_window"] = rng.randint(3, 90)
+    cfg["attention_bias"], cfg["mlp_bias"] = rng.random() < 0.25, rng.random() < 0.25
+    page = rng.choice([8, 16, 16, 32, 64])
+    dtype = "float32" if seed % 2 else "bfloat16"
+    d = os.path.join(str(tmp_path_factory.mktemp("cfg")), "model")
+    write_random_model(d, cfg, seed, dtype)
+    n = rng.randint(2, cfg["max_position_embeddings"])
+    toks = random_tokens(n, cfg["vocab_size"], seed)
+    ref = plain_llama.forward(cfg, load_plain_weights(d), toks)
+    eng = Engine(d, EngineOptions(dtype=dtype, kv_block_size=page, max_num_seqs=2, max_num_batched_tokens=600,
+                                  num_kv_blocks=n // page + 3, use_cuda_graphs=rng.random() < 0.6, poison_freed_pages=True))
+    head = n - rng.randint(0, min(20, n - 1))
+    cut = rng.randint(1, head)
+    rows = [eng.step([StepEntry("x", toks[:cut], list(range(cut)))]).double().cpu().clone()]
+    if cut < head:
+        rows.append(eng.step([StepEntry("x", toks[cut:head], list(range(head - cut)))]).double().cpu().clone())
+    for t in toks[head:]:
+        rows.append(eng.step([StepEntry("x", [t], [0])]).double().cpu().clone())
+    eng.check_status()
+    err_rows = (torch.cat(rows) - ref).abs().max(dim=1).values / ref.abs().max()
+    bad = torch.nonzero(err_rows > TOL[dtype])
+    assert bad.numel() == 0, f"{cfg}, page {page}: first differs at position {int(bad[0])}: {float(err_rows[int(bad[0])]):.3e}"
+
+
 def test_peaked_attention_shows_one_wrong_page(models):
     """What the peaked weights are for: two pages of values that trade places (the keys stay) move
     the bfloat16 logits of the next token far beyond the bound, while on the plain random weights,
